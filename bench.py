@@ -1,0 +1,320 @@
+#!/usr/bin/env python
+"""Benchmark of the policy-rollout forward (env-steps/s), one JSON line on stdout.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --steps K --warmup W    # CPU arm (host cores)
+
+A step is one batched policy forward over `--envs` envs per GPU (default 262,144,
+h256x2: the configuration the headline metric is quoted on) with synthetic records,
+N(0,1) recurrent state and N(0,1/fan_in) weights.  `value` is timed with CUDA events
+on the launching stream with inputs resident in HBM; `e2e` goes through
+cfx_policy_forward_host with pinned host buffers (copies inside the timed region).
+Under torchrun each rank drives its own GPU and its own contiguous slice of envs;
+there is no data-path collective, only a barrier and a max over ranks of the timings.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "craftax.cu_b200"))
+
+A = 43
+METRIC = "policy_fwd_env_steps_per_s"
+UNIT = "env-steps/s"
+
+
+def algorithmic_work(H, L):
+    """Per env-step: FLOPs of the three GEMM stages and bytes that must cross HBM
+    (record, state read+write, logits+value, action, logprob, env action, prev_terminal)."""
+    flops = 2 * 843 * H + L * 2 * 3 * H * H + 2 * (A + 1) * H
+    byts = 996 + L * H * 4 * 2 + (A + 1) * 4 + 4 + 4 + 4 + 4
+    return flops, byts
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.thread.join(timeout=2)
+        mhz = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [nm for i, nm in enumerate(names)
+                   if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": float(np.median(mhz)) if mhz else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(mhz)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def run_cfx(args):
+    import cfx
+    rank, world, local = dist_env()
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = local
+    n, H, L = args.envs, args.hidden, args.layers
+    prec = args.precision
+    rng = np.random.default_rng(4 + rank)
+    from cfx.synth import synthetic_records, init_weights
+    base = synthetic_records(min(n, 8192), seed=4 + rank)
+    rec = np.tile(base, (n // base.shape[0] + 1, 1))[:n]
+    rec = rec[rng.permutation(n)] if n <= 65536 else rec
+    params = init_weights(H, L, A, seed=0)
+    pol = cfx.Policy(n, H, L, A, prec, device=dev)
+    pol.set_weights(params)
+    state = rng.standard_normal((L, n, H), dtype=np.float32)
+    pol.set_state(state)
+    del state
+    prev_t = (rng.random(n) < 1.0 / 265.0).astype(np.float32)
+    d_rec = cfx.DeviceBuffer.from_host(rec, dev)
+    d_pt = cfx.DeviceBuffer.from_host(prev_t, dev)
+    d_env = cfx.DeviceBuffer((n,), np.float32, dev)
+    d_act = cfx.DeviceBuffer((n,), np.int32, dev)
+    d_lp = cfx.DeviceBuffer((n,), np.float32, dev)
+    d_val = cfx.DeviceBuffer((n,), np.float32, dev)
+    d_lav = cfx.DeviceBuffer((n, A + 1), np.float32, dev)
+    stream = pol.stream
+
+    def step():
+        pol.forward_device(d_rec, d_pt, None, env_actions=d_env, actions=d_act, logprobs=d_lp,
+                           values=d_val, logits_av=d_lav, seed=2, env_offset=rank * n,
+                           bump_step=True, stream=stream)
+
+    def barrier():
+        if dist is not None:
+            import torch
+            dist.barrier()
+            torch.cuda.synchronize()
+        pol.sync()
+
+    for _ in range(args.warmup):
+        step()
+    pol.sync()
+    launches_per_step = pol.last_launches
+    sampler = ClockSampler(dev)
+    sampler.start()
+    timers = [cfx.Timer(dev) for _ in range(args.steps)]
+    barrier()
+    t_all = cfx.Timer(dev)
+    t_all.start(stream)
+    for t in timers:
+        t.start(stream)
+        step()
+        t.stop(stream)
+    t_all.stop(stream)
+    barrier()
+    total_ms = t_all.elapsed_ms()
+    per_step = [t.elapsed_ms() for t in timers]
+    clocks = sampler.stop()
+
+    # end to end through the host-buffer entry point, pinned buffers
+    pin_rec = cfx.PinnedBuffer((n, 996), np.uint8)
+    pin_rec.array[:] = rec
+    pin_pt = cfx.PinnedBuffer((n,), np.float32)
+    pin_pt.array[:] = prev_t
+    outs = {k: cfx.PinnedBuffer((n,), dt) for k, dt in
+            [("env_actions", np.float32), ("actions", np.int32), ("logprobs", np.float32),
+             ("values", np.float32)]}
+    out_arrays = {k: v.array for k, v in outs.items()}
+    e2e_steps = max(2, min(args.steps, 10))
+    for _ in range(2):
+        pol.forward_host(pin_rec.array, pin_pt.array, None, seed=2, env_offset=rank * n,
+                         bump_step=True, want_logits=False, out=out_arrays)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        pol.forward_host(pin_rec.array, pin_pt.array, None, seed=2, env_offset=rank * n,
+                         bump_step=True, want_logits=False, out=out_arrays)
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    h2d = n * 996 + n * 4
+    d2h = 4 * n * 4
+
+    if dist is not None:
+        import torch
+        v = torch.tensor([total_ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        total_ms, e2e_ms = v.tolist()
+    ms_per_step = total_ms / args.steps
+    value = world * n / (ms_per_step * 1e-3)
+    flops, byts = algorithmic_work(H, L)
+    peaks = load_peaks()
+    kernel_ms = float(np.mean(per_step))
+    tensor_peak = peaks["bf16_tflops"] * (0.5 if prec == "tf32" else 1.0)
+    t_hbm = n * byts / (peaks["hbm_gbs"] * 1e9)
+    t_tensor = n * flops / (tensor_peak * 1e12)
+    if prec == "fp32" or t_hbm >= t_tensor:
+        roof = {"bound": "hbm", "achieved": n * byts / (kernel_ms * 1e-3) / 1e9,
+                "peak": peaks["hbm_gbs"], "unit": "GB/s"}
+    else:
+        roof = {"bound": "tensor", "achieved": n * flops / (kernel_ms * 1e-3) / 1e12,
+                "peak": tensor_peak, "unit": "TFLOP/s"}
+    roof["frac"] = roof["achieved"] / roof["peak"]
+    roof["traffic"] = None
+    roof["peak_source"] = peaks["source"]
+    roof["fused_roofline_ms"] = max(t_hbm, t_tensor) * 1e3
+    roof["fused_roofline_frac"] = max(t_hbm, t_tensor) * 1e3 / kernel_ms
+    roof["kernel_ms"] = kernel_ms
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None,
+        "dtype": {"fp32": "f32", "f16": "f16 operands, f32 accumulate",
+                  "bf16": "bf16 operands, f32 accumulate",
+                  "tf32": "tf32 operands, f32 accumulate"}[prec],
+        "data": "synthetic",
+        "config": {"workload": f"policy forward, {n} envs/GPU, h{H}x{L}, {A} actions, 996-B records",
+                   "envs_per_gpu": n, "hidden": H, "layers": L, "precision": prec,
+                   "sharding": f"contiguous env slices x{world}, no collective",
+                   "l2": "inputs larger than L2 (records+state %.0f MB per GPU)"
+                         % ((n * 996 + L * n * H * 4) / 1e6)},
+        "roofline": roof,
+        "e2e": {"value": world * n / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_forward_rate(H, L, budget_s=args.cpu_budget)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def cpu_forward_rate(H, L, budget_s=15.0, steps=1, warmup=0, threads=0):
+    """Times the CPU arm: the reference's C env (when its prebuilt producer is present)
+    stepping a bounded sample of envs plus the oracle's fp32 host forward on all host
+    threads.  Returns the cpu_baseline object."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle as O
+    cores = threads or O.max_threads()
+    params = O.init_weights(H, L, A, seed=0)
+    probe = 64 * cores
+    rec = O.synthetic_records(probe, seed=4)
+    st = np.zeros((L, probe, H), np.float32)
+    t0 = time.perf_counter()
+    O.forward(params, rec, None, st, H, L, A, threads=cores)
+    rate = probe / (time.perf_counter() - t0)
+    per_step = max(32 * cores, int(rate * budget_s / max(1, steps + warmup)) // 32 * 32)
+    use_env = O.RefEnv.available()
+    env = O.RefEnv(per_step, 0) if use_env else None
+    rec = env.records if use_env else O.synthetic_records(per_step, seed=4)
+    st = np.zeros((L, per_step, H), np.float32)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        lav = O.forward(params, rec, env.terminals if use_env else None, st, H, L, A, threads=cores)
+        if use_env:
+            env.step(np.argmax(lav[:, :A], 1).astype(np.float32))
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    if env:
+        env.close()
+    v = per_step / float(np.mean(times))
+    return {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{per_step} envs x {steps} step(s): "
+                      + ("reference C env (craftax_full.c, compact obs) stepping + " if use_env else "")
+                      + "oracle fp32 scalar forward, OpenMP over envs",
+            "ms_per_step": float(np.mean(times)) * 1e3, "envs_per_step": per_step}
+
+
+def run_reference(args):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    H, L = args.hidden, args.layers
+    total = max(1, args.steps + args.warmup)
+    b = cpu_forward_rate(H, L, budget_s=min(120.0, 12.0 * total), steps=args.steps,
+                         warmup=args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": b["value"], "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": b["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"policy forward, {args.envs} envs/GPU, h{H}x{L}, {A} actions, 996-B records",
+                   "envs_per_gpu": args.envs, "hidden": H, "layers": L,
+                   "note": "CPU arm: bounded sample of the workload per step on the host cores"},
+        "cpu_baseline": {k: b[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": b["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="cfx", choices=["cfx", "reference"])
+    ap.add_argument("--envs", type=int, default=262144, help="envs per GPU")
+    ap.add_argument("--hidden", type=int, default=256)
+    ap.add_argument("--layers", type=int, default=2)
+    ap.add_argument("--precision", default=None, choices=["fp32", "f16", "bf16", "tf32"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-budget", type=float, default=15.0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "cfx" else args.warmup
+    if args.precision is None:
+        args.precision = DEFAULT_PRECISION
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_cfx(args)
+
+
+DEFAULT_PRECISION = "fp32"
+
+if __name__ == "__main__":
+    main()

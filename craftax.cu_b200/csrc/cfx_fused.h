@@ -1,0 +1,36 @@
+// Interface of the fused tcgen05 forward (one kernel per step) to the C-ABI layer.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace cfx {
+
+struct FusedPlan;  // operand mirrors, tensor maps, status word; owned by the handle
+
+struct FusedArgs {
+    const uint8_t* records;
+    const float* prev_terminals;
+    const float* uniforms;
+    float* state;  // [L][n][H]
+    float* env_actions;
+    int32_t* actions;
+    float* logprobs;
+    float* values;
+    float* logits_av;
+    float* r_state;
+    uint64_t seed, env_offset;
+    const unsigned long long* step_ctr;
+};
+
+// Shapes the fused kernel is instantiated for.
+bool fused_supported(int H, int L, int A, int precision);
+int fused_create(FusedPlan** out, int device, int n, int H, int L, int A, int precision,
+                 float* state);
+// Rebuilds the operand mirrors from the fp32 arena (device pointer).
+int fused_refresh(FusedPlan* plan, const float* params, cudaStream_t st);
+int fused_forward(FusedPlan* plan, const FusedArgs& a, cudaStream_t st, int* launches);
+// Reads and clears the device status word (non-zero = a bounded wait gave up).
+int fused_check_status(FusedPlan* plan, cudaStream_t st, unsigned* status);
+void fused_destroy(FusedPlan* plan);
+
+}  // namespace cfx

@@ -1,0 +1,196 @@
+/*
+ * cfx.h -- C ABI of the B200 policy-rollout forward for craftax.cu.
+ *
+ * The reference keeps its whole host side `static` in one translation unit
+ * (craftax_full.cu) and is reused by #include under -DCRAFTAX_CU_LIB; it has
+ * no exported ABI.  Each entry point below therefore cites the reference
+ * function whose job it takes over inside the `run` rollout loop
+ * (cu_rollout_step, craftax_full.cu:12022-12087).
+ *
+ * Conventions: plain pointers and sizes only; `stream` arguments are
+ * cudaStream_t passed as void* (NULL = the handle's own non-blocking stream);
+ * every function returns a cfx_status and never exits the process (the
+ * reference prints and exit(1)s, craftax_full.cu:8635-8642); cfx_last_error()
+ * gives the message for the calling thread.  All device pointers must belong
+ * to the handle's device.  There is no CPU fallback: without a usable GPU and
+ * the compiled kernels every compute call fails.
+ */
+#ifndef CFX_H
+#define CFX_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CFX_OBS_FEATURES 843 /* CF_NN_OBS,     craftax_full.cu:9089  */
+#define CFX_OBS_MAP 792      /* CF_NN_MAP,     craftax_full.cu:9091  */
+#define CFX_OBS_TAIL 51      /* CF_NN_TAIL,    craftax_full.cu:9092  */
+#define CFX_RECORD_BYTES 996 /* CF_TRAIN_OBS,  craftax_full.cu:9111  */
+
+typedef enum cfx_status {
+    CFX_OK = 0,
+    CFX_ERR_INVALID = 1,        /* bad argument (null, size, alignment, n % 32) */
+    CFX_ERR_CUDA = 2,           /* a CUDA runtime/driver call failed            */
+    CFX_ERR_DEVICE_TIMEOUT = 3, /* a bounded wait inside a kernel gave up       */
+    CFX_ERR_IO = 4,             /* checkpoint file problem                      */
+    CFX_ERR_UNSUPPORTED = 5     /* shape/precision not built into this library  */
+} cfx_status;
+
+/* GEMM operand type of the forward.  Accumulation, the MinGRU cell, the
+ * recurrent state and every output are fp32 in all modes. */
+typedef enum cfx_precision {
+    CFX_PREC_FP32 = 0, /* CUDA-core fmaf in the scalar reference's summation order
+                          (role of CRAFTAX_VERIFY_FP32, craftax_full.cu:12513)   */
+    CFX_PREC_F16 = 1,  /* fused tcgen05 kernel, fp16 operands (11-bit significand,
+                          the same as tf32, at the bf16 rate)                    */
+    CFX_PREC_BF16 = 2, /* fused tcgen05 kernel, bf16 operands (the reference's
+                          CF_GEMM_BF16 mode, craftax_full.cu:11309)              */
+    CFX_PREC_TF32 = 3  /* fused tcgen05 kernel, tf32 operands (the reference's
+                          cublasSgemm TF32 mode, craftax_full.cu:11297)          */
+} cfx_precision;
+
+typedef struct cfx_policy cfx_policy;
+
+/* Number of fp32 parameters of the flat arena
+ * W_enc[843][H] | b_enc[H] | W_gru[L][3H][H] | W_a[A][H] | b_a[A] | W_v[H] | b_v
+ * (CF_NN_PARAM_COUNT, craftax_full.cu:9094-9102). */
+size_t cfx_param_count(int hidden, int layers, int num_actions);
+
+/* Replaces cu_policy_init (craftax_full.cu:11819-11907): allocates the
+ * parameter arena, operand mirrors, the zeroed recurrent state [L][n][H], the
+ * device step counter (= 0) and a non-blocking stream on `device`.
+ * num_envs must be a positive multiple of 32 (craftax_full.cu:11820).
+ * Weights start as zeros; call one of the three setters below. */
+int cfx_policy_create(cfx_policy** out, int device, int num_envs, int hidden,
+                      int layers, int num_actions, int precision);
+
+/* Replaces cu_policy_free (craftax_full.cu:11909-11921). */
+int cfx_policy_destroy(cfx_policy* p);
+
+/* Copies a full arena (host pointer, or device pointer when on_device != 0)
+ * and rebuilds the operand mirrors -- the job of cu_params_refresh_bf16 +
+ * cu_pack_wav (craftax_full.cu:11805-11817), also what a trainer calls after
+ * each optimiser step (craftax_full.cu:13343-13344). */
+int cfx_policy_set_weights(cfx_policy* p, const float* arena, size_t count, int on_device);
+
+/* Copies the fp32 arena back to host memory. */
+int cfx_policy_get_weights(cfx_policy* p, float* host_arena, size_t count);
+
+/* The reference's own initialiser: seven segments drawn U(+-1/sqrt(fan_in))
+ * from Philox4_32_10(seed, subsequence = segment, offset = index)
+ * (k_nn_init_weights craftax_full.cu:9123-9131, segments :11832-11845;
+ * the reference passes seed 1234). */
+int cfx_policy_init_weights(cfx_policy* p, uint64_t seed);
+
+/* CFW1 checkpoint: 16-byte header {0x31574643, hidden, layers, param_count}
+ * then the fp32 arena (cu_save_weights / cu_load_weights,
+ * craftax_full.cu:12244-12293).  Load validates all four header words. */
+int cfx_policy_save_cfw1(cfx_policy* p, const char* path);
+int cfx_policy_load_cfw1(cfx_policy* p, const char* path);
+
+/* Switches the operand type (the reference's CF_GEMM_BF16 / math-mode
+ * switches, craftax_full.cu:11306-11312, 12512-12514) and rebuilds mirrors. */
+int cfx_policy_set_precision(cfx_policy* p, int precision);
+int cfx_policy_get_precision(const cfx_policy* p);
+
+/* Device pointer to the live recurrent state, fp32 [layers][num_envs][hidden]
+ * (CuPolicy.h_state, craftax_full.cu:11761, element l*H*n + e*H + k as indexed
+ * by k_mingru_epi_fwd :9361), and a zero fill of it. */
+float* cfx_policy_state(cfx_policy* p);
+int cfx_policy_reset_state(cfx_policy* p, void* stream);
+
+/* Device step counter = Philox sampler offset (CuPolicy.step_ctr,
+ * craftax_full.cu:11773; k_bump_ctr :9770).  Reading it on the device keeps
+ * the forward replayable from a CUDA graph. */
+int cfx_policy_set_step(cfx_policy* p, uint64_t step, void* stream);
+int cfx_policy_get_step(cfx_policy* p, uint64_t* step);
+int cfx_policy_bump_step(cfx_policy* p, void* stream);
+
+/* The handle's stream; number of kernels the last forward launched. */
+void* cfx_policy_stream(cfx_policy* p);
+int cfx_policy_last_launches(const cfx_policy* p);
+
+/* One batched policy forward: everything cu_rollout_step does between "the
+ * record row is complete" and "the env action slots are filled"
+ * (k_expand_obs :10028, encoder GEMM + k_add_bias :11954-11962, cu_gru_chain
+ * :11978, head GEMM :12040-12045, k_value_sample :9714).
+ *
+ * Inputs (device): records uint8 [n][996] (16-byte aligned base);
+ * prev_terminals float [n] (CuVec.d_terminals; non-zero zeroes that env's
+ * state before use; NULL = none); uniforms float [n] or NULL.  With NULL the
+ * kernel draws u = curand_uniform(Philox4_32_10(seed ^ 0xA5A5A5A5A5A5A5A5,
+ * subsequence = env_offset + e, offset = device step counter)) exactly as
+ * k_value_sample does (:9733-9736).
+ * Outputs (device, any may be NULL except actions): env_actions float [n]
+ * (CuVec.d_actions, read back by the env step), actions int32 [n], logprobs
+ * float [n], values float [n]; logits_av float [n][A+1] = logits and value
+ * WITH biases added (the reference's scratch holds them before the bias add,
+ * :9725-9730); r_state float [L][n][H] = post-zero state inputs for BPTT
+ * (:9370-9375; fp32 only).
+ * The recurrent state is updated in place.  The step counter is bumped on
+ * the device after the forward when bump_step != 0.
+ * No allocation, no host synchronisation and no host-varying kernel argument
+ * happens inside: the call is capturable in a CUDA graph. */
+typedef struct cfx_forward_io {
+    const uint8_t* records;
+    const float* prev_terminals;
+    const float* uniforms;
+    float* env_actions;
+    int32_t* actions;
+    float* logprobs;
+    float* values;
+    float* logits_av;
+    float* r_state;
+    uint64_t seed;
+    uint64_t env_offset;
+    int bump_step;
+} cfx_forward_io;
+
+int cfx_policy_forward(cfx_policy* p, const cfx_forward_io* io, void* stream);
+
+/* Same forward with HOST buffers (pinned for full copy speed): copies
+ * records/prev_terminals/uniforms to handle-owned device staging, runs
+ * cfx_policy_forward, copies every non-NULL output back and synchronises. */
+int cfx_policy_forward_host(cfx_policy* p, const cfx_forward_io* host_io);
+
+/* Stand-alone stages, for the reference's bitwise gates.
+ * cfx_expand_obs: records -> fp32 features [n][843], bit-exact image of
+ * k_expand_obs (:10028-10053).  cfx_sample_actions: logits [n][ld] (biases
+ * included) + uniforms -> action, logprob; the arithmetic of
+ * cf_nn_sample_action (:9147-9165).  cfx_philox_uniforms: the uniforms the
+ * forward would draw for (seed, env_offset, step). */
+int cfx_expand_obs(int device, const uint8_t* records, float* features, int n, void* stream);
+int cfx_sample_actions(int device, const float* logits, int ld, int num_actions,
+                       const float* uniforms, int n, int32_t* actions, float* logprobs,
+                       void* stream);
+int cfx_philox_uniforms(int device, uint64_t seed, uint64_t env_offset, uint64_t step,
+                        int n, float* uniforms, void* stream);
+
+/* Thin device-memory and timing helpers so that C, C++ or ctypes callers need
+ * no other CUDA binding (cudaMalloc / cudaMemcpyAsync / cudaEvent wrappers). */
+int cfx_device_count(int* count);
+int cfx_device_name(int device, char* buf, size_t len, int* sm_count, int* cc_major, int* cc_minor);
+int cfx_device_alloc(int device, void** ptr, size_t bytes);
+int cfx_device_free(int device, void* ptr);
+int cfx_host_alloc_pinned(void** ptr, size_t bytes);
+int cfx_host_free_pinned(void* ptr);
+int cfx_memcpy_h2d(int device, void* dst, const void* src, size_t bytes, void* stream);
+int cfx_memcpy_d2h(int device, void* dst, const void* src, size_t bytes, void* stream);
+int cfx_memset(int device, void* dst, int value, size_t bytes, void* stream);
+int cfx_stream_sync(int device, void* stream);
+int cfx_timer_create(int device, void** timer);
+int cfx_timer_destroy(void* timer);
+int cfx_timer_start(void* timer, void* stream); /* cudaEventRecord on `stream` */
+int cfx_timer_stop(void* timer, void* stream);
+int cfx_timer_elapsed_ms(void* timer, float* ms); /* synchronises on the stop event */
+
+const char* cfx_last_error(void);
+const char* cfx_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CFX_H */

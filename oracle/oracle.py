@@ -1,0 +1,159 @@
+"""ctypes front end of the CPU oracle (TEST INFRASTRUCTURE).
+
+Only tests, the smoke check and the bench's CPU-baseline leg import this
+module.  It wraps ``libcfx_oracle.so`` (the C restatement of the reference's
+scalar fp32 policy, see cfx_oracle.c) and, when present, the record producer
+built from the reference's own C environment (``_ref/libcfref_env.so``).
+"""
+import ctypes as C
+import os
+import subprocess
+import sys
+
+import numpy as np
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                                "craftax.cu_b200"))
+from cfx.synth import MAP, OBS, REC, TAIL, init_weights, offsets, synthetic_records  # noqa: E402,F401
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+_lib = None
+
+
+def build():
+    """Compile the oracle (and the reference-derived helpers when the
+    reference sources are present)."""
+    subprocess.run(["make", "-s", "-C", HERE], check=True)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = os.path.join(HERE, "libcfx_oracle.so")
+        if not os.path.exists(path):
+            build()
+        L = C.CDLL(path)
+        L.cfxo_param_count.restype = C.c_size_t
+        L.cfxo_param_count.argtypes = [C.c_int] * 3
+        L.cfxo_expand.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+        L.cfxo_sample.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int,
+                                  C.c_void_p, C.c_void_p]
+        L.cfxo_forward.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                   C.c_void_p, C.c_void_p, C.c_int, C.c_void_p,
+                                   C.c_void_p, C.c_void_p]
+        L.cfxo_max_threads.restype = C.c_int
+        L.cfxo_set_threads.argtypes = [C.c_int]
+        _lib = L
+    return _lib
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def param_count(H=256, L=2, A=43):
+    return int(lib().cfxo_param_count(H, L, A))
+
+
+def expand(rec):
+    rec = np.ascontiguousarray(rec, np.uint8).reshape(-1, REC)
+    out = np.empty((rec.shape[0], OBS), np.float32)
+    lib().cfxo_expand(_p(rec), _p(out), rec.shape[0])
+    return out
+
+
+def sample(logits, u, A=43):
+    logits = np.ascontiguousarray(logits, np.float32)
+    n, ld = logits.shape
+    u = np.ascontiguousarray(u, np.float32)
+    act = np.empty(n, np.int32)
+    lp = np.empty(n, np.float32)
+    lib().cfxo_sample(_p(logits), ld, A, _p(u), n, _p(act), _p(lp))
+    return act, lp
+
+
+def forward(params, rec, prev_terminals, state, H=256, L=2, A=43, want_h=False,
+            want_r_state=False, threads=0):
+    """One forward.  state [L][n][H] is updated in place.  Returns logits_av
+    [n][A+1] (biases included, value in column A) and optional extras."""
+    rec = np.ascontiguousarray(rec, np.uint8).reshape(-1, REC)
+    n = rec.shape[0]
+    params = np.ascontiguousarray(params, np.float32)
+    assert params.size == param_count(H, L, A)
+    assert state.dtype == np.float32 and state.shape == (L, n, H) and state.flags.c_contiguous
+    pt = None if prev_terminals is None else np.ascontiguousarray(prev_terminals, np.float32)
+    lav = np.empty((n, A + 1), np.float32)
+    h = np.empty((n, H), np.float32) if want_h else None
+    rs = np.empty((L, n, H), np.float32) if want_r_state else None
+    if threads:
+        lib().cfxo_set_threads(threads)
+    lib().cfxo_forward(_p(params), H, L, A, _p(rec), _p(pt), _p(state), n, _p(lav), _p(h), _p(rs))
+    out = [lav]
+    if want_h:
+        out.append(h)
+    if want_r_state:
+        out.append(rs)
+    return out[0] if len(out) == 1 else tuple(out)
+
+
+def max_threads():
+    return int(lib().cfxo_max_threads())
+
+
+class RefEnv:
+    """The reference's C environment (compact-obs build) as a record producer.
+    Available only where ``_ref/libcfref_env.so`` has been built."""
+
+    path = os.path.join(HERE, "_ref", "libcfref_env.so")
+
+    @classmethod
+    def available(cls):
+        return os.path.exists(cls.path)
+
+    def __init__(self, n, seed):
+        L = C.CDLL(self.path)
+        L.refenv_create.restype = C.c_void_p
+        L.refenv_create.argtypes = [C.c_int, C.c_ulonglong]
+        for f in ("refenv_records", "refenv_terminals", "refenv_rewards", "refenv_actions"):
+            getattr(L, f).restype = C.c_void_p
+            getattr(L, f).argtypes = [C.c_void_p]
+        L.refenv_step_random.argtypes = [C.c_void_p]
+        L.refenv_step.argtypes = [C.c_void_p, C.c_void_p]
+        L.refenv_destroy.argtypes = [C.c_void_p]
+        assert L.refenv_record_size() == REC
+        self.L, self.n = L, n
+        self.h = L.refenv_create(n, seed)
+
+    def _view(self, ptr, shape, dtype):
+        size = int(np.prod(shape)) * np.dtype(dtype).itemsize
+        buf = (C.c_char * size).from_address(ptr)
+        return np.frombuffer(buf, dtype=dtype).reshape(shape)
+
+    @property
+    def records(self):
+        return self._view(self.L.refenv_records(self.h), (self.n, REC), np.uint8)
+
+    @property
+    def terminals(self):
+        return self._view(self.L.refenv_terminals(self.h), (self.n,), np.float32)
+
+    @property
+    def rewards(self):
+        return self._view(self.L.refenv_rewards(self.h), (self.n,), np.float32)
+
+    @property
+    def actions(self):
+        return self._view(self.L.refenv_actions(self.h), (self.n,), np.float32)
+
+    def step_random(self):
+        self.L.refenv_step_random(self.h)
+
+    def step(self, actions):
+        a = np.ascontiguousarray(actions, np.float32)
+        self.L.refenv_step(self.h, _p(a))
+
+    def close(self):
+        if self.h:
+            self.L.refenv_destroy(self.h)
+            self.h = None
