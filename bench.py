@@ -153,6 +153,7 @@ def run_cfx(args):
         t.stop(stream)
     t_all.stop(stream)
     barrier()
+    pol.check()
     total_ms = t_all.elapsed_ms()
     per_step = [t.elapsed_ms() for t in timers]
     clocks = sampler.stop()
@@ -314,7 +315,7 @@ def main():
         run_cfx(args)
 
 
-DEFAULT_PRECISION = "fp32"
+DEFAULT_PRECISION = "f16"
 
 if __name__ == "__main__":
     main()

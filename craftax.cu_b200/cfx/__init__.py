@@ -53,6 +53,7 @@ _SIGS = {
     "cfx_policy_last_launches": (C.c_int, [C.c_void_p]),
     "cfx_policy_forward": (C.c_int, [C.c_void_p, C.POINTER(ForwardIO), C.c_void_p]),
     "cfx_policy_forward_host": (C.c_int, [C.c_void_p, C.POINTER(ForwardIO)]),
+    "cfx_policy_check": (C.c_int, [C.c_void_p, C.c_void_p]),
     "cfx_expand_obs": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "cfx_sample_actions": (C.c_int, [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int,
                                      C.c_void_p, C.c_void_p, C.c_void_p]),
@@ -284,6 +285,10 @@ class Policy:
 
     def sync(self):
         check(lib().cfx_stream_sync(self.device, self.stream))
+
+    def check(self, stream=None):
+        """Synchronise and raise if a device-side bounded wait gave up."""
+        check(lib().cfx_policy_check(self.h, stream))
 
     @property
     def last_launches(self):

@@ -420,6 +420,23 @@ int cfx_policy_forward(cfx_policy* p, const cfx_forward_io* io, void* stream) {
 
 }  // extern "C"
 
+extern "C" int cfx_policy_check(cfx_policy* p, void* stream) {
+    CFX_REQUIRE(p, "cfx_policy_check: NULL handle");
+    DeviceGuard g(p->device);
+    cudaStream_t st = stream ? (cudaStream_t)stream : p->stream;
+    CFX_CUDA(cudaStreamSynchronize(st));
+    if (p->fused) {
+        unsigned status = 0;
+        int rc = fused_check_status(p->fused, st, &status);
+        if (rc) return rc;
+        if (status) {
+            set_error("device-side wait timed out: site %u, block %u", status & 0xFF, status >> 8);
+            return CFX_ERR_DEVICE_TIMEOUT;
+        }
+    }
+    return CFX_OK;
+}
+
 // ------------------------------------------------------------------ host-buffer forward
 template <typename T>
 static int ensure_staging(T** slot, size_t count) {
@@ -478,17 +495,7 @@ int cfx_policy_forward_host(cfx_policy* p, const cfx_forward_io* h) {
         CFX_CUDA(cudaMemcpyAsync(h->logits_av, p->st_logits, lav * sizeof(float), cudaMemcpyDeviceToHost, st));
     if (h->r_state)
         CFX_CUDA(cudaMemcpyAsync(h->r_state, p->st_r_state, rs * sizeof(float), cudaMemcpyDeviceToHost, st));
-    CFX_CUDA(cudaStreamSynchronize(st));
-    if (p->fused) {
-        unsigned status = 0;
-        rc = fused_check_status(p->fused, st, &status);
-        if (rc) return rc;
-        if (status) {
-            set_error("cfx_policy_forward_host: device-side wait timed out (status 0x%08x)", status);
-            return CFX_ERR_DEVICE_TIMEOUT;
-        }
-    }
-    return CFX_OK;
+    return cfx_policy_check(p, st);
 }
 
 // ------------------------------------------------------------------ stand-alone stages

@@ -151,6 +151,13 @@ typedef struct cfx_forward_io {
 
 int cfx_policy_forward(cfx_policy* p, const cfx_forward_io* io, void* stream);
 
+/* Synchronises `stream` (NULL = the handle's stream) and reports a device-side failure of
+ * any forward since the last check: every wait inside the fused kernel is bounded, and a
+ * wait that gives up ends the kernel and leaves a status word behind
+ * (CFX_ERR_DEVICE_TIMEOUT).  The reference has no counterpart (its kernels cannot time
+ * out; errors surface through CU_CHECK, craftax_full.cu:8635). */
+int cfx_policy_check(cfx_policy* p, void* stream);
+
 /* Same forward with HOST buffers (pinned for full copy speed): copies
  * records/prev_terminals/uniforms to handle-owned device staging, runs
  * cfx_policy_forward, copies every non-NULL output back and synchronises. */

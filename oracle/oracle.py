@@ -157,3 +157,103 @@ class RefEnv:
         if self.h:
             self.L.refenv_destroy(self.h)
             self.h = None
+
+
+class RefCuda:
+    """The reference's own CUDA policy forward (its kernels and cuBLAS wrappers, compiled
+    from its sources by oracle/Makefile into ``_ref/libcfref_cuda_l{L}.so``).  Runs only
+    on a GPU box; used to pin the oracle and the fused kernel and as the GPU baseline."""
+
+    BF16, TF32, FP32 = 0, 1, 2
+
+    @classmethod
+    def path(cls, layers):
+        return os.path.join(HERE, "_ref", f"libcfref_cuda_l{layers}.so")
+
+    @classmethod
+    def available(cls, layers=2):
+        return os.path.exists(cls.path(layers))
+
+    def __init__(self, n, layers=2):
+        L = C.CDLL(self.path(layers))
+        L.refcu_create.restype = C.c_void_p
+        L.refcu_create.argtypes = [C.c_int]
+        L.refcu_destroy.argtypes = [C.c_void_p]
+        L.refcu_set_weights.argtypes = [C.c_void_p, C.c_void_p]
+        L.refcu_get_weights.argtypes = [C.c_void_p, C.c_void_p]
+        L.refcu_set_state.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        L.refcu_get_state.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        L.refcu_set_step.argtypes = [C.c_void_p, C.c_ulonglong]
+        L.refcu_forward.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_ulonglong,
+                                    C.c_void_p] + [C.c_void_p] * 5
+        L.refcu_time_forward.restype = C.c_float
+        L.refcu_time_forward.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
+                                         C.c_int, C.c_int]
+        L.refcu_scalar_set_state.argtypes = [C.c_void_p, C.c_void_p]
+        L.refcu_scalar_get_state.argtypes = [C.c_void_p, C.c_void_p]
+        L.refcu_scalar_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_ulonglong] + \
+            [C.c_void_p] * 4
+        assert L.refcu_layers() == layers and L.refcu_hidden() == 256
+        self.L, self.n, self.layers, self.H = L, n, layers, 256
+        self.h = L.refcu_create(n)
+
+    def set_weights(self, params):
+        p = np.ascontiguousarray(params, np.float32)
+        assert p.size == self.L.refcu_param_count()
+        self.L.refcu_set_weights(self.h, _p(p))
+
+    def get_weights(self):
+        p = np.empty(self.L.refcu_param_count(), np.float32)
+        self.L.refcu_get_weights(self.h, _p(p))
+        return p
+
+    def set_state(self, mode, state):
+        s = np.ascontiguousarray(state, np.float32)
+        assert s.shape == (self.layers, self.n, self.H)
+        self.L.refcu_set_state(self.h, mode, _p(s))
+
+    def get_state(self, mode):
+        s = np.empty((self.layers, self.n, self.H), np.float32)
+        self.L.refcu_get_state(self.h, mode, _p(s))
+        return s
+
+    def set_step(self, step):
+        self.L.refcu_set_step(self.h, step)
+
+    def forward(self, mode, d_rec_ptr, d_prev_terminals_ptr, seed):
+        """Device pointers in; returns dict with logits_av (biases NOT included, as the
+        reference stores them), h3, actions, logprobs, values (host arrays)."""
+        n = self.n
+        o = {"logits_nobias": np.empty((n, 44), np.float32), "h3": np.empty((n, self.H), np.float32),
+             "actions": np.empty(n, np.int32), "logprobs": np.empty(n, np.float32),
+             "values": np.empty(n, np.float32)}
+        self.L.refcu_forward(self.h, mode, d_rec_ptr, d_prev_terminals_ptr, seed, None,
+                             _p(o["logits_nobias"]), _p(o["h3"]), _p(o["actions"]),
+                             _p(o["logprobs"]), _p(o["values"]))
+        return o
+
+    def time_forward(self, mode, d_rec_ptr, d_prev_terminals_ptr, warm=3, iters=10, graph=1):
+        return float(self.L.refcu_time_forward(self.h, mode, d_rec_ptr, d_prev_terminals_ptr,
+                                               warm, iters, graph))
+
+    def scalar_set_state(self, state):
+        s = np.ascontiguousarray(state, np.float32)
+        self.L.refcu_scalar_set_state(self.h, _p(s))
+
+    def scalar_get_state(self):
+        s = np.empty((self.layers, self.n, self.H), np.float32)
+        self.L.refcu_scalar_get_state(self.h, _p(s))
+        return s
+
+    def scalar_forward(self, d_rec_ptr, d_prev_terminals_ptr, seed):
+        n = self.n
+        o = {"h3": np.empty((n, self.H), np.float32), "actions": np.empty(n, np.int32),
+             "logprobs": np.empty(n, np.float32), "values": np.empty(n, np.float32)}
+        self.L.refcu_scalar_forward(self.h, d_rec_ptr, d_prev_terminals_ptr, seed, _p(o["h3"]),
+                                    _p(o["actions"]), _p(o["logprobs"]), _p(o["values"]))
+        return o
+
+    def close(self):
+        if self.h:
+            self.L.refcu_destroy(self.h)
+            self.h = None

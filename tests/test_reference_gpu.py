@@ -1,0 +1,106 @@
+"""Pins the CPU oracle (and the strict CUDA path) against the REFERENCE's own CUDA code
+run on the same GPU: its scalar fp32 policy kernel and its batched cuBLAS pipeline in
+strict-fp32 math mode, compiled from the reference sources into oracle/_ref/ (prebuilt
+where the sources live; skipped when that library was not built)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+H, L, A = 256, 2, 43
+
+
+@pytest.fixture(scope="module")
+def refcu(oracle, gpu):
+    if not oracle.RefCuda.available(L):
+        pytest.skip("oracle/_ref/libcfref_cuda_l2.so not built (reference sources absent)")
+    return oracle.RefCuda
+
+
+def _inputs(cfx, oracle, golden_env, n_rep=1):
+    recs = golden_env["records"]
+    rec = np.concatenate([recs[3]] * n_rep)
+    n = rec.shape[0]
+    rng = np.random.default_rng(21)
+    state = rng.normal(0, 1, (L, n, H)).astype(np.float32)
+    prev_t = (rng.random(n) < 0.2).astype(np.float32)
+    return rec, state, prev_t, n
+
+
+@pytest.mark.parametrize("scheme", ["normal", "uniform"])
+def test_oracle_matches_reference_scalar_kernel(cfx, oracle, refcu, golden_env, scheme):
+    rec, state, prev_t, n = _inputs(cfx, oracle, golden_env)
+    params = oracle.init_weights(H, L, A, seed=7, scheme=scheme)
+    ref = refcu(n, L)
+    ref.set_weights(params)
+    ref.set_step(5)
+    ref.scalar_set_state(state)
+    d_rec = cfx.DeviceBuffer.from_host(rec)
+    d_pt = cfx.DeviceBuffer.from_host(prev_t)
+    r = ref.scalar_forward(d_rec.ptr, d_pt.ptr, seed=17)
+    st = state.copy()
+    lav, h3 = oracle.forward(params, rec, prev_t, st, H, L, A, want_h=True)
+    # same operation order on both sides; expf differs by an ulp between libm and CUDA
+    assert np.abs(r["h3"] - h3).max() < 1e-5
+    assert np.abs(r["values"] - lav[:, A]).max() < 1e-5
+    assert np.abs(ref.scalar_get_state() - st).max() < 1e-5
+    u = cfx.philox_uniforms(17, 0, 5, n)
+    a, lp = oracle.sample(lav, u, A)
+    assert (a != r["actions"]).sum() <= 1
+    same = a == r["actions"]
+    assert np.abs(lp[same] - r["logprobs"][same]).max() < 1e-5
+    ref.close()
+
+
+def test_strict_path_matches_reference_fp32_pipeline(cfx, oracle, refcu, golden_env):
+    rec, state, prev_t, n = _inputs(cfx, oracle, golden_env, n_rep=2)
+    params = oracle.init_weights(H, L, A, seed=9)
+    ref = refcu(n, L)
+    ref.set_weights(params)
+    ref.set_step(0)
+    ref.set_state(ref.FP32, state)
+    d_rec = cfx.DeviceBuffer.from_host(rec)
+    d_pt = cfx.DeviceBuffer.from_host(prev_t)
+    r = ref.forward(ref.FP32, d_rec.ptr, d_pt.ptr, seed=3)
+    o = oracle.offsets(H, L, A)
+    bias = np.concatenate([params[o["b_a"]:o["w_v"]], params[o["b_v"]:o["b_v"] + 1]])
+    ref_lav = r["logits_nobias"] + bias[None, :]
+    pol = cfx.Policy(n, H, L, A, "fp32")
+    pol.set_weights(params)
+    pol.set_state(state)
+    d = pol.forward_host(rec, prev_t, None, seed=3)
+    assert np.abs(d["logits_av"] - ref_lav).max() < 1e-4
+    assert np.abs(pol.get_state() - ref.get_state(ref.FP32)).max() < 1e-4
+    assert (d["actions"] != r["actions"]).mean() < 0.01
+    # sampler stage: identical logits + identical uniforms -> identical bits
+    u = cfx.philox_uniforms(3, 0, 0, n)
+    a, lp = cfx.sample_actions(ref_lav, u)
+    assert np.array_equal(a, r["actions"])
+    assert np.array_equal(lp.view(np.uint32), r["logprobs"].view(np.uint32))
+    assert np.array_equal(ref_lav[:, A].view(np.uint32), r["values"].view(np.uint32))
+    pol.close()
+    ref.close()
+
+
+def test_expand_matches_reference_kernel_through_its_pipeline(cfx, oracle, refcu):
+    """With W_enc a 0/1 selection matrix, zero biases and zero gate weights, the reference's
+    strict-fp32 pipeline maps feature x to h3 through exactly representable steps
+    (per layer: out = 0.25, p = 0.5, h = 0.5*0.25 + 0.5*h), so its k_expand_obs output is
+    checked bit for bit through its own GEMM, and our expand against it."""
+    n = 64
+    rec = oracle.synthetic_records(n, seed=12)
+    o = oracle.offsets(H, L, A)
+    ours = cfx.expand_obs(rec)
+    half, quarter = np.float32(0.5), np.float32(0.25)
+    for base in (0, 256, 512, 843 - 256):
+        params = np.zeros(o["count"], np.float32)
+        W = params[:o["b_enc"]].reshape(843, H)
+        W[base + np.arange(H), np.arange(H)] = 1.0
+        ref = refcu(n, L)
+        ref.set_weights(params)
+        d_rec = cfx.DeviceBuffer.from_host(rec)
+        r = ref.forward(ref.FP32, d_rec.ptr, None, seed=1)
+        h = ours[:, base:base + H]
+        for _ in range(L):
+            h = half * quarter + half * h
+        assert np.array_equal(r["h3"].view(np.uint32), h.astype(np.float32).view(np.uint32)), base
+        ref.close()
