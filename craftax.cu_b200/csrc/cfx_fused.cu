@@ -12,13 +12,18 @@
 // Tile-level dataflow (M = 128 envs = the 128 TMEM lanes; thread r of a quarter-warp set
 // owns env row r):
 //   TMEM columns   gate phase: A0 [0,128) A1 [128,256) (layer inputs, 16-bit packed, ping-pong)
-//                              G0 [256,352) G1 [352,448) (gate accumulators of one 32-unit
-//                              slice: zh|zg|zp, double buffered)  HEAD [448,496)
+//                              G [256,448) (gate accumulators of one 64-unit slice: zh|zg|zp;
+//                              the workers move it to registers at once, which frees it for
+//                              the next slice's MMAs while the cell runs)  HEAD [448,496)
 //                  encoder phase: operand-chunk ring [0,256) (8 x 32 columns), accumulator
 //                              [256,512)
-//   shared memory  weight ring 7 x 16 KB | state ring 4 x 16 KB | record ring 4 x 10 KB
-//   warps          0 weight loads, 1 MMA issue + TMEM alloc, 2 record loads, 3 state loads,
-//                  4 state stores, 5..12 workers (expand, epilogues, sampler)
+//   shared memory  weight ring 3 x 32 KB | state ring 4 x 16 KB | record ring 4 x 10 KB
+//   warps          0 weight loads (3 lanes), 1 MMA issue + TMEM alloc, 2 record loads
+//                  (16 lanes), 3 state loads (lanes 0-3, lane 0 also L2-prefetches the next
+//                  tile) + state stores (lanes 8-11), 4..11 workers (expand, cell, sampler)
+// One round of (mbarrier wait, arrive.expect_tx, bulk copy) costs its issuing thread about
+// 500 cycles on B200, so every copy role spreads its sequence over several lanes of its
+// warp (item k belongs to lane k mod lanes) and weight stages are 24-32 KB.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -37,22 +42,38 @@ constexpr int kH = 256;          // hidden units
 constexpr int kA = 43;           // actions
 constexpr int kTile = 128;       // envs per tile
 constexpr int kMaxLayers = 4;
-constexpr int kSliceUnits = 32;  // hidden units per gate slice
-constexpr int kSlices = kH / kSliceUnits;  // 8
+constexpr int kSliceUnits = 64;  // hidden units per gate slice (N = 192: zh|zg|zp)
+constexpr int kSlices = kH / kSliceUnits;  // 4
+constexpr int kHalfUnits = 32;   // units of a slice handled by one worker warpgroup
+constexpr int kStateItems = kH / kHalfUnits;  // 8 state boxes (128 rows x 32 units) per layer
 constexpr int kKBlocks = kH / 64;          // 4 K blocks of 64 per 256-wide operand
 constexpr int kEncChunks = 14;   // 12 full map chunks, 1 partial (24 bytes), 1 tail (51 floats)
 constexpr int kRecSubs = 16;     // record ring fills per tile: 13 map + 3 tail boxes-sets
 constexpr int kHeadN = 48;       // 43 logits + value, padded to a multiple of 16
 
-constexpr int kBSlot = 16384, kNB = 7;
+constexpr int kBSlot = 32768, kNB = 3;
 constexpr int kSSlot = 16384, kNS = 4;
 constexpr int kRBoxBytes = 32 * 80, kRSlot = 4 * kRBoxBytes, kNR = 4;
 constexpr int kAexpSlots = 8;
 
-constexpr int kEncStageBytes = 128 * 128;            // [128 units][64 K] 16-bit
-constexpr int kGateStageBytes = 3 * kSliceUnits * 128;  // [96 rows][64 K]
-constexpr int kHeadStageBytes = kHeadN * 128;        // [48 rows][64 K]
-constexpr int kEncStages = kEncChunks * 2;
+// Image blocks (one K block of 64 columns each) and the ring stages that carry them:
+// encoder stage = one chunk, 256 units (two 128-unit blocks, 32 KB); gate stage = one K block
+// of one 64-unit slice (192 rows, 24 KB); head stage = all four K blocks (24 KB).
+constexpr int kEncStageBytes = 128 * 128;            // block: [128 units][64 K] 16-bit
+constexpr int kGateStageBytes = 3 * kSliceUnits * 128;  // block: [96 rows][64 K]
+constexpr int kHeadStageBytes = kHeadN * 128;        // block: [48 rows][64 K]
+constexpr int kEncStages = kEncChunks * 2;           // encoder blocks in the image
+constexpr int kEncCopyBytes = 2 * kEncStageBytes, kGateCopyBytes = kGateStageBytes,
+              kHeadCopyBytes = kKBlocks * kHeadStageBytes;
+constexpr int kWLanes = 3, kRGroups = 4, kSLanes = 4;
+// A lane that handles every G-th item of an N-slot ring waits on its slot's "empty" barrier
+// by phase parity; that is only sound while it cannot run two phases ahead of the slot,
+// i.e. while G <= N (its previous item, G back, already needed the slot use N+G back).
+// A ring shared by several consumers is only sound if every slot is always consumed by the
+// same consumer (a consumer that skips slots owned by others could otherwise be two phases
+// off): the record ring (4 slots, fills alternate between the worker warpgroups) and the
+// state ring (4 slots, slices alternate) satisfy this; each weight ring has one consumer.
+static_assert(kWLanes <= kNB && kRGroups <= kNR && kSLanes <= kNS && kNR == 4 && kNS == 4, "ring ownership");
 
 __host__ __device__ constexpr size_t image_bytes(int L) {
     return (size_t)kEncStages * kEncStageBytes + (size_t)L * kSlices * kKBlocks * kGateStageBytes +
@@ -60,7 +81,7 @@ __host__ __device__ constexpr size_t image_bytes(int L) {
 }
 
 // TMEM columns
-constexpr uint32_t kColA0 = 0, kColA1 = 128, kColG0 = 256, kColG1 = 352, kColHead = 448;
+constexpr uint32_t kColA0 = 0, kColA1 = 128, kColG = 256, kColHead = 448;
 constexpr uint32_t kColAexp = 0, kColAcc = 256;
 
 // shared memory map (offsets from a 1024-byte aligned base)
@@ -74,22 +95,24 @@ enum Bar {
     ST_READY = S_EMPTY + kNS, R_FULL = ST_READY + kNS, R_EMPTY = R_FULL + kNR,
     AEXP_FULL = R_EMPTY + kNR, AEXP_EMPTY = AEXP_FULL + kAexpSlots,
     ACC_FULL = AEXP_EMPTY + kAexpSlots, A_KB = ACC_FULL + 1, G_FULL = A_KB + kKBlocks,
-    G_EMPTY = G_FULL + 2, H_FULL = G_EMPTY + 2, NUM_BARS = H_FULL + 1
+    G_EMPTY = G_FULL + 1, H_FULL = G_EMPTY + 1, H_EMPTY = H_FULL + 1, NUM_BARS = H_EMPTY + 1
 };
 constexpr int kOffMisc = kOffBars + NUM_BARS * 8;  // tmem base, abort flag
 constexpr int kSmemBytes = kOffMisc + 16 + 1024;   // + alignment slack
 
-constexpr int kWorkerWarp0 = 5, kNumWarps = 13, kThreads = kNumWarps * 32;
+constexpr int kWorkerWarp0 = 4, kNumWarps = 12, kThreads = kNumWarps * 32;
 
 // wait-site codes recorded in the status word when a bounded wait gives up
 enum WaitCode : uint32_t {
     W_B_EMPTY = 1, W_B_FULL, W_R_EMPTY, W_R_FULL, W_S_EMPTY, W_S_FULL, W_ST_READY, W_AEXP_EMPTY,
-    W_AEXP_FULL, W_ACC_FULL, W_A_KB, W_G_FULL, W_G_EMPTY, W_H_FULL
+    W_AEXP_FULL, W_ACC_FULL, W_A_KB, W_G_FULL, W_G_EMPTY, W_H_FULL, W_H_EMPTY
 };
 
 struct Params {
     CUtensorMap rec_map;                 // uint8 [n/4][3984], box 32 x 80
     CUtensorMap state_map[kMaxLayers];   // fp32 [n][256] per layer, box 128 x 32, SWIZZLE_128B
+    const uint8_t* records;              // [n][996], for the L2 prefetch of the next tile
+    const float* state;                  // [L][n][256]
     const uint8_t* image;                // pre-swizzled 16-bit weight stages in consumption order
     const float* params;                 // fp32 arena (biases are read from it)
     const float* prev_terminals;
@@ -104,6 +127,7 @@ struct Params {
     uint64_t seed, env_offset;
     int n, L, num_tiles;
     size_t off_b_enc, off_b_a, off_b_v;
+    long long* timeline;  // debug builds only (CFX_TIMELINE): per-role (tag, clock) log of block 0
 };
 
 // ------------------------------------------------------------------ weight image
@@ -252,26 +276,104 @@ struct Smem {
     }
 };
 
+// Debug builds (-DCFX_CHECK): typed shared/global accesses verify their alignment, report a
+// violation and substitute an aligned address inside the same buffer.
+#ifdef CFX_CHECK
+template <typename T>
+__device__ __forceinline__ T* chk_ptr(T* p, const char* what) {
+    if ((reinterpret_cast<uintptr_t>(p) & (sizeof(T) - 1)) != 0) {
+        printf("CFX_CHECK %s: block %d thread %d ptr=%llx\n", what, (int)blockIdx.x, (int)threadIdx.x,
+               (unsigned long long)reinterpret_cast<uintptr_t>(p));
+        return reinterpret_cast<T*>(reinterpret_cast<uintptr_t>(p) & ~(uintptr_t)(sizeof(T) - 1));
+    }
+    return p;
+}
+#define CHKP(p, what) chk_ptr(p, what)
+#else
+#define CHKP(p, what) (p)
+#endif
+
+// Optional timeline (compile with -DCFX_TIMELINE): block 0 logs (tag, clock64) pairs per role.
+#ifdef CFX_TIMELINE
+#define TL_INIT(role) long long* tl_ptr = P.timeline + (role) * 4096; int tl_i = 0
+#define TL(tag)                                                               \
+    do {                                                                      \
+        if (blockIdx.x == 0 && P.timeline != nullptr && tl_i < 2047) {        \
+            tl_ptr[2 * tl_i] = (long long)(tag);                              \
+            tl_ptr[2 * tl_i + 1] = clock64();                                 \
+            tl_i++;                                                           \
+            tl_ptr[4094] = tl_i;                                              \
+        }                                                                     \
+    } while (0)
+#else
+#define TL_INIT(role)
+#define TL(tag)
+#endif
+
 // every role runs in its own function: a failed (timed-out) wait returns to the common exit
 #define CFX_WAIT(barid, parity, code) \
     if (!mbar_wait(sm.bar(barid), (parity), sm.abort_flag(), (code))) return
 
+// Record-ring fill order within a tile.  The expand is split by chunk between the two worker
+// warpgroups: wg 1 converts chunks 0..6 (fills 0..6), wg 0 chunks 7..13 (fills 7..12 and the
+// three tail fills 13..15).  Fills are issued interleaved (wg1, wg0, wg1, ...) so that with a
+// 4-slot ring each warpgroup effectively owns two slots and neither waits for the other.
+__device__ __forceinline__ int rec_fill_at(int pos) {   // ring position -> fill index
+    if (pos >= 14) return pos;
+    return (pos & 1) ? 7 + (pos >> 1) : (pos >> 1);
+}
+__device__ __forceinline__ int rec_pos_of(int fill) {   // fill index -> ring position
+    if (fill >= 14) return fill;
+    return fill < 7 ? 2 * fill : 2 * (fill - 7) + 1;
+}
+
+// One tile ahead, the records and the state rows of the CTA's next tile are pulled into L2,
+// so that the ring loads hit L2 (hundreds of cycles) instead of HBM (thousands): the rings
+// are far too small to cover HBM latency at the rate the encoder and the cell consume.
+// Called by one state-load lane at the start of each tile, which paces it.
+__device__ __forceinline__ void l2_prefetch_tile(const Params& P, int t) {
+    if (t >= P.num_tiles) return;
+    constexpr uint32_t kPiece = 32768;
+    const int rows = min(kTile, P.n - t * kTile);
+    const uint8_t* rp = P.records + (size_t)t * kTile * kRec;
+    const uint32_t rbytes = (uint32_t)rows * kRec;
+    for (uint32_t o = 0; o < rbytes; o += kPiece) bulk_prefetch_l2(rp + o, min(kPiece, rbytes - o));
+    for (int l = 0; l < P.L; l++) {
+        const uint8_t* sp =
+            reinterpret_cast<const uint8_t*>(P.state + ((size_t)l * P.n + (size_t)t * kTile) * kH);
+        const uint32_t sbytes = (uint32_t)rows * kH * 4;
+        for (uint32_t o = 0; o < sbytes; o += kPiece) bulk_prefetch_l2(sp + o, min(kPiece, sbytes - o));
+    }
+}
+
 // ------------------------------------------------------------------ producer roles
 // Weight stages: the image is laid out in consumption order, so the source pointer just
 // advances; every tile replays the same sequence (it stays L2 resident).
-__device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& P) {
+// Weight stages: the image is laid out in consumption order, so stage s of a tile starts
+// where stage s-1 ended; every tile replays the same sequence (it stays L2 resident).
+// One lane per ring slot.
+__device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& P, int lane) {
     const int stages_gate = P.L * kSlices * kKBlocks;
+    const size_t enc_bytes = (size_t)kEncStages * kEncStageBytes;
     uint32_t cnt = 0;
+    TL_INIT(3);
     for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x) {
-        const uint8_t* src = P.image;
-        for (int s = 0; s < kEncStages + stages_gate + kKBlocks; s++, cnt++) {
-            const uint32_t bytes = s < kEncStages ? kEncStageBytes
-                                   : (s < kEncStages + stages_gate ? kGateStageBytes : kHeadStageBytes);
+        for (int s = 0; s < kEncChunks + stages_gate + 1; s++, cnt++) {
+            if ((int)(cnt % kWLanes) != lane) continue;
+            uint32_t bytes;
+            size_t off;
+            if (s < kEncChunks) {
+                bytes = kEncCopyBytes; off = (size_t)s * kEncCopyBytes;
+            } else if (s < kEncChunks + stages_gate) {
+                bytes = kGateCopyBytes; off = enc_bytes + (size_t)(s - kEncChunks) * kGateCopyBytes;
+            } else {
+                bytes = kHeadCopyBytes; off = enc_bytes + (size_t)stages_gate * kGateCopyBytes;
+            }
             const int slot = cnt % kNB;
             CFX_WAIT(B_EMPTY + slot, ((cnt / kNB) & 1) ^ 1, W_B_EMPTY);
+            if (lane == 0) TL(0x10000 | s);
             mbar_arrive_expect_tx(sm.bar(B_FULL + slot), bytes);
-            bulk_g2s(smem_u32(sm.b_slot(slot)), src, bytes, sm.bar(B_FULL + slot));
-            src += bytes;
+            bulk_g2s(smem_u32(sm.b_slot(slot)), P.image + off, bytes, sm.bar(B_FULL + slot));
         }
     }
 }
@@ -280,35 +382,37 @@ __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& 
 // aligned row); env 4g+i of a tile sits in row g at byte 996 i.  A 64-byte feature chunk of
 // all 128 envs is fetched as four boxes (one per i) of 32 rows x 80 bytes starting at the
 // 16-byte boundary below 996 i + 64 c; the 204 tail bytes take three more such box sets.
-__device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& P) {
+__device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& P, int lane) {
+    const int group = lane >> 2, i = lane & 3;  // lane = 4 * (fill index mod 4) + box
     uint32_t cnt = 0;
     for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x) {
-        for (int sub = 0; sub < kRecSubs; sub++, cnt++) {
+        for (int pos = 0; pos < kRecSubs; pos++, cnt++) {
+            if ((int)(cnt % kRGroups) != group) continue;
+            const int sub = rec_fill_at(pos);
             const int slot = cnt % kNR;
             CFX_WAIT(R_EMPTY + slot, ((cnt / kNR) & 1) ^ 1, W_R_EMPTY);
-            mbar_arrive_expect_tx(sm.bar(R_FULL + slot), kRSlot);
-            const int byte0 = sub < 13 ? 64 * sub : kMap + 80 * (sub - 13);
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int x0 = sub < 13 ? ((kRec * i + byte0) & ~15)
-                                        : ((kRec * i + kMap) & ~15) + 80 * (sub - 13);
-                tensor_g2s_2d(smem_u32(sm.r_slot(slot) + i * kRBoxBytes), &P.rec_map, x0, tile * 32,
-                              sm.bar(R_FULL + slot));
-            }
+            mbar_arrive_expect_tx(sm.bar(R_FULL + slot), kRBoxBytes);
+            const int x0 = sub < 13 ? ((kRec * i + 64 * sub) & ~15)
+                                    : ((kRec * i + kMap) & ~15) + 80 * (sub - 13);
+            tensor_g2s_2d(smem_u32(sm.r_slot(slot) + i * kRBoxBytes), &P.rec_map, x0, tile * 32,
+                          sm.bar(R_FULL + slot));
         }
     }
 }
 
-// State slices: layer l, tile rows, 32 units -> one 16 KB box, 128-byte swizzled.
-__device__ __forceinline__ void role_state_loads(const Smem& sm, const Params& P) {
+// State boxes: layer l, tile rows, 32 units -> one 16 KB box, 128-byte swizzled; box j of a
+// layer belongs to slice j / 2 and worker warpgroup j & 1.
+__device__ __forceinline__ void role_state_loads(const Smem& sm, const Params& P, int lane) {
     uint32_t cnt = 0;
     for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x) {
+        if (lane == 0) l2_prefetch_tile(P, tile + gridDim.x);
         for (int l = 0; l < P.L; l++) {
-            for (int j = 0; j < kSlices; j++, cnt++) {
+            for (int j = 0; j < kStateItems; j++, cnt++) {
+                if ((int)(cnt % kSLanes) != lane) continue;
                 const int slot = cnt % kNS;
                 CFX_WAIT(S_EMPTY + slot, ((cnt / kNS) & 1) ^ 1, W_S_EMPTY);
                 mbar_arrive_expect_tx(sm.bar(S_FULL + slot), kSSlot);
-                tensor_g2s_2d(smem_u32(sm.s_slot(slot)), &P.state_map[l], j * kSliceUnits,
+                tensor_g2s_2d(smem_u32(sm.s_slot(slot)), &P.state_map[l], j * kHalfUnits,
                               tile * kTile, sm.bar(S_FULL + slot));
             }
         }
@@ -317,14 +421,15 @@ __device__ __forceinline__ void role_state_loads(const Smem& sm, const Params& P
 
 // The workers overwrite a state slot in place with the new state; this warp writes it
 // back (rows beyond n are clipped by the tensor map) and recycles the slot.
-__device__ __forceinline__ void role_state_stores(const Smem& sm, const Params& P) {
+__device__ __forceinline__ void role_state_stores(const Smem& sm, const Params& P, int lane) {
     uint32_t cnt = 0;
     for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x) {
         for (int l = 0; l < P.L; l++) {
-            for (int j = 0; j < kSlices; j++, cnt++) {
+            for (int j = 0; j < kStateItems; j++, cnt++) {
+                if ((int)(cnt % kSLanes) != lane) continue;
                 const int slot = cnt % kNS;
                 CFX_WAIT(ST_READY + slot, (cnt / kNS) & 1, W_ST_READY);
-                tensor_s2g_2d(&P.state_map[l], smem_u32(sm.s_slot(slot)), j * kSliceUnits,
+                tensor_s2g_2d(&P.state_map[l], smem_u32(sm.s_slot(slot)), j * kHalfUnits,
                               tile * kTile);
                 bulk_commit_group();
                 bulk_wait_group_read<0>();
@@ -335,77 +440,105 @@ __device__ __forceinline__ void role_state_stores(const Smem& sm, const Params& 
 }
 
 // ------------------------------------------------------------------ MMA role
+// The whole warp runs this role converged (loop state stays warp-uniform); only the leader
+// lane issues MMAs and commits.  Issue cost matters: the issuer shares its scheduler with two
+// busy worker warps and needs ~90 cycles per MMA instruction, so MMAs are made as wide as the
+// tensor memory budget allows (N = 192 / 256, 96 / 128 cycles of tensor pipe each),
+// descriptors are one add away from a per-slot base and every K-step loop is fully unrolled
+// (rebuilding descriptors per MMA measured ~150 cycles per instruction on B200).
 template <typename T16>
-__device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32_t tmem) {
+__device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32_t tmem, bool leader) {
     constexpr uint32_t fmt = Op16<T16>::kFmt;
-    constexpr uint32_t idesc_enc = make_idesc(fmt, 128, 128);
+    constexpr uint32_t idesc_enc = make_idesc(fmt, 128, kH);
     constexpr uint32_t idesc_gate = make_idesc(fmt, 128, 3 * kSliceUnits);
     constexpr uint32_t idesc_head = make_idesc(fmt, 128, kHeadN);
-    uint32_t bcnt = 0, acnt = 0, akb_use = 0, gcnt[2] = {0, 0};
-    for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x) {
-        // ---- encoder: 14 operand chunks x 2 unit halves
-        for (int kc = 0; kc < kEncChunks; kc++, acnt++) {
+    const uint64_t bdesc0 = smem_desc_sw128(smem_u32(sm.b_slot(0)));
+    uint32_t bcnt = 0, acnt = 0, akb_use = 0, gcnt = 0, tcnt = 0;
+    TL_INIT(0);
+    for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x, tcnt++) {
+        if (leader) TL(0x1000000);
+        // the encoder accumulator overlaps the head accumulator of the previous tile:
+        // wait until the sampler threads have read it
+        CFX_WAIT(H_EMPTY, (tcnt & 1) ^ 1, W_H_EMPTY);
+        // ---- encoder: 14 operand chunks, N = 256 units
+        for (int kc = 0; kc < kEncChunks; kc++, acnt++, bcnt++) {
             const int as = acnt % kAexpSlots;
+            const int slot = bcnt % kNB;
             CFX_WAIT(AEXP_FULL + as, (acnt / kAexpSlots) & 1, W_AEXP_FULL);
+            if (leader) TL(0x20000 | kc);
+            CFX_WAIT(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
+            if (leader) TL(0x30000 | kc);
             tc_fence_after_sync();
-            const int ksteps = kc == 12 ? 2 : 4;
             const uint32_t a_col = tmem + kColAexp + as * 32;
-            for (int half = 0; half < 2; half++, bcnt++) {
-                const int slot = bcnt % kNB;
-                CFX_WAIT(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
-                tc_fence_after_sync();
-                const uint32_t b_addr = smem_u32(sm.b_slot(slot));
-                for (int ks = 0; ks < ksteps; ks++)
-                    mma_f16_ts(tmem + kColAcc + half * 128, a_col + ks * 8,
-                               smem_desc_sw128(b_addr + ks * 32), idesc_enc, (kc | ks) != 0);
+            const uint64_t bd = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
+            if (leader) {
+                if (kc == 0) mma_f16_ts(tmem + kColAcc, a_col, bd, idesc_enc, 0);
+                else mma_f16_ts(tmem + kColAcc, a_col, bd, idesc_enc, 1);
+                mma_f16_ts(tmem + kColAcc, a_col + 8, bd + 2, idesc_enc, 1);
+                if (kc != 12) {  // chunk 12 carries 24 map bytes: two K steps
+                    mma_f16_ts(tmem + kColAcc, a_col + 16, bd + 4, idesc_enc, 1);
+                    mma_f16_ts(tmem + kColAcc, a_col + 24, bd + 6, idesc_enc, 1);
+                }
                 mma_commit(sm.bar(B_EMPTY + slot));
+                mma_commit(sm.bar(AEXP_EMPTY + as));
+                TL(0x38000 | kc);
             }
-            mma_commit(sm.bar(AEXP_EMPTY + as));
+            __syncwarp();
         }
-        mma_commit(sm.bar(ACC_FULL));
-        // ---- MinGRU layers: 8 slices x 4 K blocks, N = 96 (zh|zg|zp of 32 units)
+        if (leader) mma_commit(sm.bar(ACC_FULL));
+        __syncwarp();
+        // ---- MinGRU layers: 4 slices of 64 units, one stage per K block, N = 192 (zh|zg|zp)
         for (int l = 0; l < P.L; l++, akb_use++) {
             const uint32_t a_cur = tmem + ((l & 1) ? kColA1 : kColA0);
-            for (int j = 0; j < kSlices; j++) {
-                const int g = j & 1;
-                CFX_WAIT(G_EMPTY + g, (gcnt[g] & 1) ^ 1, W_G_EMPTY);
-                gcnt[g]++;
-                tc_fence_after_sync();
-                const uint32_t d_col = tmem + (g ? kColG1 : kColG0);
+            for (int j = 0; j < kSlices; j++, gcnt++) {
+                CFX_WAIT(G_EMPTY, (gcnt & 1) ^ 1, W_G_EMPTY);
+                if (leader) TL(0x40000 | (l << 8) | j);
+#pragma unroll
                 for (int kb = 0; kb < kKBlocks; kb++, bcnt++) {
-                    if (j == 0) {
-                        CFX_WAIT(A_KB + kb, akb_use & 1, W_A_KB);
-                        tc_fence_after_sync();
-                    }
+                    if (j == 0) CFX_WAIT(A_KB + kb, akb_use & 1, W_A_KB);
                     const int slot = bcnt % kNB;
                     CFX_WAIT(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
+                    if (leader) TL(0x50000 | (l << 8) | (j << 2) | kb);
                     tc_fence_after_sync();
-                    const uint32_t b_addr = smem_u32(sm.b_slot(slot));
-                    for (int ks = 0; ks < 4; ks++)
-                        mma_f16_ts(d_col, a_cur + kb * 32 + ks * 8, smem_desc_sw128(b_addr + ks * 32),
-                                   idesc_gate, (kb | ks) != 0);
-                    mma_commit(sm.bar(B_EMPTY + slot));
+                    const uint64_t bd = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
+                    if (leader) {
+#pragma unroll
+                        for (int ks = 0; ks < 4; ks++)
+                            mma_f16_ts(tmem + kColG, a_cur + kb * 32 + ks * 8, bd + (uint64_t)(2 * ks),
+                                       idesc_gate, (kb | ks) != 0 ? 1u : 0u);
+                        mma_commit(sm.bar(B_EMPTY + slot));
+                        TL(0x58000 | (l << 8) | (j << 2) | kb);
+                    }
+                    __syncwarp();
                 }
-                mma_commit(sm.bar(G_FULL + g));
+                if (leader) mma_commit(sm.bar(G_FULL));
+                __syncwarp();
             }
         }
-        // ---- heads: N = 48
+        // ---- heads: N = 48, one stage with all four K blocks
         {
             const uint32_t a_cur = tmem + ((P.L & 1) ? kColA1 : kColA0);
-            for (int kb = 0; kb < kKBlocks; kb++, bcnt++) {
-                CFX_WAIT(A_KB + kb, akb_use & 1, W_A_KB);
-                tc_fence_after_sync();
-                const int slot = bcnt % kNB;
-                CFX_WAIT(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
-                tc_fence_after_sync();
-                const uint32_t b_addr = smem_u32(sm.b_slot(slot));
-                for (int ks = 0; ks < 4; ks++)
-                    mma_f16_ts(tmem + kColHead, a_cur + kb * 32 + ks * 8,
-                               smem_desc_sw128(b_addr + ks * 32), idesc_head, (kb | ks) != 0);
-                mma_commit(sm.bar(B_EMPTY + slot));
-            }
+#pragma unroll
+            for (int kb = 0; kb < kKBlocks; kb++) CFX_WAIT(A_KB + kb, akb_use & 1, W_A_KB);
             akb_use++;
-            mma_commit(sm.bar(H_FULL));
+            const int slot = bcnt % kNB;
+            CFX_WAIT(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
+            tc_fence_after_sync();
+            const uint64_t bd = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
+            if (leader) {
+#pragma unroll
+                for (int kb = 0; kb < kKBlocks; kb++)
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++)
+                        mma_f16_ts(tmem + kColHead, a_cur + kb * 32 + ks * 8,
+                                   bd + (uint64_t)((kb * kHeadStageBytes + ks * 32) >> 4), idesc_head,
+                                   (kb | ks) != 0 ? 1u : 0u);
+                mma_commit(sm.bar(B_EMPTY + slot));
+                mma_commit(sm.bar(H_FULL));
+                TL(0x60000);
+            }
+            __syncwarp();
+            bcnt++;
         }
     }
 }
@@ -424,43 +557,52 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
     const int gi = row >> 2, ii = row & 3;
     const float* bias = sm.bias();
     const uint32_t rec_row_off = ii * kRBoxBytes + gi * 80;
-    uint32_t rcnt = 0, acnt = 0, tcnt = 0, gcnt = 0, it = 0;
+    uint32_t tcnt = 0, gcnt = 0, it = 0;
+    TL_INIT(1 + wg);
+    const bool tl_on = (quarter == 0 && lane == 0);
     for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x, it++, tcnt++) {
+        if (tl_on) TL(0x1000000);
         const int env = tile * kTile + row;
         const bool valid = env < P.n;
         const bool zero_state =
             valid && P.prev_terminals != nullptr && P.prev_terminals[env] != 0.0f;
 
-        // ---- expand: record bytes -> 16-bit operand rows in the TMEM chunk ring
-        for (int kc = 0; kc < kEncChunks; kc++, acnt++) {
+        // ---- expand: record bytes -> 16-bit operand rows in the TMEM chunk ring.
+        // wg 1 converts chunks 0..6, wg 0 chunks 7..13; a warp writes all 32 columns of its rows.
+        for (int kk = 0; kk < kEncChunks / 2; kk++) {
+            const int kc = wg == 1 ? kk : 7 + kk;
+            const uint32_t acnt = it * kEncChunks + kc;
             const int as = acnt % kAexpSlots;
             CFX_WAIT(AEXP_EMPTY + as, ((acnt / kAexpSlots) & 1) ^ 1, W_AEXP_EMPTY);
+            if (tl_on) TL(0x70000 | kc);
             tc_fence_after_sync();
-            uint32_t regs[16];
+            uint32_t regs[32];
             if (kc < 13) {
+                const uint32_t rcnt = it * kRecSubs + rec_pos_of(kc);
                 const int slot = rcnt % kNR;
                 CFX_WAIT(R_FULL + slot, (rcnt / kNR) & 1, W_R_FULL);
-                const uint8_t* src = sm.r_slot(slot) + rec_row_off + ((kRec * ii) & 15) + 32 * wg;
+                if (tl_on) TL(0x80000 | kc);
+                const uint8_t* src = sm.r_slot(slot) + rec_row_off + ((kRec * ii) & 15);
 #pragma unroll
-                for (int q = 0; q < 8; q++) {
+                for (int q = 0; q < 16; q++) {
                     uint32_t w32 = *reinterpret_cast<const uint32_t*>(src + 4 * q);
-                    if (kc == 12 && (wg == 1 || q >= 6)) w32 = 0;  // bytes 792.. are not map bytes
+                    if (kc == 12 && q >= 6) w32 = 0;  // record bytes 792.. are not map bytes
                     Op::bytes4(w32, regs[2 * q], regs[2 * q + 1]);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sm.bar(R_EMPTY + slot));
-                rcnt++;
             } else {
+                const uint32_t rcnt = it * kRecSubs + 13;  // the three tail fills sit at 13, 14, 15
 #pragma unroll
-                for (int s = 0; s < 3; s++)
-                    CFX_WAIT(R_FULL + (rcnt + s) % kNR, ((rcnt + s) / kNR) & 1, W_R_FULL);
+                for (int s3 = 0; s3 < 3; s3++)
+                    CFX_WAIT(R_FULL + (rcnt + s3) % kNR, ((rcnt + s3) / kNR) & 1, W_R_FULL);
                 const uint32_t rem = (kRec * ii + kMap) & 15;
 #pragma unroll
-                for (int q = 0; q < 16; q++) {
+                for (int q = 0; q < 32; q++) {
                     float v[2];
 #pragma unroll
                     for (int e = 0; e < 2; e++) {
-                        const int f = 32 * wg + 2 * q + e;  // tail float index (wg is warp-uniform)
+                        const int f = 2 * q + e;  // tail float index
                         v[e] = 0.0f;
                         if (f < kTail) {
                             const uint32_t off = rem + 4 * f;
@@ -474,19 +616,26 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 __syncwarp();
                 if (lane == 0) {
 #pragma unroll
-                    for (int s = 0; s < 3; s++) mbar_arrive(sm.bar(R_EMPTY + (rcnt + s) % kNR));
+                    for (int s3 = 0; s3 < 3; s3++) mbar_arrive(sm.bar(R_EMPTY + (rcnt + s3) % kNR));
                 }
-                rcnt += 3;
             }
-            tmem_st16(tmem + lane_base + kColAexp + as * 32 + 16 * wg, regs);
+            {
+                uint32_t lo[16], hi[16];
+#pragma unroll
+                for (int q = 0; q < 16; q++) { lo[q] = regs[q]; hi[q] = regs[16 + q]; }
+                tmem_st16(tmem + lane_base + kColAexp + as * 32, lo);
+                tmem_st16(tmem + lane_base + kColAexp + as * 32 + 16, hi);
+            }
             tmem_wait_st();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(sm.bar(AEXP_FULL + as));
+            if (tl_on) TL(0x90000 | kc);
         }
 
         // ---- encoder epilogue: accumulator + bias -> layer-0 input A0 (wg = unit half)
         CFX_WAIT(ACC_FULL, tcnt & 1, W_ACC_FULL);
+        if (tl_on) TL(0xA0000);
         tc_fence_after_sync();
 #pragma unroll 2
         for (int b = 0; b < 8; b++) {
@@ -510,73 +659,89 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
             mbar_arrive(sm.bar(A_KB + 2 * wg + 1));
         }
 
-        // ---- MinGRU layers: wg handles slices j = wg, wg+2, ... from gate buffer G[wg]
+        // ---- MinGRU layers: both warpgroups work on every 64-unit slice; wg handles units
+        // [64 j + 32 wg, 64 j + 32 wg + 32) = state box 2 j + wg of the layer
         for (int l = 0; l < P.L; l++) {
             const uint32_t a_cur = tmem + lane_base + ((l & 1) ? kColA1 : kColA0);
             const uint32_t a_next = tmem + lane_base + ((l & 1) ? kColA0 : kColA1);
-            for (int jj = 0; jj < kSlices / 2; jj++, gcnt++) {
-                const int j = 2 * jj + wg;
-                CFX_WAIT(G_FULL + wg, gcnt & 1, W_G_FULL);
+            for (int j = 0; j < kSlices; j++, gcnt++) {
+                CFX_WAIT(G_FULL, gcnt & 1, W_G_FULL);
+                if (tl_on) TL(0xB0000 | (l << 8) | j);
                 tc_fence_after_sync();
-                const uint32_t scnt = (it * P.L + l) * kSlices + j;
+                const int box = 2 * j + wg;
+                const uint32_t scnt = (it * P.L + l) * kStateItems + box;
                 const int slot = scnt % kNS;
-                const uint32_t gcol = tmem + lane_base + (wg ? kColG1 : kColG0);
+                const uint32_t gcol = tmem + lane_base + kColG + kHalfUnits * wg;
                 uint8_t* rbase = sm.s_slot(slot) + (row >> 3) * 1024 + (row & 7) * 128;
                 const int xr = row & 7;
-                bool state_ready = false;
+                // this thread's 96 gate columns and 32 layer inputs go to registers at once, so
+                // the accumulator is handed back to the MMA warp right away
+                uint32_t zh[32], zg[32], zp[32], xin[16];
+                {
+                    uint32_t t0[16], t1[16];
+                    tmem_ld16(gcol, t0);
+                    tmem_ld16(gcol + 16, t1);
+#pragma unroll
+                    for (int q = 0; q < 16; q++) { zh[q] = t0[q]; zh[16 + q] = t1[q]; }
+                    tmem_ld16(gcol + kSliceUnits, t0);
+                    tmem_ld16(gcol + kSliceUnits + 16, t1);
+#pragma unroll
+                    for (int q = 0; q < 16; q++) { zg[q] = t0[q]; zg[16 + q] = t1[q]; }
+                    tmem_ld16(gcol + 2 * kSliceUnits, t0);
+                    tmem_ld16(gcol + 2 * kSliceUnits + 16, t1);
+#pragma unroll
+                    for (int q = 0; q < 16; q++) { zp[q] = t0[q]; zp[16 + q] = t1[q]; }
+                    tmem_ld16(a_cur + 16 * box, xin);
+                    tmem_wait_ld();
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sm.bar(G_EMPTY));
+                if (tl_on) TL(0xB8000 | (l << 8) | j);
+                CFX_WAIT(S_FULL + slot, (scnt / kNS) & 1, W_S_FULL);
+                if (tl_on) TL(0xC0000 | (l << 8) | j);
 #pragma unroll
                 for (int hf = 0; hf < 2; hf++) {
-                    uint32_t zh[16], zg[16], zp[16], xin[8], hn[8];
-                    tmem_ld16(gcol + 16 * hf, zh);
-                    tmem_ld16(gcol + 32 + 16 * hf, zg);
-                    tmem_ld16(gcol + 64 + 16 * hf, zp);
-                    tmem_ld8(a_cur + 16 * j + 8 * hf, xin);
-                    tmem_wait_ld();
-                    if (hf == 1) {  // all gate columns of this slice are in registers
-                        tc_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(sm.bar(G_EMPTY + wg));
-                    }
-                    if (!state_ready) {
-                        CFX_WAIT(S_FULL + slot, (scnt / kNS) & 1, W_S_FULL);
-                        state_ready = true;
-                    }
+                    uint32_t hn[8];
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
+                        const int u = 16 * hf + 4 * q;  // first of four units
                         float4* sp = reinterpret_cast<float4*>(rbase + (((4 * hf + q) ^ xr) << 4));
                         float4 st = *sp;
                         if (zero_state) st = make_float4(0.f, 0.f, 0.f, 0.f);
-                        const float2 x01 = Op::unpack(xin[2 * q]), x23 = Op::unpack(xin[2 * q + 1]);
+                        const float2 x01 = Op::unpack(xin[u / 2]), x23 = Op::unpack(xin[u / 2 + 1]);
                         float4 out;
                         float h0, h1, h2, h3;
-                        mingru_cell(__uint_as_float(zh[4 * q]), __uint_as_float(zg[4 * q]),
-                                    __uint_as_float(zp[4 * q]), st.x, x01.x, out.x, h0);
-                        mingru_cell(__uint_as_float(zh[4 * q + 1]), __uint_as_float(zg[4 * q + 1]),
-                                    __uint_as_float(zp[4 * q + 1]), st.y, x01.y, out.y, h1);
-                        mingru_cell(__uint_as_float(zh[4 * q + 2]), __uint_as_float(zg[4 * q + 2]),
-                                    __uint_as_float(zp[4 * q + 2]), st.z, x23.x, out.z, h2);
-                        mingru_cell(__uint_as_float(zh[4 * q + 3]), __uint_as_float(zg[4 * q + 3]),
-                                    __uint_as_float(zp[4 * q + 3]), st.w, x23.y, out.w, h3);
+                        mingru_cell(__uint_as_float(zh[u]), __uint_as_float(zg[u]),
+                                    __uint_as_float(zp[u]), st.x, x01.x, out.x, h0);
+                        mingru_cell(__uint_as_float(zh[u + 1]), __uint_as_float(zg[u + 1]),
+                                    __uint_as_float(zp[u + 1]), st.y, x01.y, out.y, h1);
+                        mingru_cell(__uint_as_float(zh[u + 2]), __uint_as_float(zg[u + 2]),
+                                    __uint_as_float(zp[u + 2]), st.z, x23.x, out.z, h2);
+                        mingru_cell(__uint_as_float(zh[u + 3]), __uint_as_float(zg[u + 3]),
+                                    __uint_as_float(zp[u + 3]), st.w, x23.y, out.w, h3);
                         *sp = out;
                         hn[2 * q] = Op::pack(h0, h1);
                         hn[2 * q + 1] = Op::pack(h2, h3);
                     }
-                    tmem_st8(a_next + 16 * j + 8 * hf, hn);
+                    tmem_st8(a_next + 16 * box + 8 * hf, hn);
                 }
                 tmem_wait_st();
                 tc_fence_before_sync();
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(sm.bar(A_KB + (j >> 1)));
+                    mbar_arrive(sm.bar(A_KB + j));
                     mbar_arrive(sm.bar(ST_READY + slot));
                 }
+                if (tl_on) TL(0xD0000 | (l << 8) | j);
             }
         }
 
         // ---- heads + sampler (wg 0: one thread per env; wg 1 only passes the barrier so
         // that its next-tile operand writes cannot overtake the last MMA)
         CFX_WAIT(H_FULL, tcnt & 1, W_H_FULL);
+        if (tl_on) TL(0xE0000);
         tc_fence_after_sync();
         if (wg == 0) {
             uint32_t hv[kHeadN];
@@ -589,6 +754,8 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
             }
             tmem_wait_ld();
             tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sm.bar(H_EMPTY));
             if (valid) {
                 float logits[kA];
 #pragma unroll
@@ -616,6 +783,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 if (P.logprobs) P.logprobs[env] = lp;
                 if (P.values) P.values[env] = value;
             }
+            if (tl_on) TL(0xF0000);
         }
     }
 }
@@ -638,15 +806,16 @@ k_policy_fused(const __grid_constant__ Params P) {
         init(S_FULL, kNS, 1);
         init(S_EMPTY, kNS, 1);
         init(ST_READY, kNS, 4);
-        init(R_FULL, kNR, 1);
-        init(R_EMPTY, kNR, 8);
-        init(AEXP_FULL, kAexpSlots, 8);
+        init(R_FULL, kNR, 4);
+        init(R_EMPTY, kNR, 4);
+        init(AEXP_FULL, kAexpSlots, 4);
         init(AEXP_EMPTY, kAexpSlots, 1);
         init(ACC_FULL, 1, 1);
         init(A_KB, kKBlocks, 8);
-        init(G_FULL, 2, 1);
-        init(G_EMPTY, 2, 4);
+        init(G_FULL, 1, 1);
+        init(G_EMPTY, 1, 8);
         init(H_FULL, 1, 1);
+        init(H_EMPTY, 1, 4);
         *sm.abort_flag() = 0;
         fence_mbar_init();
     }
@@ -654,7 +823,7 @@ k_policy_fused(const __grid_constant__ Params P) {
         tmem_alloc(smem_u32(sm.tmem_base()), 512);
         tmem_relinquish();
     }
-    if (warp == 2 && lane == 0) {
+    if (warp == 3 && lane == 31) {
         prefetch_tensormap(&P.rec_map);
         for (int l = 0; l < P.L; l++) prefetch_tensormap(&P.state_map[l]);
     }
@@ -671,16 +840,16 @@ k_policy_fused(const __grid_constant__ Params P) {
     const uint32_t tmem = *sm.tmem_base();
 
     if (warp == 0) {
-        if (lane == 0) role_weight_loads(sm, P);
+        if (lane < kWLanes) role_weight_loads(sm, P, lane);
     } else if (warp == 1) {
-        if (lane == 0) role_mma<T16>(sm, P, tmem);
+        role_mma<T16>(sm, P, tmem, lane == 0);
     } else if (warp == 2) {
-        if (lane == 0) role_record_loads(sm, P);
+        if (lane < 4 * kRGroups) role_record_loads(sm, P, lane);
     } else if (warp == 3) {
-        if (lane == 0) role_state_loads(sm, P);
-    } else if (warp == 4) {
-        if (lane == 0) {
-            role_state_stores(sm, P);
+        if (lane < kSLanes) {
+            role_state_loads(sm, P, lane);
+        } else if (lane >= 8 && lane < 8 + kSLanes) {
+            role_state_stores(sm, P, lane - 8);
             bulk_wait_group<0>();
         }
     } else {
@@ -712,6 +881,7 @@ struct FusedPlan {
     const float* params = nullptr;
     CUtensorMap state_map[fused::kMaxLayers];
     int sm_count = 0;
+    long long* timeline = nullptr;
 };
 
 bool fused_supported(int H, int L, int A, int precision) {
@@ -745,7 +915,7 @@ int fused_create(FusedPlan** out, int device, int n, int H, int L, int A, int pr
     for (int l = 0; l < L; l++) {
         if (!make_tmap_2d(&p->state_map[l], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4,
                           state + (size_t)l * n * H, (uint64_t)n, (uint64_t)H, (uint64_t)H * 4,
-                          fused::kTile, fused::kSliceUnits, CU_TENSOR_MAP_SWIZZLE_128B)) {
+                          fused::kTile, fused::kHalfUnits, CU_TENSOR_MAP_SWIZZLE_128B)) {
             fused_destroy(p);
             set_error("fused_create: cuTensorMapEncodeTiled failed for the state");
             return CFX_ERR_CUDA;
@@ -795,6 +965,8 @@ int fused_forward(FusedPlan* p, const FusedArgs& a, cudaStream_t st, int* launch
     }
     for (int l = 0; l < p->L; l++) P.state_map[l] = p->state_map[l];
     const ArenaLayout o = ArenaLayout::make(p->H, p->L, p->A);
+    P.records = a.records;
+    P.state = a.state;
     P.image = p->image;
     P.params = p->params;
     P.prev_terminals = a.prev_terminals;
@@ -814,6 +986,7 @@ int fused_forward(FusedPlan* p, const FusedArgs& a, cudaStream_t st, int* launch
     P.off_b_enc = o.b_enc;
     P.off_b_a = o.b_a;
     P.off_b_v = o.b_v;
+    P.timeline = p->timeline;
     const int grid = P.num_tiles < p->sm_count ? P.num_tiles : p->sm_count;
     if (p->precision == CFX_PREC_F16)
         fused::k_policy_fused<__half><<<grid, fused::kThreads, fused::kSmemBytes, st>>>(P);
@@ -833,8 +1006,24 @@ int fused_check_status(FusedPlan* p, cudaStream_t st, unsigned* status) {
     return CFX_OK;
 }
 
+#ifdef CFX_TIMELINE
+// Debug builds: (re)arms the timeline log and copies it out (8 roles x 4096 words).
+extern "C" int cfx_debug_timeline(FusedPlan* p, long long* host_out, int arm) {
+    const size_t bytes = 8 * 4096 * sizeof(long long);
+    if (arm) {
+        if (!p->timeline) CFX_CUDA(cudaMalloc((void**)&p->timeline, bytes));
+        CFX_CUDA(cudaMemset(p->timeline, 0, bytes));
+        return CFX_OK;
+    }
+    if (!p->timeline) return CFX_ERR_INVALID;
+    CFX_CUDA(cudaMemcpy(host_out, p->timeline, bytes, cudaMemcpyDeviceToHost));
+    return CFX_OK;
+}
+#endif
+
 void fused_destroy(FusedPlan* p) {
     if (!p) return;
+    if (p->timeline) cudaFree(p->timeline);
     if (p->image) cudaFree(p->image);
     if (p->status) cudaFree(p->status);
     delete p;

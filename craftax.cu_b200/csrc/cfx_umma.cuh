@@ -10,6 +10,27 @@
 namespace cfx {
 namespace umma {
 
+// Debug builds (-DCFX_CHECK): every wrapper verifies the alignment rules of its operands,
+// reports a violation with printf and SKIPS the operation (the kernel's bounded waits then
+// end it with a status code instead of a fault).
+#ifdef CFX_CHECK
+#define CFX_CHK(cond, what, a, b)                                                          \
+    if (!(cond)) {                                                                         \
+        printf("CFX_CHECK %s: block %d thread %d a=%llx b=%llx\n", what, (int)blockIdx.x,  \
+               (int)threadIdx.x, (unsigned long long)(a), (unsigned long long)(b));        \
+        return;                                                                            \
+    }
+#define CFX_CHK_BOOL(cond, what, a, b)                                                     \
+    if (!(cond)) {                                                                         \
+        printf("CFX_CHECK %s: block %d thread %d a=%llx b=%llx\n", what, (int)blockIdx.x,  \
+               (int)threadIdx.x, (unsigned long long)(a), (unsigned long long)(b));        \
+        return false;                                                                      \
+    }
+#else
+#define CFX_CHK(cond, what, a, b)
+#define CFX_CHK_BOOL(cond, what, a, b)
+#endif
+
 // ------------------------------------------------------------------ addresses
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -33,19 +54,23 @@ __device__ __forceinline__ bool elect_one() {
 
 // ------------------------------------------------------------------ mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    CFX_CHK((bar & 7) == 0 && bar < 233472, "mbar_init", bar, count)
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
 __device__ __forceinline__ void fence_mbar_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    CFX_CHK((bar & 7) == 0 && bar < 233472, "mbar_arrive", bar, 0)
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    CFX_CHK((bar & 7) == 0 && bar < 233472, "mbar_expect_tx", bar, bytes)
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    CFX_CHK_BOOL((bar & 7) == 0 && bar < 233472, "mbar_try_wait", bar, parity)
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred P;\n\t"
@@ -101,6 +126,7 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 // dst, src 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes,
                                          uint32_t bar) {
+    CFX_CHK((dst_smem & 15) == 0 && ((uintptr_t)src & 15) == 0 && (bytes & 15) == 0 && (bar & 7) == 0, "bulk_g2s", dst_smem, (uintptr_t)src)
     asm volatile(
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
@@ -116,6 +142,7 @@ __device__ __forceinline__ void bulk_s2g(void* dst, uint32_t src_smem, uint32_t 
 // a multiple of 16 bytes), y = outer coordinate.
 __device__ __forceinline__ void tensor_g2s_2d(uint32_t dst_smem, const CUtensorMap* map, int x,
                                               int y, uint32_t bar) {
+    CFX_CHK((dst_smem & 127) == 0 && ((uintptr_t)map & 63) == 0 && (bar & 7) == 0, "tensor_g2s", dst_smem, (uintptr_t)map)
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
         "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst_smem),
@@ -125,6 +152,7 @@ __device__ __forceinline__ void tensor_g2s_2d(uint32_t dst_smem, const CUtensorM
 // 2-D tiled tensor copy shared -> global (bulk async-group completion).
 __device__ __forceinline__ void tensor_s2g_2d(const CUtensorMap* map, uint32_t src_smem, int x,
                                               int y) {
+    CFX_CHK((src_smem & 127) == 0 && ((uintptr_t)map & 63) == 0, "tensor_s2g", src_smem, (uintptr_t)map)
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
                  ::"l"(map), "r"(src_smem), "r"(x), "r"(y)
                  : "memory");
@@ -141,6 +169,11 @@ template <int N>
 __device__ __forceinline__ void bulk_wait_group() {
     asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
+// Asks the memory system to bring [src, src + bytes) into L2 (no completion tracking);
+// src 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -148,6 +181,7 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
 // ------------------------------------------------------------------ TMEM
 // Allocation by one full warp; the base address is written to shared memory.
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+    CFX_CHK((dst_smem & 3) == 0, "tmem_alloc", dst_smem, ncols)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
                  "r"(ncols)
                  : "memory");
@@ -260,6 +294,7 @@ __device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, ui
 // Makes the mbarrier track completion of all MMAs this thread issued so far
 // (implies tcgen05.fence::before_thread_sync).
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
+    CFX_CHK((bar & 7) == 0 && bar < 233472, "mma_commit", bar, 0)
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                  : "memory");
 }
