@@ -47,42 +47,51 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """Samples the SM clock and the clock-event (throttle) reasons of one GPU every ~2 ms
+    with NVML (read-only queries) while the timed region runs; falls back to nvidia-smi."""
+    REASONS = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20,
+               "hw_thermal_slowdown": 0x40}
 
     def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.mhz, self.bits, self.max_mhz = index, [], 0, None
+        self._stop = threading.Event()
+        self.thread = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                 "--format=csv,noheader,nounits", "-lms", "20"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            def loop():
+                while not self._stop.is_set():
+                    self.mhz.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                    try:
+                        self.bits |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
+                    except Exception:
+                        self.bits |= int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                    time.sleep(0.002)
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+        except Exception as e:  # NVML missing: one nvidia-smi sample at stop()
+            self.err = str(e)
 
     def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        self.thread.join(timeout=2)
-        mhz = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [nm for i, nm in enumerate(names)
-                   if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
-        return {"sm_mhz": float(np.median(mhz)) if mhz else None,
-                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
-                "samples": len(mhz)}
+        if self.thread is not None:
+            self._stop.set()
+            self.thread.join(timeout=2)
+            reasons = [k for k, b in self.REASONS.items() if self.bits & b]
+            return {"sm_mhz": float(np.median(self.mhz)) if self.mhz else None,
+                    "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(self.mhz)}
+        try:
+            out = subprocess.run(["nvidia-smi", "-i", str(self.index),
+                                  "--query-gpu=clocks.sm,clocks.max.sm", "--format=csv,noheader,nounits"],
+                                 capture_output=True, text=True, timeout=10).stdout.split(",")
+            return {"sm_mhz": float(out[0]), "sm_max_mhz": float(out[1]), "reasons": [],
+                    "samples": 1, "note": "nvidia-smi after the timed region (NVML unavailable)"}
+        except Exception:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock query unavailable"]}
 
 
 def dist_env():
@@ -201,7 +210,10 @@ def run_cfx(args):
         roof = {"bound": "tensor", "achieved": n * flops / (kernel_ms * 1e-3) / 1e12,
                 "peak": tensor_peak, "unit": "TFLOP/s"}
     roof["frac"] = roof["achieved"] / roof["peak"]
-    roof["traffic"] = None
+    # DRAM bytes per launch: per-env figure of the committed ncu capture (65,536 envs, fp16,
+    # L = 2: 378.15 MB read+write), scaled by envs; only quoted for that configuration
+    roof["traffic"] = (NCU_DRAM_BYTES_PER_ENV * n if (prec in ("f16", "bf16") and H == 256 and L == 2)
+                       else None)
     roof["peak_source"] = peaks["source"]
     roof["fused_roofline_ms"] = max(t_hbm, t_tensor) * 1e3
     roof["fused_roofline_frac"] = max(t_hbm, t_tensor) * 1e3 / kernel_ms
@@ -293,12 +305,47 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_ref_cublas(args):
+    """The reference's own CUDA forward (its kernels + cuBLAS, built from its sources into
+    oracle/_ref/) on one B200, forward-only, CUDA-graph replay as in its `run` mode."""
+    rank, _, local = dist_env()
+    if rank != 0:
+        return
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import cfx
+    import oracle as O
+    n, L = args.envs, args.layers
+    if cfx.device_count() < 1:
+        print(json.dumps({"impl": "ref-cublas", "unavailable": "no CUDA device"}))
+        return
+    if args.hidden != 256 or not O.RefCuda.available(L):
+        print(json.dumps({"impl": "ref-cublas", "unavailable":
+                          f"oracle/_ref/libcfref_cuda_l{L}.so not built (reference sources absent)"}))
+        return
+    from cfx.synth import synthetic_records, init_weights
+    ref = O.RefCuda(n, L)
+    ref.set_weights(init_weights(256, L, A, seed=0))
+    base = synthetic_records(min(n, 8192), seed=4)
+    rec = np.tile(base, (n // base.shape[0] + 1, 1))[:n]
+    d_rec = cfx.DeviceBuffer.from_host(rec, local)
+    d_pt = cfx.DeviceBuffer.from_host((np.random.default_rng(4).random(n) < 1 / 265).astype(np.float32), local)
+    mode = {"bf16": ref.BF16, "tf32": ref.TF32, "fp32": ref.FP32}[args.ref_mode]
+    ms = ref.time_forward(mode, d_rec.ptr, d_pt.ptr, warm=max(3, args.warmup), iters=args.steps, graph=1)
+    print(json.dumps({"impl": "ref-cublas", "metric": METRIC, "value": n / (ms * 1e-3), "unit": UNIT,
+                      "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+                      "higher_is_better": True, "dtype": args.ref_mode, "data": "synthetic",
+                      "config": {"workload": f"reference cuBLAS forward, {n} envs, h256x{L}, graph replay",
+                                 "mode": args.ref_mode}}), flush=True)
+    ref.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="cfx", choices=["cfx", "reference"])
+    ap.add_argument("--impl", default="cfx", choices=["cfx", "reference", "ref-cublas"])
+    ap.add_argument("--ref-mode", default="bf16", choices=["bf16", "tf32", "fp32"])
     ap.add_argument("--envs", type=int, default=262144, help="envs per GPU")
     ap.add_argument("--hidden", type=int, default=256)
     ap.add_argument("--layers", type=int, default=2)
@@ -311,11 +358,14 @@ def main():
         args.precision = DEFAULT_PRECISION
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "ref-cublas":
+        run_ref_cublas(args)
     else:
         run_cfx(args)
 
 
 DEFAULT_PRECISION = "f16"
+NCU_DRAM_BYTES_PER_ENV = 378.15e6 / 65536
 
 if __name__ == "__main__":
     main()
