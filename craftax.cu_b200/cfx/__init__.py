@@ -54,6 +54,8 @@ _SIGS = {
     "cfx_policy_forward": (C.c_int, [C.c_void_p, C.POINTER(ForwardIO), C.c_void_p]),
     "cfx_policy_forward_host": (C.c_int, [C.c_void_p, C.POINTER(ForwardIO)]),
     "cfx_policy_check": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "cfx_strict_forward_static": (C.c_int, [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                            C.c_void_p, C.POINTER(ForwardIO), C.c_void_p, C.c_void_p]),
     "cfx_expand_obs": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "cfx_sample_actions": (C.c_int, [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int,
                                      C.c_void_p, C.c_void_p, C.c_void_p]),

@@ -275,3 +275,85 @@ int strict_forward(const StrictArgs& a, cudaStream_t st, int* launches) {
 }
 
 }  // namespace cfx
+
+// ---------------------------------------------------------------- allocation-free variant
+// Strict fp32 forward whose scratch lives in a fixed device array instead of buffers from
+// cudaMalloc.  Meant for hosts that must not allocate once they are running: a rollout
+// worker embedded in another runtime that owns the whole device heap and hands out no
+// memory, or a latency-bound loop where cudaMalloc's device-wide synchronisation (and its
+// chance of failing on a fragmented heap hours into a run) is not acceptable.  Such a caller
+// brings its own parameter arena, state, inputs and outputs; everything else is here.
+//
+// Limits: hidden = 256, layers <= 4, actions <= 63, num_envs <= 1024 (multiple of 32).
+// The array (5.5 MB) is resident on every GPU that loads this library until the process
+// exits.  All calls share it: two calls that overlap on the GPU (different streams, or
+// different host threads) race on it; serialise them.  Nothing in it has to start at zero:
+// the transposed gate matrices, both layer buffers and the logits are fully rewritten by
+// each call before they are read, so stale contents of an earlier call are harmless.
+namespace cfx {
+constexpr int kStaticMaxEnvs = 1024, kStaticHidden = 256, kStaticMaxLayers = 4;
+constexpr size_t kStaticGates = (size_t)kStaticMaxLayers * 3 * kStaticHidden * kStaticHidden;
+constexpr size_t kStaticLayerBuf = (size_t)kStaticMaxEnvs * kStaticHidden;
+constexpr size_t kStaticLogits = (size_t)kStaticMaxEnvs * (kMaxActions + 1);
+constexpr size_t kStaticFloats = kStaticGates + 2 * kStaticLayerBuf + kStaticLogits;
+
+static __device__ __align__(256) float g_static_scratch[kStaticFloats];
+
+// Device address of the array per device ordinal; in host code the symbol's name is only a
+// handle for cudaGetSymbolAddress, never a pointer a kernel could use.
+static float* g_static_scratch_addr[64] = {nullptr};
+}  // namespace cfx
+
+extern "C" int cfx_strict_forward_static(int device, const float* params, int hidden, int layers,
+                                         int num_actions, int num_envs, float* state,
+                                         const cfx_forward_io* io, const uint64_t* step_ctr,
+                                         void* stream) {
+    using namespace cfx;
+    CFX_REQUIRE(params && state && io, "cfx_strict_forward_static: NULL argument");
+    CFX_REQUIRE(io->records && io->actions, "cfx_strict_forward_static: records/actions is NULL");
+    CFX_REQUIRE(device >= 0 && device < 64, "cfx_strict_forward_static: device %d out of [0,64)", device);
+    CFX_REQUIRE(hidden == kStaticHidden,
+                "cfx_strict_forward_static: hidden=%d, the fixed scratch is sized for %d", hidden,
+                kStaticHidden);
+    CFX_REQUIRE(layers >= 1 && layers <= kStaticMaxLayers,
+                "cfx_strict_forward_static: layers=%d exceeds the fixed scratch (max %d)", layers,
+                kStaticMaxLayers);
+    CFX_REQUIRE(num_actions >= 2 && num_actions <= kMaxActions,
+                "cfx_strict_forward_static: num_actions=%d out of [2,%d]", num_actions, kMaxActions);
+    CFX_REQUIRE(num_envs > 0 && num_envs % 32 == 0 && num_envs <= kStaticMaxEnvs,
+                "cfx_strict_forward_static: num_envs=%d must be a multiple of 32 and at most %d "
+                "(size of the fixed scratch)", num_envs, kStaticMaxEnvs);
+    DeviceGuard g(device);
+    if (g_static_scratch_addr[device] == nullptr) {
+        // one-time set-up for this device, with it current: resolve the array's device address
+        float* addr = nullptr;
+        CFX_CUDA(cudaGetSymbolAddress((void**)&addr, g_static_scratch));
+        CFX_REQUIRE(addr != nullptr, "cfx_strict_forward_static: no device address for the scratch");
+        g_static_scratch_addr[device] = addr;
+    }
+    float* base = g_static_scratch_addr[device];
+    cudaStream_t st = (cudaStream_t)stream;
+    const ArenaLayout o = ArenaLayout::make(hidden, layers, num_actions);
+    int rc = launch_transpose_gates(params + o.w_gru, base, hidden, layers, st);
+    if (rc) return rc;
+    StrictArgs a;
+    a.n = num_envs; a.H = hidden; a.L = layers; a.A = num_actions;
+    a.params = params;
+    a.gates_t = base;
+    a.records = io->records;
+    a.prev_terminals = io->prev_terminals;
+    a.uniforms = io->uniforms;
+    a.state = state;
+    a.scratch_h[0] = base + kStaticGates;
+    a.scratch_h[1] = base + kStaticGates + kStaticLayerBuf;
+    a.logits_av = io->logits_av ? io->logits_av : base + kStaticGates + 2 * kStaticLayerBuf;
+    a.r_state = io->r_state;
+    a.env_actions = io->env_actions;
+    a.actions = io->actions;
+    a.logprobs = io->logprobs;
+    a.values = io->values;
+    a.seed = io->seed;
+    a.env_offset = io->env_offset;
+    a.step_ctr = reinterpret_cast<const unsigned long long*>(step_ctr);
+    return strict_forward(a, st, nullptr);
+}

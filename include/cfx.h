@@ -163,6 +163,25 @@ int cfx_policy_check(cfx_policy* p, void* stream);
  * cfx_policy_forward, copies every non-NULL output back and synchronises. */
 int cfx_policy_forward_host(cfx_policy* p, const cfx_forward_io* host_io);
 
+/* Strict-fp32 forward for callers that cannot allocate device memory while they run -- a
+ * rollout worker living inside another runtime that owns the device heap, or a loop that
+ * cannot afford cudaMalloc's device-wide synchronisation or its failure on a fragmented heap.
+ * It has no counterpart in the reference (which allocates all scratch in cu_policy_init).
+ * The caller passes everything persistent itself (all device pointers): the fp32 arena
+ * `params`, the recurrent state [layers][num_envs][hidden] (updated in place), the inputs and
+ * outputs in `io` (as for cfx_policy_forward; bump_step is ignored), and `step_ctr`, the
+ * device counter holding the Philox offset (NULL = 0).  Scratch (transposed gate matrices,
+ * two layer buffers, logits) lives in one fixed 5.5 MB device array inside the library,
+ * resident on every GPU that loads it: hidden must be 256, layers <= 4, num_actions <= 63,
+ * num_envs <= 1024 and a multiple of 32; larger sizes are rejected with CFX_ERR_INVALID.
+ * The first call on a device looks the array's address up (cudaGetSymbolAddress) and should
+ * therefore come before any stream capture.  No call allocates or frees.  All calls share the
+ * array: calls that overlap on the GPU race on it.  Results equal cfx_policy_forward with
+ * CFX_PREC_FP32 bit for bit. */
+int cfx_strict_forward_static(int device, const float* params, int hidden, int layers,
+                              int num_actions, int num_envs, float* state,
+                              const cfx_forward_io* io, const uint64_t* step_ctr, void* stream);
+
 /* Stand-alone stages, for the reference's bitwise gates.
  * cfx_expand_obs: records -> fp32 features [n][843], bit-exact image of
  * k_expand_obs (:10028-10053).  cfx_sample_actions: logits [n][ld] (biases
