@@ -19,8 +19,8 @@
 //                              [256,512)
 //   shared memory  weight ring 3 x 32 KB | state ring 4 x 16 KB | record ring 4 x 10 KB
 //   warps          0 weight loads (3 lanes), 1 MMA issue + TMEM alloc, 2 record loads
-//                  (16 lanes), 3 state loads (lanes 0-3, lane 0 also L2-prefetches the next
-//                  tile) + state stores (lanes 8-11), 4..11 workers (expand, cell, sampler)
+//                  (4 lanes, one per slot), 3 state ring (4 lanes, one per slot: load, store, and the
+//                  L2 prefetch of the next tile), 4..11 workers (expand, cell, sampler)
 // One round of (mbarrier wait, arrive.expect_tx, bulk copy) costs its issuing thread about
 // 500 cycles on B200, so every copy role spreads its sequence over several lanes of its
 // warp (item k belongs to lane k mod lanes) and weight stages are 24-32 KB.
@@ -313,6 +313,13 @@ __device__ __forceinline__ T* chk_ptr(T* p, const char* what) {
 // every role runs in its own function: a failed (timed-out) wait returns to the common exit
 #define CFX_WAIT(barid, parity, code) \
     if (!mbar_wait(sm.bar(barid), (parity), sm.abort_flag(), (code))) return
+// converged warp, only the leader lane polls (one shared-memory poller instead of 32)
+#define CFX_WAIT_LEADER(barid, parity, code)                                                   \
+    {                                                                                          \
+        int ok_ = 1;                                                                           \
+        if (leader) ok_ = mbar_wait(sm.bar(barid), (parity), sm.abort_flag(), (code)) ? 1 : 0; \
+        if (!__shfl_sync(0xffffffffu, ok_, 0)) return;                                         \
+    }
 
 // Record-ring fill order within a tile.  The expand is split by chunk between the two worker
 // warpgroups: wg 1 converts chunks 0..6 (fills 0..6), wg 0 chunks 7..13 (fills 7..12 and the
@@ -327,22 +334,33 @@ __device__ __forceinline__ int rec_pos_of(int fill) {   // fill index -> ring po
     return fill < 7 ? 2 * fill : 2 * (fill - 7) + 1;
 }
 
-// One tile ahead, the records and the state rows of the CTA's next tile are pulled into L2,
-// so that the ring loads hit L2 (hundreds of cycles) instead of HBM (thousands): the rings
-// are far too small to cover HBM latency at the rate the encoder and the cell consume.
-// Called by one state-load lane at the start of each tile, which paces it.
-__device__ __forceinline__ void l2_prefetch_tile(const Params& P, int t) {
-    if (t >= P.num_tiles) return;
-    constexpr uint32_t kPiece = 32768;
-    const int rows = min(kTile, P.n - t * kTile);
-    const uint8_t* rp = P.records + (size_t)t * kTile * kRec;
-    const uint32_t rbytes = (uint32_t)rows * kRec;
-    for (uint32_t o = 0; o < rbytes; o += kPiece) bulk_prefetch_l2(rp + o, min(kPiece, rbytes - o));
-    for (int l = 0; l < P.L; l++) {
-        const uint8_t* sp =
-            reinterpret_cast<const uint8_t*>(P.state + ((size_t)l * P.n + (size_t)t * kTile) * kH);
-        const uint32_t sbytes = (uint32_t)rows * kH * 4;
-        for (uint32_t o = 0; o < sbytes; o += kPiece) bulk_prefetch_l2(sp + o, min(kPiece, sbytes - o));
+// Software prefetch into L2.  The rings are far too small to cover HBM latency at the rate the
+// encoder and the cell consume, so every byte a ring will load is requested from HBM ahead of
+// time in 16 KB pieces, and the ring loads then hit L2 (hundreds of cycles instead of
+// thousands).  The state-ring lanes issue the pieces, a few with every state box they serve,
+// which spreads them over the gate phases (one burst per tile delayed that tile's own loads by
+// thousands of cycles) and keeps the distance to the use short (a whole tile ahead, part of
+// the data had been evicted again):
+//   while layer l < L-1 runs   -> the state rows of layer l+1 of the same tile
+//   while the last layer runs  -> the records and the layer-0 state rows of the CTA's next tile
+constexpr uint32_t kL2Piece = 16384;
+__device__ __forceinline__ void l2_prefetch_rows(const uint8_t* base, uint32_t bytes, int piece) {
+    const uint32_t o = (uint32_t)piece * kL2Piece;
+    if (o < bytes) bulk_prefetch_l2(base + o, min(kL2Piece, bytes - o));
+}
+__device__ __forceinline__ void l2_prefetch_for_box(const Params& P, int tile, int l, int j) {
+    if (l < P.L - 1) {
+        const int rows = min(kTile, P.n - tile * kTile);
+        l2_prefetch_rows(reinterpret_cast<const uint8_t*>(
+                             P.state + ((size_t)(l + 1) * P.n + (size_t)tile * kTile) * kH),
+                         (uint32_t)rows * kH * 4, j);
+    } else {
+        const int t = tile + gridDim.x;
+        if (t >= P.num_tiles) return;
+        const int rows = min(kTile, P.n - t * kTile);
+        l2_prefetch_rows(P.records + (size_t)t * kTile * kRec, (uint32_t)rows * kRec, j);
+        l2_prefetch_rows(reinterpret_cast<const uint8_t*>(P.state + (size_t)t * kTile * kH),
+                         (uint32_t)rows * kH * 4, j);
     }
 }
 
@@ -383,60 +401,51 @@ __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& 
 // all 128 envs is fetched as four boxes (one per i) of 32 rows x 80 bytes starting at the
 // 16-byte boundary below 996 i + 64 c; the 204 tail bytes take three more such box sets.
 __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& P, int lane) {
-    const int group = lane >> 2, i = lane & 3;  // lane = 4 * (fill index mod 4) + box
+    // lane `lane` owns ring slot `lane` and issues all four boxes of the fills that land on it
     uint32_t cnt = 0;
+    const uint32_t slot_addr = smem_u32(sm.r_slot(lane));
     for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x) {
         for (int pos = 0; pos < kRecSubs; pos++, cnt++) {
-            if ((int)(cnt % kRGroups) != group) continue;
+            if ((int)(cnt % kNR) != lane) continue;
             const int sub = rec_fill_at(pos);
-            const int slot = cnt % kNR;
-            CFX_WAIT(R_EMPTY + slot, ((cnt / kNR) & 1) ^ 1, W_R_EMPTY);
-            mbar_arrive_expect_tx(sm.bar(R_FULL + slot), kRBoxBytes);
-            const int x0 = sub < 13 ? ((kRec * i + 64 * sub) & ~15)
-                                    : ((kRec * i + kMap) & ~15) + 80 * (sub - 13);
-            tensor_g2s_2d(smem_u32(sm.r_slot(slot) + i * kRBoxBytes), &P.rec_map, x0, tile * 32,
-                          sm.bar(R_FULL + slot));
+            CFX_WAIT(R_EMPTY + lane, ((cnt / kNR) & 1) ^ 1, W_R_EMPTY);
+            mbar_arrive_expect_tx(sm.bar(R_FULL + lane), kRSlot);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int x0 = sub < 13 ? ((kRec * i + 64 * sub) & ~15)
+                                        : ((kRec * i + kMap) & ~15) + 80 * (sub - 13);
+                tensor_g2s_2d(slot_addr + i * kRBoxBytes, &P.rec_map, x0, tile * 32, sm.bar(R_FULL + lane));
+            }
         }
     }
 }
 
 // State boxes: layer l, tile rows, 32 units -> one 16 KB box, 128-byte swizzled; box j of a
-// layer belongs to slice j / 2 and worker warpgroup j & 1.
-__device__ __forceinline__ void role_state_loads(const Smem& sm, const Params& P, int lane) {
-    uint32_t cnt = 0;
-    for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x) {
-        if (lane == 0) l2_prefetch_tile(P, tile + gridDim.x);
-        for (int l = 0; l < P.L; l++) {
-            for (int j = 0; j < kStateItems; j++, cnt++) {
-                if ((int)(cnt % kSLanes) != lane) continue;
-                const int slot = cnt % kNS;
-                CFX_WAIT(S_EMPTY + slot, ((cnt / kNS) & 1) ^ 1, W_S_EMPTY);
-                mbar_arrive_expect_tx(sm.bar(S_FULL + slot), kSSlot);
-                tensor_g2s_2d(smem_u32(sm.s_slot(slot)), &P.state_map[l], j * kHalfUnits,
-                              tile * kTile, sm.bar(S_FULL + slot));
-            }
-        }
-    }
-}
-
-// The workers overwrite a state slot in place with the new state; this warp writes it
-// back (rows beyond n are clipped by the tensor map) and recycles the slot.
-__device__ __forceinline__ void role_state_stores(const Smem& sm, const Params& P, int lane) {
-    uint32_t cnt = 0;
+// layer belongs to slice j / 2 and worker warpgroup j & 1.  Lane `lane` owns ring slot `lane`
+// and serves the boxes that fall on it one after the other: load, wait until the workers have
+// replaced the contents with the new state, write it back (rows beyond n are clipped by the
+// tensor map), and only then load the next box into the slot.  One lane per slot needs no
+// "slot empty" barrier and saves a hand-off.
+__device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P, int lane) {
+    uint32_t cnt = 0, uses = 0;
+    const uint32_t slot_addr = smem_u32(sm.s_slot(lane));
     for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x) {
         for (int l = 0; l < P.L; l++) {
             for (int j = 0; j < kStateItems; j++, cnt++) {
-                if ((int)(cnt % kSLanes) != lane) continue;
-                const int slot = cnt % kNS;
-                CFX_WAIT(ST_READY + slot, (cnt / kNS) & 1, W_ST_READY);
-                tensor_s2g_2d(&P.state_map[l], smem_u32(sm.s_slot(slot)), j * kHalfUnits,
-                              tile * kTile);
+                if ((int)(cnt % kNS) != lane) continue;
+                mbar_arrive_expect_tx(sm.bar(S_FULL + lane), kSSlot);
+                tensor_g2s_2d(slot_addr, &P.state_map[l], j * kHalfUnits, tile * kTile,
+                              sm.bar(S_FULL + lane));
+                l2_prefetch_for_box(P, tile, l, j);
+                CFX_WAIT(ST_READY + lane, uses & 1, W_ST_READY);
+                uses++;
+                tensor_s2g_2d(&P.state_map[l], slot_addr, j * kHalfUnits, tile * kTile);
                 bulk_commit_group();
                 bulk_wait_group_read<0>();
-                mbar_arrive(sm.bar(S_EMPTY + slot));
             }
         }
     }
+    bulk_wait_group<0>();
 }
 
 // ------------------------------------------------------------------ MMA role
@@ -459,14 +468,14 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
         if (leader) TL(0x1000000);
         // the encoder accumulator overlaps the head accumulator of the previous tile:
         // wait until the sampler threads have read it
-        CFX_WAIT(H_EMPTY, (tcnt & 1) ^ 1, W_H_EMPTY);
+        CFX_WAIT_LEADER(H_EMPTY, (tcnt & 1) ^ 1, W_H_EMPTY);
         // ---- encoder: 14 operand chunks, N = 256 units
         for (int kc = 0; kc < kEncChunks; kc++, acnt++, bcnt++) {
             const int as = acnt % kAexpSlots;
             const int slot = bcnt % kNB;
-            CFX_WAIT(AEXP_FULL + as, (acnt / kAexpSlots) & 1, W_AEXP_FULL);
+            CFX_WAIT_LEADER(AEXP_FULL + as, (acnt / kAexpSlots) & 1, W_AEXP_FULL);
             if (leader) TL(0x20000 | kc);
-            CFX_WAIT(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
+            CFX_WAIT_LEADER(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
             if (leader) TL(0x30000 | kc);
             tc_fence_after_sync();
             const uint32_t a_col = tmem + kColAexp + as * 32;
@@ -491,13 +500,13 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
         for (int l = 0; l < P.L; l++, akb_use++) {
             const uint32_t a_cur = tmem + ((l & 1) ? kColA1 : kColA0);
             for (int j = 0; j < kSlices; j++, gcnt++) {
-                CFX_WAIT(G_EMPTY, (gcnt & 1) ^ 1, W_G_EMPTY);
+                CFX_WAIT_LEADER(G_EMPTY, (gcnt & 1) ^ 1, W_G_EMPTY);
                 if (leader) TL(0x40000 | (l << 8) | j);
 #pragma unroll
                 for (int kb = 0; kb < kKBlocks; kb++, bcnt++) {
-                    if (j == 0) CFX_WAIT(A_KB + kb, akb_use & 1, W_A_KB);
+                    if (j == 0) CFX_WAIT_LEADER(A_KB + kb, akb_use & 1, W_A_KB);
                     const int slot = bcnt % kNB;
-                    CFX_WAIT(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
+                    CFX_WAIT_LEADER(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
                     if (leader) TL(0x50000 | (l << 8) | (j << 2) | kb);
                     tc_fence_after_sync();
                     const uint64_t bd = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
@@ -519,10 +528,10 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
         {
             const uint32_t a_cur = tmem + ((P.L & 1) ? kColA1 : kColA0);
 #pragma unroll
-            for (int kb = 0; kb < kKBlocks; kb++) CFX_WAIT(A_KB + kb, akb_use & 1, W_A_KB);
+            for (int kb = 0; kb < kKBlocks; kb++) CFX_WAIT_LEADER(A_KB + kb, akb_use & 1, W_A_KB);
             akb_use++;
             const int slot = bcnt % kNB;
-            CFX_WAIT(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
+            CFX_WAIT_LEADER(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
             tc_fence_after_sync();
             const uint64_t bd = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
             if (leader) {
@@ -806,7 +815,7 @@ k_policy_fused(const __grid_constant__ Params P) {
         init(S_FULL, kNS, 1);
         init(S_EMPTY, kNS, 1);
         init(ST_READY, kNS, 4);
-        init(R_FULL, kNR, 4);
+        init(R_FULL, kNR, 1);
         init(R_EMPTY, kNR, 4);
         init(AEXP_FULL, kAexpSlots, 4);
         init(AEXP_EMPTY, kAexpSlots, 1);
@@ -844,14 +853,9 @@ k_policy_fused(const __grid_constant__ Params P) {
     } else if (warp == 1) {
         role_mma<T16>(sm, P, tmem, lane == 0);
     } else if (warp == 2) {
-        if (lane < 4 * kRGroups) role_record_loads(sm, P, lane);
+        if (lane < kNR) role_record_loads(sm, P, lane);
     } else if (warp == 3) {
-        if (lane < kSLanes) {
-            role_state_loads(sm, P, lane);
-        } else if (lane >= 8 && lane < 8 + kSLanes) {
-            role_state_stores(sm, P, lane - 8);
-            bulk_wait_group<0>();
-        }
+        if (lane < kNS) role_state_ring(sm, P, lane);
     } else {
         role_worker<T16>(sm, P, tmem, warp, lane);
     }
