@@ -31,6 +31,14 @@ typedef struct {
                          kernels read prev_terminals unconditionally */
 } refcu;
 
+/* Host-to-device copy that has LANDED when it returns.  A pageable cudaMemcpy returns once
+ * the data is staged; the reference's policy streams are non-blocking, so work enqueued on
+ * them next would not wait for the DMA (it would repack or read stale weights). */
+static void refcu_h2d(void* dst, const void* src, size_t bytes) {
+    CU_CHECK(cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice));
+    CU_CHECK(cudaDeviceSynchronize());
+}
+
 static CuPolicy* refcu_pick(refcu* r, int mode) {
     g_gemm_bf16 = (mode == REFCU_BF16) ? 1 : 0;
     CUBLAS_CHECK(cublasSetMathMode(
@@ -79,8 +87,7 @@ void refcu_set_weights(void* h, const float* host_arena) {
     refcu* r = (refcu*)h;
     for (int i = 0; i < 2; i++) {
         CuPolicy* p = &r->pol[i];
-        CU_CHECK(cudaMemcpy(p->params, host_arena, (size_t)CF_NN_PARAM_COUNT * sizeof(float),
-                            cudaMemcpyHostToDevice));
+        refcu_h2d(p->params, host_arena, (size_t)CF_NN_PARAM_COUNT * sizeof(float));
         g_gemm_bf16 = (i == 0);
         cu_params_refresh_bf16(p, p->stream);
         cu_pack_wav(p, p->stream);
@@ -98,9 +105,7 @@ void refcu_get_weights(void* h, float* host_arena) {
 void refcu_set_state(void* h, int mode, const float* host_state) {
     refcu* r = (refcu*)h;
     CuPolicy* p = &r->pol[mode == REFCU_BF16 ? 0 : 1];
-    CU_CHECK(cudaMemcpy(p->h_state, host_state,
-                        (size_t)CF_NN_LAYERS * CF_NN_HIDDEN * r->n * sizeof(float),
-                        cudaMemcpyHostToDevice));
+    refcu_h2d(p->h_state, host_state, (size_t)CF_NN_LAYERS * CF_NN_HIDDEN * r->n * sizeof(float));
 }
 
 void refcu_get_state(void* h, int mode, float* host_state) {
@@ -114,7 +119,7 @@ void refcu_get_state(void* h, int mode, float* host_state) {
 void refcu_set_step(void* h, unsigned long long step) {
     refcu* r = (refcu*)h;
     for (int i = 0; i < 2; i++)
-        CU_CHECK(cudaMemcpy(r->pol[i].step_ctr, &step, sizeof(step), cudaMemcpyHostToDevice));
+        refcu_h2d(r->pol[i].step_ctr, &step, sizeof(step));
 }
 
 /* Enqueues the batched forward on the policy's stream (no sync). */
@@ -220,7 +225,7 @@ void refcu_scalar_set_state(void* h, const float* host_state_lnh) {
         for (int e = 0; e < n; e++)
             for (int k = 0; k < H; k++)
                 t[((size_t)l * H + k) * n + e] = host_state_lnh[((size_t)l * n + e) * H + k];
-    CU_CHECK(cudaMemcpy(r->ref_state, t, (size_t)L * H * n * sizeof(float), cudaMemcpyHostToDevice));
+    refcu_h2d(r->ref_state, t, (size_t)L * H * n * sizeof(float));
     free(t);
 }
 

@@ -16,7 +16,7 @@ def refcu(oracle, gpu):
     return oracle.RefCuda
 
 
-def _inputs(cfx, oracle, golden_env, n_rep=1):
+def _inputs(cfx, oracle, golden_env, n_rep=1, L=L):
     recs = golden_env["records"]
     rec = np.concatenate([recs[3]] * n_rep)
     n = rec.shape[0]
@@ -26,9 +26,11 @@ def _inputs(cfx, oracle, golden_env, n_rep=1):
     return rec, state, prev_t, n
 
 
-@pytest.mark.parametrize("scheme", ["normal", "uniform"])
-def test_oracle_matches_reference_scalar_kernel(cfx, oracle, refcu, golden_env, scheme):
-    rec, state, prev_t, n = _inputs(cfx, oracle, golden_env)
+@pytest.mark.parametrize("scheme,L", [("normal", 2), ("uniform", 2), ("normal", 3)])
+def test_oracle_matches_reference_scalar_kernel(cfx, oracle, refcu, golden_env, scheme, L):
+    if not refcu.available(L):
+        pytest.skip(f"oracle/_ref/libcfref_cuda_l{L}.so not built")
+    rec, state, prev_t, n = _inputs(cfx, oracle, golden_env, L=L)
     params = oracle.init_weights(H, L, A, seed=7, scheme=scheme)
     ref = refcu(n, L)
     ref.set_weights(params)
@@ -51,8 +53,11 @@ def test_oracle_matches_reference_scalar_kernel(cfx, oracle, refcu, golden_env, 
     ref.close()
 
 
-def test_strict_path_matches_reference_fp32_pipeline(cfx, oracle, refcu, golden_env):
-    rec, state, prev_t, n = _inputs(cfx, oracle, golden_env, n_rep=2)
+@pytest.mark.parametrize("L", [2, 3])
+def test_strict_path_matches_reference_fp32_pipeline(cfx, oracle, refcu, golden_env, L):
+    if not refcu.available(L):
+        pytest.skip(f"oracle/_ref/libcfref_cuda_l{L}.so not built")
+    rec, state, prev_t, n = _inputs(cfx, oracle, golden_env, n_rep=2, L=L)
     params = oracle.init_weights(H, L, A, seed=9)
     ref = refcu(n, L)
     ref.set_weights(params)
