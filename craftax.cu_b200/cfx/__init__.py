@@ -12,7 +12,8 @@ import os
 import numpy as np
 
 PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LIB_PATH = os.path.join(PKG, "libcfx.so")
+# CFX_LIB names another build of the same library (a debug or experimental build)
+LIB_PATH = os.environ.get("CFX_LIB") or os.path.join(PKG, "libcfx.so")
 
 OBS, MAP, TAIL, REC = 843, 792, 51, 996
 PREC_FP32, PREC_F16, PREC_BF16, PREC_TF32 = 0, 1, 2, 3

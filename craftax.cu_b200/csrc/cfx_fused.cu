@@ -48,10 +48,10 @@ constexpr int kHalfUnits = 32;   // units of a slice handled by one worker warpg
 constexpr int kStateItems = kH / kHalfUnits;  // 8 state boxes (128 rows x 32 units) per layer
 constexpr int kKBlocks = kH / 64;          // 4 K blocks of 64 per 256-wide operand
 constexpr int kEncChunks = 14;   // 12 full map chunks, 1 partial (24 bytes), 1 tail (51 floats)
-constexpr int kRecSubs = 16;     // record ring fills per tile: 13 map + 3 tail boxes-sets
+constexpr int kRecFills = 13;    // record ring fills per tile: one per map chunk (the tail has its own buffer)
 constexpr int kHeadN = 48;       // 43 logits + value, padded to a multiple of 16
 
-constexpr int kBSlot = 32768, kNB = 3;
+constexpr int kBSlot = 32768, kNB = 4;
 constexpr int kSSlot = 16384, kNS = 4;
 constexpr int kRBoxBytes = 32 * 80, kRSlot = 4 * kRBoxBytes, kNR = 4;
 constexpr int kAexpSlots = 8;
@@ -65,7 +65,7 @@ constexpr int kHeadStageBytes = kHeadN * 128;        // block: [48 rows][64 K]
 constexpr int kEncStages = kEncChunks * 2;           // encoder blocks in the image
 constexpr int kEncCopyBytes = 2 * kEncStageBytes, kGateCopyBytes = kGateStageBytes,
               kHeadCopyBytes = kKBlocks * kHeadStageBytes;
-constexpr int kWLanes = 3, kRGroups = 4, kSLanes = 4;
+constexpr int kWLanes = 4, kSLanes = 4;
 // A lane that handles every G-th item of an N-slot ring waits on its slot's "empty" barrier
 // by phase parity; that is only sound while it cannot run two phases ahead of the slot,
 // i.e. while G <= N (its previous item, G back, already needed the slot use N+G back).
@@ -73,7 +73,7 @@ constexpr int kWLanes = 3, kRGroups = 4, kSLanes = 4;
 // same consumer (a consumer that skips slots owned by others could otherwise be two phases
 // off): the record ring (4 slots, fills alternate between the worker warpgroups) and the
 // state ring (4 slots, slices alternate) satisfy this; each weight ring has one consumer.
-static_assert(kWLanes <= kNB && kRGroups <= kNR && kSLanes <= kNS && kNR == 4 && kNS == 4, "ring ownership");
+static_assert(kWLanes <= kNB && kSLanes <= kNS && kNS == 4, "ring ownership");
 
 __host__ __device__ constexpr size_t image_bytes(int L) {
     return (size_t)kEncStages * kEncStageBytes + (size_t)L * kSlices * kKBlocks * kGateStageBytes +
@@ -87,15 +87,23 @@ constexpr uint32_t kColAexp = 0, kColAcc = 256;
 // shared memory map (offsets from a 1024-byte aligned base)
 constexpr int kOffB = 0;
 constexpr int kOffS = kOffB + kNB * kBSlot;
-constexpr int kOffR = kOffS + kNS * kSSlot;
-constexpr int kOffBias = kOffR + kNR * kRSlot;     // b_enc[256] fp32, b_av[48] fp32
+// The record ring lives INSIDE the state slots (record slot k = the first 10 KB of state slot
+// k): records are needed only while the encoder runs, state boxes only while the gate layers
+// run.  Two per-tile hand-offs order the two uses of the memory (REC_DONE, S_DONE below).
+constexpr int kOffR = kOffS, kRStride = kSSlot;   // record slot k = the first 10 KB of state slot k
+static_assert(kNR * kRSlot <= kNS * kSSlot && kStateItems == 2 * kNS,
+              "the record slots lie inside the state slots; a state lane's last box per tile is fixed");
+constexpr int kOffT = kOffS + kNS * kSSlot;        // the 204 tail bytes of every record: 3 box sets
+constexpr int kTailBytes = 3 * kRSlot;
+constexpr int kOffBias = kOffT + kTailBytes;       // b_enc[256] fp32, b_av[48] fp32
 constexpr int kOffBars = kOffBias + (kH + kHeadN) * 4;
 enum Bar {
-    B_FULL = 0, B_EMPTY = B_FULL + kNB, S_FULL = B_EMPTY + kNB, S_EMPTY = S_FULL + kNS,
-    ST_READY = S_EMPTY + kNS, R_FULL = ST_READY + kNS, R_EMPTY = R_FULL + kNR,
+    B_FULL = 0, B_EMPTY = B_FULL + kNB, S_FULL = B_EMPTY + kNB, S_DONE = S_FULL + kNS,
+    ST_READY = S_DONE + kNS, R_FULL = ST_READY + kNS, R_EMPTY = R_FULL + kNR,
     AEXP_FULL = R_EMPTY + kNR, AEXP_EMPTY = AEXP_FULL + kAexpSlots,
     ACC_FULL = AEXP_EMPTY + kAexpSlots, A_KB = ACC_FULL + 1, G_FULL = A_KB + kKBlocks,
-    G_EMPTY = G_FULL + 1, H_FULL = G_EMPTY + 1, H_EMPTY = H_FULL + 1, NUM_BARS = H_EMPTY + 1
+    G_EMPTY = G_FULL + 1, H_FULL = G_EMPTY + 1, H_EMPTY = H_FULL + 1, REC_DONE = H_EMPTY + 1,
+    T_FULL = REC_DONE + 1, T_EMPTY = T_FULL + 1, NUM_BARS = T_EMPTY + 1
 };
 constexpr int kOffMisc = kOffBars + NUM_BARS * 8;  // tmem base, abort flag
 constexpr int kSmemBytes = kOffMisc + 16 + 1024;   // + alignment slack
@@ -105,7 +113,7 @@ constexpr int kWorkerWarp0 = 4, kNumWarps = 12, kThreads = kNumWarps * 32;
 // wait-site codes recorded in the status word when a bounded wait gives up
 enum WaitCode : uint32_t {
     W_B_EMPTY = 1, W_B_FULL, W_R_EMPTY, W_R_FULL, W_S_EMPTY, W_S_FULL, W_ST_READY, W_AEXP_EMPTY,
-    W_AEXP_FULL, W_ACC_FULL, W_A_KB, W_G_FULL, W_G_EMPTY, W_H_FULL, W_H_EMPTY
+    W_AEXP_FULL, W_ACC_FULL, W_A_KB, W_G_FULL, W_G_EMPTY, W_H_FULL, W_H_EMPTY, W_REC_DONE, W_S_DONE, W_T_FULL, W_T_EMPTY
 };
 
 struct Params {
@@ -268,7 +276,8 @@ struct Smem {
     __device__ __forceinline__ uint32_t bar(int i) const { return smem_u32(base + kOffBars + i * 8); }
     __device__ __forceinline__ uint8_t* b_slot(int s) const { return base + kOffB + s * kBSlot; }
     __device__ __forceinline__ uint8_t* s_slot(int s) const { return base + kOffS + s * kSSlot; }
-    __device__ __forceinline__ uint8_t* r_slot(int s) const { return base + kOffR + s * kRSlot; }
+    __device__ __forceinline__ uint8_t* r_slot(int s) const { return base + kOffR + s * kRStride; }
+    __device__ __forceinline__ uint8_t* t_buf() const { return base + kOffT; }
     __device__ __forceinline__ float* bias() const { return reinterpret_cast<float*>(base + kOffBias); }
     __device__ __forceinline__ uint32_t* tmem_base() const { return reinterpret_cast<uint32_t*>(base + kOffMisc); }
     __device__ __forceinline__ volatile uint32_t* abort_flag() const {
@@ -293,10 +302,30 @@ __device__ __forceinline__ T* chk_ptr(T* p, const char* what) {
 #define CHKP(p, what) (p)
 #endif
 
-// Optional timeline (compile with -DCFX_TIMELINE): block 0 logs (tag, clock64) pairs per role.
-#ifdef CFX_TIMELINE
+// Optional instrumentation of block 0 (debug builds only).
+//  -DCFX_TIMELINE: every role logs (tag, clock64) pairs.
+//  -DCFX_TIMELINE -DCFX_PROFILE: instead of a log, every role sums the cycles between
+//  consecutive marks into per-bucket registers and writes the sums once at its end (far less
+//  intrusive than the log: no stores on the timed path).
+#if defined(CFX_PROFILE)
+#define TL_INIT(role)                                  \
+    long long* tl_ptr = P.timeline + (role) * 4096;    \
+    long long pf_[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; \
+    long long pf_t = clock64()
+#define TLB(b, tag)                        \
+    do {                                   \
+        const long long n_ = clock64();    \
+        pf_[b] += n_ - pf_t;               \
+        pf_t = n_;                         \
+    } while (0)
+#define TL_FLUSH()                                                       \
+    do {                                                                 \
+        if (blockIdx.x == 0 && P.timeline != nullptr)                    \
+            for (int i_ = 0; i_ < 12; i_++) tl_ptr[i_] = pf_[i_];        \
+    } while (0)
+#elif defined(CFX_TIMELINE)
 #define TL_INIT(role) long long* tl_ptr = P.timeline + (role) * 4096; int tl_i = 0
-#define TL(tag)                                                               \
+#define TLB(b, tag)                                                           \
     do {                                                                      \
         if (blockIdx.x == 0 && P.timeline != nullptr && tl_i < 2047) {        \
             tl_ptr[2 * tl_i] = (long long)(tag);                              \
@@ -305,34 +334,41 @@ __device__ __forceinline__ T* chk_ptr(T* p, const char* what) {
             tl_ptr[4094] = tl_i;                                              \
         }                                                                     \
     } while (0)
+#define TL_FLUSH()
 #else
 #define TL_INIT(role)
-#define TL(tag)
+#define TLB(b, tag)
+#define TL_FLUSH()
 #endif
 
 // every role runs in its own function: a failed (timed-out) wait returns to the common exit
+// Copy lanes and worker warps: every lane polls with try_wait (suspends while not ready).
+// Measured alternatives, all slower on B200: one polling lane per worker warp plus a shuffle
+// (+25 % kernel time), a test_wait probe in front of the loop (+6 %).
 #define CFX_WAIT(barid, parity, code) \
     if (!mbar_wait(sm.bar(barid), (parity), sm.abort_flag(), (code))) return
-// converged warp, only the leader lane polls (one shared-memory poller instead of 32)
-#define CFX_WAIT_LEADER(barid, parity, code)                                                   \
-    {                                                                                          \
-        int ok_ = 1;                                                                           \
-        if (leader) ok_ = mbar_wait(sm.bar(barid), (parity), sm.abort_flag(), (code)) ? 1 : 0; \
-        if (!__shfl_sync(0xffffffffu, ok_, 0)) return;                                         \
-    }
+#define CFX_WAITW(barid, parity, code) CFX_WAIT(barid, parity, code)
+// The MMA role runs on ONE thread; the other lanes of its warp go straight to the exit.  (A
+// converged warp with an elected lane, one shuffle per wait and a __syncwarp per stage, was
+// 10 % slower end to end.)  It polls with test_wait: it never suspends.
+#define CFX_WAIT_LEADER(barid, parity, code) \
+    if (!mbar_wait_spin(sm.bar(barid), (parity), sm.abort_flag(), (code))) return
 
-// Record-ring fill order within a tile.  The expand is split by chunk between the two worker
-// warpgroups: wg 1 converts chunks 0..6 (fills 0..6), wg 0 chunks 7..13 (fills 7..12 and the
-// three tail fills 13..15).  Fills are issued interleaved (wg1, wg0, wg1, ...) so that with a
-// 4-slot ring each warpgroup effectively owns two slots and neither waits for the other.
-__device__ __forceinline__ int rec_fill_at(int pos) {   // ring position -> fill index
-    if (pos >= 14) return pos;
-    return (pos & 1) ? 7 + (pos >> 1) : (pos >> 1);
+// Record ring schedule.  Fill kc of a tile carries map chunk kc (64 features of all 128 envs)
+// and lands in slot kc % 4.  Even chunks are expanded by worker warpgroup 1, odd chunks and
+// the tail by warpgroup 0, so even slots belong to wg 1 and odd slots to wg 0 for the whole
+// launch.  That is what makes the phase-parity waits sound: a waiter may be at most one phase
+// ahead of its barrier, and the warpgroup that waits for a fill has itself consumed the
+// previous fill of the same slot.  (A schedule in which the other warpgroup consumed a slot's
+// next fill raised a launch failure: it passed its wait two phases early and arrived on the
+// slot's "empty" barrier out of turn.)  Slot 0 takes four fills per tile, the others three.
+__device__ __forceinline__ int rec_owner(int kc) { return (kc & 1) ^ 1; }
+__device__ __forceinline__ int rec_slot(int kc) { return kc & (kNR - 1); }
+__device__ __forceinline__ uint32_t rec_phase(uint32_t it, int kc) {   // phase index of fill kc
+    return ((kc & (kNR - 1)) == 0 ? 4u : 3u) * it + (uint32_t)(kc >> 2);
 }
-__device__ __forceinline__ int rec_pos_of(int fill) {   // fill index -> ring position
-    if (fill >= 14) return fill;
-    return fill < 7 ? 2 * fill : 2 * (fill - 7) + 1;
-}
+constexpr int kLastWg1 = 12;
+static_assert(kNR == 4 && kRecFills == 13, "schedule above");
 
 // Software prefetch into L2.  The rings are far too small to cover HBM latency at the rate the
 // encoder and the cell consume, so every byte a ring will load is requested from HBM ahead of
@@ -389,9 +425,13 @@ __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& 
             }
             const int slot = cnt % kNB;
             CFX_WAIT(B_EMPTY + slot, ((cnt / kNB) & 1) ^ 1, W_B_EMPTY);
-            if (lane == 0) TL(0x10000 | s);
+            if (lane == 0) TLB(1, 0x10000 | s);
+#ifdef CFX_ABL_NOWEIGHTS
+            mbar_arrive(sm.bar(B_FULL + slot));
+#else
             mbar_arrive_expect_tx(sm.bar(B_FULL + slot), bytes);
             bulk_g2s(smem_u32(sm.b_slot(slot)), P.image + off, bytes, sm.bar(B_FULL + slot));
+#endif
         }
     }
 }
@@ -401,21 +441,44 @@ __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& 
 // all 128 envs is fetched as four boxes (one per i) of 32 rows x 80 bytes starting at the
 // 16-byte boundary below 996 i + 64 c; the 204 tail bytes take three more such box sets.
 __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& P, int lane) {
-    // lane `lane` owns ring slot `lane` and issues all four boxes of the fills that land on it
-    uint32_t cnt = 0;
-    const uint32_t slot_addr = smem_u32(sm.r_slot(lane));
-    for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x) {
-        for (int pos = 0; pos < kRecSubs; pos++, cnt++) {
-            if ((int)(cnt % kNR) != lane) continue;
-            const int sub = rec_fill_at(pos);
-            CFX_WAIT(R_EMPTY + lane, ((cnt / kNR) & 1) ^ 1, W_R_EMPTY);
-            mbar_arrive_expect_tx(sm.bar(R_FULL + lane), kRSlot);
+    uint32_t it = 0;
+    if (lane < kNR) {
+        // lane `lane` owns ring slot `lane` and issues all four boxes of the fills that land on it
+        const uint32_t slot_addr = smem_u32(sm.r_slot(lane));
+        for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x, it++) {
+            // first fill of the tile: the previous tile's last state box has left this slot
+            CFX_WAIT(S_DONE + lane, (it & 1) ^ 1, W_S_DONE);
+            for (int kc = 0; kc < kRecFills; kc++) {
+                if (rec_slot(kc) != lane) continue;
+                CFX_WAIT(R_EMPTY + lane, (rec_phase(it, kc) & 1) ^ 1, W_R_EMPTY);
+#ifdef CFX_ABL_NOREC
+                mbar_arrive(sm.bar(R_FULL + lane));
+                continue;
+#endif
+                mbar_arrive_expect_tx(sm.bar(R_FULL + lane), kRSlot);
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int x0 = sub < 13 ? ((kRec * i + 64 * sub) & ~15)
-                                        : ((kRec * i + kMap) & ~15) + 80 * (sub - 13);
-                tensor_g2s_2d(slot_addr + i * kRBoxBytes, &P.rec_map, x0, tile * 32, sm.bar(R_FULL + lane));
+                for (int i = 0; i < 4; i++)
+                    tensor_g2s_2d(slot_addr + i * kRBoxBytes, &P.rec_map, (kRec * i + 64 * kc) & ~15,
+                                  tile * 32, sm.bar(R_FULL + lane));
             }
+        }
+    } else {
+        // the tail lane: three box sets cover the 51 raw floats (204 bytes from byte 792) of
+        // every record; they go to a buffer of their own, read by warpgroup 0 only
+        const uint32_t dst = smem_u32(sm.t_buf());
+        for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x, it++) {
+            CFX_WAIT(T_EMPTY, (it & 1) ^ 1, W_T_EMPTY);
+#ifdef CFX_ABL_NOREC
+            mbar_arrive(sm.bar(T_FULL));
+            continue;
+#endif
+            mbar_arrive_expect_tx(sm.bar(T_FULL), kTailBytes);
+#pragma unroll
+            for (int s3 = 0; s3 < 3; s3++)
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    tensor_g2s_2d(dst + s3 * kRSlot + i * kRBoxBytes, &P.rec_map,
+                                  ((kRec * i + kMap) & ~15) + 80 * s3, tile * 32, sm.bar(T_FULL));
         }
     }
 }
@@ -427,21 +490,32 @@ __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& 
 // tensor map), and only then load the next box into the slot.  One lane per slot needs no
 // "slot empty" barrier and saves a hand-off.
 __device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P, int lane) {
-    uint32_t cnt = 0, uses = 0;
+    uint32_t cnt = 0, uses = 0, it = 0;
     const uint32_t slot_addr = smem_u32(sm.s_slot(lane));
-    for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x) {
+    for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x, it++) {
         for (int l = 0; l < P.L; l++) {
             for (int j = 0; j < kStateItems; j++, cnt++) {
                 if ((int)(cnt % kNS) != lane) continue;
+                // first box of the tile: every record of the tile has been expanded
+                if (l == 0 && j == lane) CFX_WAIT(REC_DONE, it & 1, W_REC_DONE);
+#ifdef CFX_ABL_NOSTATE
+                mbar_arrive(sm.bar(S_FULL + lane));
+                CFX_WAIT(ST_READY + lane, uses & 1, W_ST_READY);
+                uses++;
+#else
                 mbar_arrive_expect_tx(sm.bar(S_FULL + lane), kSSlot);
                 tensor_g2s_2d(slot_addr, &P.state_map[l], j * kHalfUnits, tile * kTile,
                               sm.bar(S_FULL + lane));
+#ifndef CFX_ABL_NOPREFETCH
                 l2_prefetch_for_box(P, tile, l, j);
+#endif
                 CFX_WAIT(ST_READY + lane, uses & 1, W_ST_READY);
                 uses++;
                 tensor_s2g_2d(&P.state_map[l], slot_addr, j * kHalfUnits, tile * kTile);
                 bulk_commit_group();
                 bulk_wait_group_read<0>();
+#endif
+                if (l == P.L - 1 && j == lane + kNS) mbar_arrive(sm.bar(S_DONE + lane));
             }
         }
     }
@@ -449,14 +523,18 @@ __device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P,
 }
 
 // ------------------------------------------------------------------ MMA role
-// The whole warp runs this role converged (loop state stays warp-uniform); only the leader
-// lane issues MMAs and commits.  Issue cost matters: the issuer shares its scheduler with two
-// busy worker warps and needs ~90 cycles per MMA instruction, so MMAs are made as wide as the
-// tensor memory budget allows (N = 192 / 256, 96 / 128 cycles of tensor pipe each),
-// descriptors are one add away from a per-slot base and every K-step loop is fully unrolled
-// (rebuilding descriptors per MMA measured ~150 cycles per instruction on B200).
+// One thread issues every MMA of the CTA.  The tensor pipe queues about eight MMAs, so the
+// issuer runs ahead of it as long as its own loop is short: descriptors are one add away from
+// a per-slot base and every K-step loop is fully unrolled (rebuilding descriptors per MMA
+// measured ~150 cycles per instruction on B200, against 45-50 for the bare instruction), and
+// MMAs are as wide as the tensor memory budget allows (N = 192 / 256).
+#ifdef CFX_ABL_NOMMA
+#define MMA_TS(...) ((void)0)
+#else
+#define MMA_TS(...) mma_f16_ts(__VA_ARGS__)
+#endif
 template <typename T16>
-__device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32_t tmem, bool leader) {
+__device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32_t tmem) {
     constexpr uint32_t fmt = Op16<T16>::kFmt;
     constexpr uint32_t idesc_enc = make_idesc(fmt, 128, kH);
     constexpr uint32_t idesc_gate = make_idesc(fmt, 128, 3 * kSliceUnits);
@@ -465,7 +543,7 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
     uint32_t bcnt = 0, acnt = 0, akb_use = 0, gcnt = 0, tcnt = 0;
     TL_INIT(0);
     for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x, tcnt++) {
-        if (leader) TL(0x1000000);
+        TLB(0, 0x1000000);
         // the encoder accumulator overlaps the head accumulator of the previous tile:
         // wait until the sampler threads have read it
         CFX_WAIT_LEADER(H_EMPTY, (tcnt & 1) ^ 1, W_H_EMPTY);
@@ -474,54 +552,57 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
             const int as = acnt % kAexpSlots;
             const int slot = bcnt % kNB;
             CFX_WAIT_LEADER(AEXP_FULL + as, (acnt / kAexpSlots) & 1, W_AEXP_FULL);
-            if (leader) TL(0x20000 | kc);
+            TLB(2, 0x20000 | kc);
             CFX_WAIT_LEADER(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
-            if (leader) TL(0x30000 | kc);
+            TLB(3, 0x30000 | kc);
             tc_fence_after_sync();
             const uint32_t a_col = tmem + kColAexp + as * 32;
             const uint64_t bd = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
-            if (leader) {
-                if (kc == 0) mma_f16_ts(tmem + kColAcc, a_col, bd, idesc_enc, 0);
-                else mma_f16_ts(tmem + kColAcc, a_col, bd, idesc_enc, 1);
-                mma_f16_ts(tmem + kColAcc, a_col + 8, bd + 2, idesc_enc, 1);
+            {
+                if (kc == 0) MMA_TS(tmem + kColAcc, a_col, bd, idesc_enc, 0);
+                else MMA_TS(tmem + kColAcc, a_col, bd, idesc_enc, 1);
+                MMA_TS(tmem + kColAcc, a_col + 8, bd + 2, idesc_enc, 1);
                 if (kc != 12) {  // chunk 12 carries 24 map bytes: two K steps
-                    mma_f16_ts(tmem + kColAcc, a_col + 16, bd + 4, idesc_enc, 1);
-                    mma_f16_ts(tmem + kColAcc, a_col + 24, bd + 6, idesc_enc, 1);
+                    MMA_TS(tmem + kColAcc, a_col + 16, bd + 4, idesc_enc, 1);
+                    MMA_TS(tmem + kColAcc, a_col + 24, bd + 6, idesc_enc, 1);
                 }
                 mma_commit(sm.bar(B_EMPTY + slot));
                 mma_commit(sm.bar(AEXP_EMPTY + as));
-                TL(0x38000 | kc);
+                TLB(4, 0x38000 | kc);
             }
-            __syncwarp();
+            
         }
-        if (leader) mma_commit(sm.bar(ACC_FULL));
-        __syncwarp();
+        mma_commit(sm.bar(ACC_FULL));
+        
         // ---- MinGRU layers: 4 slices of 64 units, one stage per K block, N = 192 (zh|zg|zp)
         for (int l = 0; l < P.L; l++, akb_use++) {
             const uint32_t a_cur = tmem + ((l & 1) ? kColA1 : kColA0);
             for (int j = 0; j < kSlices; j++, gcnt++) {
                 CFX_WAIT_LEADER(G_EMPTY, (gcnt & 1) ^ 1, W_G_EMPTY);
-                if (leader) TL(0x40000 | (l << 8) | j);
+                TLB(5, 0x40000 | (l << 8) | j);
 #pragma unroll
                 for (int kb = 0; kb < kKBlocks; kb++, bcnt++) {
-                    if (j == 0) CFX_WAIT_LEADER(A_KB + kb, akb_use & 1, W_A_KB);
+                    if (j == 0) {
+                        CFX_WAIT_LEADER(A_KB + kb, akb_use & 1, W_A_KB);
+                        TLB(9, 0x48000 | (l << 8) | kb);
+                    }
                     const int slot = bcnt % kNB;
                     CFX_WAIT_LEADER(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
-                    if (leader) TL(0x50000 | (l << 8) | (j << 2) | kb);
+                    TLB(6, 0x50000 | (l << 8) | (j << 2) | kb);
                     tc_fence_after_sync();
                     const uint64_t bd = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
-                    if (leader) {
+                    {
 #pragma unroll
                         for (int ks = 0; ks < 4; ks++)
-                            mma_f16_ts(tmem + kColG, a_cur + kb * 32 + ks * 8, bd + (uint64_t)(2 * ks),
+                            MMA_TS(tmem + kColG, a_cur + kb * 32 + ks * 8, bd + (uint64_t)(2 * ks),
                                        idesc_gate, (kb | ks) != 0 ? 1u : 0u);
                         mma_commit(sm.bar(B_EMPTY + slot));
-                        TL(0x58000 | (l << 8) | (j << 2) | kb);
+                        TLB(7, 0x58000 | (l << 8) | (j << 2) | kb);
                     }
-                    __syncwarp();
+                    
                 }
-                if (leader) mma_commit(sm.bar(G_FULL));
-                __syncwarp();
+                mma_commit(sm.bar(G_FULL));
+                
             }
         }
         // ---- heads: N = 48, one stage with all four K blocks
@@ -534,22 +615,23 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
             CFX_WAIT_LEADER(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
             tc_fence_after_sync();
             const uint64_t bd = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
-            if (leader) {
+            {
 #pragma unroll
                 for (int kb = 0; kb < kKBlocks; kb++)
 #pragma unroll
                     for (int ks = 0; ks < 4; ks++)
-                        mma_f16_ts(tmem + kColHead, a_cur + kb * 32 + ks * 8,
+                        MMA_TS(tmem + kColHead, a_cur + kb * 32 + ks * 8,
                                    bd + (uint64_t)((kb * kHeadStageBytes + ks * 32) >> 4), idesc_head,
                                    (kb | ks) != 0 ? 1u : 0u);
                 mma_commit(sm.bar(B_EMPTY + slot));
                 mma_commit(sm.bar(H_FULL));
-                TL(0x60000);
+                TLB(8, 0x60000);
             }
-            __syncwarp();
+            
             bcnt++;
         }
     }
+    TL_FLUSH();
 }
 
 // ------------------------------------------------------------------ worker role
@@ -570,41 +652,43 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
     TL_INIT(1 + wg);
     const bool tl_on = (quarter == 0 && lane == 0);
     for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x, it++, tcnt++) {
-        if (tl_on) TL(0x1000000);
+        if (tl_on) TLB(0, 0x1000000);
         const int env = tile * kTile + row;
         const bool valid = env < P.n;
         const bool zero_state =
             valid && P.prev_terminals != nullptr && P.prev_terminals[env] != 0.0f;
 
         // ---- expand: record bytes -> 16-bit operand rows in the TMEM chunk ring.
-        // wg 1 converts chunks 0..6, wg 0 chunks 7..13; a warp writes all 32 columns of its rows.
-        for (int kk = 0; kk < kEncChunks / 2; kk++) {
-            const int kc = wg == 1 ? kk : 7 + kk;
+        // wg 1 converts the even chunks, wg 0 the odd ones and the tail; a warp writes all 32
+        // columns of its rows.
+        for (int kc = 0; kc < kEncChunks; kc++) {
+            if ((kc < kRecFills ? rec_owner(kc) : 0) != wg) continue;
             const uint32_t acnt = it * kEncChunks + kc;
             const int as = acnt % kAexpSlots;
-            CFX_WAIT(AEXP_EMPTY + as, ((acnt / kAexpSlots) & 1) ^ 1, W_AEXP_EMPTY);
-            if (tl_on) TL(0x70000 | kc);
+            CFX_WAITW(AEXP_EMPTY + as, ((acnt / kAexpSlots) & 1) ^ 1, W_AEXP_EMPTY);
+            if (tl_on) TLB(2, 0x70000 | kc);
             tc_fence_after_sync();
             uint32_t regs[32];
             if (kc < 13) {
-                const uint32_t rcnt = it * kRecSubs + rec_pos_of(kc);
-                const int slot = rcnt % kNR;
-                CFX_WAIT(R_FULL + slot, (rcnt / kNR) & 1, W_R_FULL);
-                if (tl_on) TL(0x80000 | kc);
+                const int slot = rec_slot(kc);
+                CFX_WAITW(R_FULL + slot, rec_phase(it, kc) & 1, W_R_FULL);
+                if (tl_on) TLB(3, 0x80000 | kc);
                 const uint8_t* src = sm.r_slot(slot) + rec_row_off + ((kRec * ii) & 15);
+#ifdef CFX_ABL_NOEXPAND
+#pragma unroll
+                for (int q = 0; q < 32; q++) regs[q] = 0x3c003c00u + (uint32_t)(src - sm.base);
+#else
 #pragma unroll
                 for (int q = 0; q < 16; q++) {
                     uint32_t w32 = *reinterpret_cast<const uint32_t*>(src + 4 * q);
                     if (kc == 12 && q >= 6) w32 = 0;  // record bytes 792.. are not map bytes
                     Op::bytes4(w32, regs[2 * q], regs[2 * q + 1]);
                 }
+#endif
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sm.bar(R_EMPTY + slot));
             } else {
-                const uint32_t rcnt = it * kRecSubs + 13;  // the three tail fills sit at 13, 14, 15
-#pragma unroll
-                for (int s3 = 0; s3 < 3; s3++)
-                    CFX_WAIT(R_FULL + (rcnt + s3) % kNR, ((rcnt + s3) / kNR) & 1, W_R_FULL);
+                CFX_WAITW(T_FULL, it & 1, W_T_FULL);
                 const uint32_t rem = (kRec * ii + kMap) & 15;
 #pragma unroll
                 for (int q = 0; q < 32; q++) {
@@ -617,17 +701,15 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                             const uint32_t off = rem + 4 * f;
                             const uint32_t sidx = off / 80, within = off - sidx * 80;
                             v[e] = *reinterpret_cast<const float*>(
-                                sm.r_slot((rcnt + sidx) % kNR) + rec_row_off + within);
+                                sm.t_buf() + sidx * kRSlot + rec_row_off + within);
                         }
                     }
                     regs[q] = Op::pack(v[0], v[1]);
                 }
                 __syncwarp();
-                if (lane == 0) {
-#pragma unroll
-                    for (int s3 = 0; s3 < 3; s3++) mbar_arrive(sm.bar(R_EMPTY + (rcnt + s3) % kNR));
-                }
+                if (lane == 0) mbar_arrive(sm.bar(T_EMPTY));
             }
+            if ((kc == kLastWg1 || kc == kEncChunks - 1) && lane == 0) mbar_arrive(sm.bar(REC_DONE));
             {
                 uint32_t lo[16], hi[16];
 #pragma unroll
@@ -639,12 +721,12 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(sm.bar(AEXP_FULL + as));
-            if (tl_on) TL(0x90000 | kc);
+            if (tl_on) TLB(4, 0x90000 | kc);
         }
 
         // ---- encoder epilogue: accumulator + bias -> layer-0 input A0 (wg = unit half)
-        CFX_WAIT(ACC_FULL, tcnt & 1, W_ACC_FULL);
-        if (tl_on) TL(0xA0000);
+        CFX_WAITW(ACC_FULL, tcnt & 1, W_ACC_FULL);
+        if (tl_on) TLB(5, 0xA0000);
         tc_fence_after_sync();
 #pragma unroll 2
         for (int b = 0; b < 8; b++) {
@@ -667,6 +749,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
             mbar_arrive(sm.bar(A_KB + 2 * wg + 1));
             mbar_arrive(sm.bar(A_KB + 2 * wg + 1));
         }
+        if (tl_on) TLB(1, 0xA8000);
 
         // ---- MinGRU layers: both warpgroups work on every 64-unit slice; wg handles units
         // [64 j + 32 wg, 64 j + 32 wg + 32) = state box 2 j + wg of the layer
@@ -674,8 +757,8 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
             const uint32_t a_cur = tmem + lane_base + ((l & 1) ? kColA1 : kColA0);
             const uint32_t a_next = tmem + lane_base + ((l & 1) ? kColA0 : kColA1);
             for (int j = 0; j < kSlices; j++, gcnt++) {
-                CFX_WAIT(G_FULL, gcnt & 1, W_G_FULL);
-                if (tl_on) TL(0xB0000 | (l << 8) | j);
+                CFX_WAITW(G_FULL, gcnt & 1, W_G_FULL);
+                if (tl_on) TLB(6, 0xB0000 | (l << 8) | j);
                 tc_fence_after_sync();
                 const int box = 2 * j + wg;
                 const uint32_t scnt = (it * P.L + l) * kStateItems + box;
@@ -706,9 +789,9 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sm.bar(G_EMPTY));
-                if (tl_on) TL(0xB8000 | (l << 8) | j);
-                CFX_WAIT(S_FULL + slot, (scnt / kNS) & 1, W_S_FULL);
-                if (tl_on) TL(0xC0000 | (l << 8) | j);
+                if (tl_on) TLB(7, 0xB8000 | (l << 8) | j);
+                CFX_WAITW(S_FULL + slot, (scnt / kNS) & 1, W_S_FULL);
+                if (tl_on) TLB(8, 0xC0000 | (l << 8) | j);
 #pragma unroll
                 for (int hf = 0; hf < 2; hf++) {
                     uint32_t hn[8];
@@ -716,6 +799,12 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                     for (int q = 0; q < 4; q++) {
                         const int u = 16 * hf + 4 * q;  // first of four units
                         float4* sp = reinterpret_cast<float4*>(rbase + (((4 * hf + q) ^ xr) << 4));
+#ifdef CFX_ABL_NOCELL
+                        hn[2 * q] = zh[u] ^ zg[u + 1] ^ zp[u + 2] ^ xin[u / 2];
+                        hn[2 * q + 1] = zh[u + 3] ^ zg[u + 2] ^ zp[u] ^ xin[u / 2 + 1];
+                        if (zero_state && hn[2 * q] == 0x12345u) *sp = make_float4(0.f, 0.f, 0.f, 0.f);
+                        continue;
+#endif
                         float4 st = *sp;
                         if (zero_state) st = make_float4(0.f, 0.f, 0.f, 0.f);
                         const float2 x01 = Op::unpack(xin[u / 2]), x23 = Op::unpack(xin[u / 2 + 1]);
@@ -743,14 +832,14 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                     mbar_arrive(sm.bar(A_KB + j));
                     mbar_arrive(sm.bar(ST_READY + slot));
                 }
-                if (tl_on) TL(0xD0000 | (l << 8) | j);
+                if (tl_on) TLB(9, 0xD0000 | (l << 8) | j);
             }
         }
 
         // ---- heads + sampler (wg 0: one thread per env; wg 1 only passes the barrier so
         // that its next-tile operand writes cannot overtake the last MMA)
-        CFX_WAIT(H_FULL, tcnt & 1, W_H_FULL);
-        if (tl_on) TL(0xE0000);
+        CFX_WAITW(H_FULL, tcnt & 1, W_H_FULL);
+        if (tl_on) TLB(10, 0xE0000);
         tc_fence_after_sync();
         if (wg == 0) {
             uint32_t hv[kHeadN];
@@ -765,7 +854,11 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(sm.bar(H_EMPTY));
+#ifdef CFX_ABL_NOSAMPLER
+            if (valid && hv[0] == 0x7fc12345u) {
+#else
             if (valid) {
+#endif
                 float logits[kA];
 #pragma unroll
                 for (int a = 0; a < kA; a++) logits[a] = __uint_as_float(hv[a]) + bias[kH + a];
@@ -792,9 +885,10 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 if (P.logprobs) P.logprobs[env] = lp;
                 if (P.values) P.values[env] = value;
             }
-            if (tl_on) TL(0xF0000);
+            if (tl_on) TLB(11, 0xF0000);
         }
     }
+    if (tl_on) TL_FLUSH();
 }
 
 // ------------------------------------------------------------------ kernel
@@ -813,7 +907,7 @@ k_policy_fused(const __grid_constant__ Params P) {
         init(B_FULL, kNB, 1);
         init(B_EMPTY, kNB, 1);
         init(S_FULL, kNS, 1);
-        init(S_EMPTY, kNS, 1);
+        init(S_DONE, kNS, 1);
         init(ST_READY, kNS, 4);
         init(R_FULL, kNR, 1);
         init(R_EMPTY, kNR, 4);
@@ -825,6 +919,9 @@ k_policy_fused(const __grid_constant__ Params P) {
         init(G_EMPTY, 1, 8);
         init(H_FULL, 1, 1);
         init(H_EMPTY, 1, 4);
+        init(REC_DONE, 1, 8);
+        init(T_FULL, 1, 1);
+        init(T_EMPTY, 1, 4);
         *sm.abort_flag() = 0;
         fence_mbar_init();
     }
@@ -851,9 +948,9 @@ k_policy_fused(const __grid_constant__ Params P) {
     if (warp == 0) {
         if (lane < kWLanes) role_weight_loads(sm, P, lane);
     } else if (warp == 1) {
-        role_mma<T16>(sm, P, tmem, lane == 0);
+        if (lane == 0) role_mma<T16>(sm, P, tmem);
     } else if (warp == 2) {
-        if (lane < kNR) role_record_loads(sm, P, lane);
+        if (lane < kNR + 1) role_record_loads(sm, P, lane);
     } else if (warp == 3) {
         if (lane < kNS) role_state_ring(sm, P, lane);
     } else {
