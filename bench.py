@@ -47,7 +47,7 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples the SM clock and the clock-event (throttle) reasons of one GPU every ~2 ms
+    """Samples the SM clock and the clock-event (throttle) reasons of one GPU every ~1 ms
     with NVML (read-only queries) while the timed region runs; falls back to nvidia-smi."""
     REASONS = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20,
                "hw_thermal_slowdown": 0x40}
@@ -71,7 +71,7 @@ class ClockSampler:
                         self.bits |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
                     except Exception:
                         self.bits |= int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
-                    time.sleep(0.002)
+                    time.sleep(0.0005)
             self.thread = threading.Thread(target=loop, daemon=True)
             self.thread.start()
         except Exception as e:  # NVML missing: one nvidia-smi sample at stop()
@@ -342,7 +342,7 @@ def run_ref_cublas(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="cfx", choices=["cfx", "reference", "ref-cublas"])
     ap.add_argument("--ref-mode", default="bf16", choices=["bf16", "tf32", "fp32"])
@@ -365,7 +365,7 @@ def main():
 
 
 DEFAULT_PRECISION = "f16"
-NCU_DRAM_BYTES_PER_ENV = 378.15e6 / 65536
+NCU_DRAM_BYTES_PER_ENV = (206.87e6 + 90.29e6) / 65536   # ncu capture at 65,536 envs, see profiles/
 
 if __name__ == "__main__":
     main()
