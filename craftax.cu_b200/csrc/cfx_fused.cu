@@ -51,7 +51,18 @@ constexpr int kEncChunks = 14;   // 12 full map chunks, 1 partial (24 bytes), 1 
 constexpr int kRecFills = 13;    // record ring fills per tile: one per map chunk (the tail has its own buffer)
 constexpr int kHeadN = 48;       // 43 logits + value, padded to a multiple of 16
 
-constexpr int kBSlot = 32768, kNB = 4;
+// Weight ring: 128 KB.  One CTA per tile: 4 slots of 32 KB (a whole stage).  CTA pairs
+// (cta_group::2): 8 slots of 16 KB, every CTA stages its half of the rows of each B tile.
+constexpr int kBRingBytes = 131072, kNBMax = 8;
+template <bool PAIR> struct Cfg {
+    static constexpr int kNB = PAIR ? 8 : 4;
+    static constexpr int kBSlot = kBRingBytes / kNB;
+    static constexpr int kWLanes = kNB;                  // one lane per slot
+    static constexpr int kHeadRows = PAIR ? 64 : 48;     // N of the head MMA (pairs need N % 32 == 0)
+    static constexpr int kHeadKbBytes = (PAIR ? 32 : 48) * 128;   // one K block of the head rows a CTA stages
+    static constexpr int kM = PAIR ? 256 : 128;
+    static constexpr int kCtas = PAIR ? 2 : 1;
+};
 constexpr int kSSlot = 16384, kNS = 4;
 constexpr int kRBoxBytes = 32 * 80, kRSlot = 4 * kRBoxBytes, kNR = 4;
 constexpr int kAexpSlots = 8;
@@ -62,10 +73,11 @@ constexpr int kAexpSlots = 8;
 constexpr int kEncStageBytes = 128 * 128;            // block: [128 units][64 K] 16-bit
 constexpr int kGateStageBytes = 3 * kSliceUnits * 128;  // block: [96 rows][64 K]
 constexpr int kHeadStageBytes = kHeadN * 128;        // block: [48 rows][64 K]
+constexpr int kHeadPairBytes = 2 * kKBlocks * 32 * 128;  // pair layout: [half][K block][32 rows][64 K]
 constexpr int kEncStages = kEncChunks * 2;           // encoder blocks in the image
 constexpr int kEncCopyBytes = 2 * kEncStageBytes, kGateCopyBytes = kGateStageBytes,
               kHeadCopyBytes = kKBlocks * kHeadStageBytes;
-constexpr int kWLanes = 4, kSLanes = 4;
+constexpr int kSLanes = 4;
 // A lane that handles every G-th item of an N-slot ring waits on its slot's "empty" barrier
 // by phase parity; that is only sound while it cannot run two phases ahead of the slot,
 // i.e. while G <= N (its previous item, G back, already needed the slot use N+G back).
@@ -73,11 +85,11 @@ constexpr int kWLanes = 4, kSLanes = 4;
 // same consumer (a consumer that skips slots owned by others could otherwise be two phases
 // off): the record ring (4 slots, fills alternate between the worker warpgroups) and the
 // state ring (4 slots, slices alternate) satisfy this; each weight ring has one consumer.
-static_assert(kWLanes <= kNB && kSLanes <= kNS && kNS == 4, "ring ownership");
+static_assert(kSLanes <= kNS && kNS == 4, "ring ownership");
 
-__host__ __device__ constexpr size_t image_bytes(int L) {
+__host__ __device__ constexpr size_t image_bytes(int L) {   // room for either head layout
     return (size_t)kEncStages * kEncStageBytes + (size_t)L * kSlices * kKBlocks * kGateStageBytes +
-           (size_t)kKBlocks * kHeadStageBytes;
+           (size_t)kHeadPairBytes;
 }
 
 // TMEM columns
@@ -86,7 +98,7 @@ constexpr uint32_t kColAexp = 0, kColAcc = 256;
 
 // shared memory map (offsets from a 1024-byte aligned base)
 constexpr int kOffB = 0;
-constexpr int kOffS = kOffB + kNB * kBSlot;
+constexpr int kOffS = kOffB + kBRingBytes;
 // The record ring lives INSIDE the state slots (record slot k = the first 10 KB of state slot
 // k): records are needed only while the encoder runs, state boxes only while the gate layers
 // run.  Two per-tile hand-offs order the two uses of the memory (REC_DONE, S_DONE below).
@@ -98,7 +110,7 @@ constexpr int kTailBytes = 3 * kRSlot;
 constexpr int kOffBias = kOffT + kTailBytes;       // b_enc[256] fp32, b_av[48] fp32
 constexpr int kOffBars = kOffBias + (kH + kHeadN) * 4;
 enum Bar {
-    B_FULL = 0, B_EMPTY = B_FULL + kNB, S_FULL = B_EMPTY + kNB, S_DONE = S_FULL + kNS,
+    B_FULL = 0, B_EMPTY = B_FULL + kNBMax, S_FULL = B_EMPTY + kNBMax, S_DONE = S_FULL + kNS,
     ST_READY = S_DONE + kNS, R_FULL = ST_READY + kNS, R_EMPTY = R_FULL + kNR,
     AEXP_FULL = R_EMPTY + kNR, AEXP_EMPTY = AEXP_FULL + kAexpSlots,
     ACC_FULL = AEXP_EMPTY + kAexpSlots, A_KB = ACC_FULL + 1, G_FULL = A_KB + kKBlocks,
@@ -134,6 +146,7 @@ struct Params {
     uint32_t* status;
     uint64_t seed, env_offset;
     int n, L, num_tiles;
+    int num_tiles_loop;   // trip bound of the tile loops: num_tiles, rounded up to even for CTA pairs
     size_t off_b_enc, off_b_a, off_b_v;
     long long* timeline;  // debug builds only (CFX_TIMELINE): per-role (tag, clock) log of block 0
 };
@@ -168,7 +181,7 @@ __device__ inline __nv_bfloat16 to16<__nv_bfloat16>(float v) {
 // kernel: encoder (chunk-major, unit halves), gate layers (layer, slice, K block), head.
 template <typename T16>
 __global__ void k_pack_image(const float* __restrict__ params, uint8_t* __restrict__ image, int L,
-                             size_t off_w_gru, size_t off_w_a, size_t off_w_v) {
+                             size_t off_w_gru, size_t off_w_a, size_t off_w_v, int pair) {
     const size_t total = image_bytes(L) / 2;
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
@@ -193,13 +206,24 @@ __global__ void k_pack_image(const float* __restrict__ params, uint8_t* __restri
         const int kb = s % kKBlocks, j = (s / kKBlocks) % kSlices, l = s / (kKBlocks * kSlices);
         const int gate = row / kSliceUnits, unit = j * kSliceUnits + row % kSliceUnits;
         v = params[off_w_gru + ((size_t)l * 3 * kH + gate * kH + unit) * kH + kb * 64 + c];
-    } else {
+    } else if (!pair) {
         const size_t b = byte - enc_bytes - gate_bytes;
+        if (b >= (size_t)kKBlocks * kHeadStageBytes) return;
         const int kb = (int)(b / kHeadStageBytes), e = (int)((b % kHeadStageBytes) / 2);
         row = e / 64; c = e % 64;
         stage = image + enc_bytes + gate_bytes + (size_t)kb * kHeadStageBytes;
         if (row < kA) v = params[off_w_a + (size_t)row * kH + kb * 64 + c];
         else if (row == kA) v = params[off_w_v + kb * 64 + c];
+    } else {
+        // pair layout: CTA r of a pair stages head rows [32 r, 32 r + 32): [r][K block][32][64 K]
+        const size_t b = byte - enc_bytes - gate_bytes;
+        const int blk = (int)(b / 4096), e = (int)((b % 4096) / 2);
+        const int r = blk / kKBlocks, kb = blk % kKBlocks;
+        row = e / 64; c = e % 64;
+        stage = image + enc_bytes + gate_bytes + (size_t)blk * 4096;
+        const int grow = 32 * r + (int)row;
+        if (grow < kA) v = params[off_w_a + (size_t)grow * kH + kb * 64 + c];
+        else if (grow == kA) v = params[off_w_v + kb * 64 + c];
     }
     *reinterpret_cast<T16*>(stage + sw128_off(row, c * 2)) = to16<T16>(v);
 }
@@ -274,7 +298,7 @@ __device__ __forceinline__ void mingru_cell(float zh, float zg, float zp, float 
 struct Smem {
     uint8_t* base;
     __device__ __forceinline__ uint32_t bar(int i) const { return smem_u32(base + kOffBars + i * 8); }
-    __device__ __forceinline__ uint8_t* b_slot(int s) const { return base + kOffB + s * kBSlot; }
+    __device__ __forceinline__ uint8_t* b_ring() const { return base + kOffB; }
     __device__ __forceinline__ uint8_t* s_slot(int s) const { return base + kOffS + s * kSSlot; }
     __device__ __forceinline__ uint8_t* r_slot(int s) const { return base + kOffR + s * kRStride; }
     __device__ __forceinline__ uint8_t* t_buf() const { return base + kOffT; }
@@ -350,9 +374,13 @@ __device__ __forceinline__ T* chk_ptr(T* p, const char* what) {
 #define CFX_WAITW(barid, parity, code) CFX_WAIT(barid, parity, code)
 // The MMA role runs on ONE thread; the other lanes of its warp go straight to the exit.  (A
 // converged warp with an elected lane, one shuffle per wait and a __syncwarp per stage, was
-// 10 % slower end to end.)  It polls with test_wait: it never suspends.
-#define CFX_WAIT_LEADER(barid, parity, code) \
-    if (!mbar_wait_spin(sm.bar(barid), (parity), sm.abort_flag(), (code))) return
+// 10 % slower end to end.)  It polls with test_wait: it never suspends.  The first probe is
+// inline: almost every wait of this thread finds its barrier complete (5 failed probes in the
+// 32 weight waits of a tile), and the bounded loop costs ~150 cycles more than one probe.
+#define CFX_WAIT_LEADER(barid, parity, code)                                          \
+    if (!mbar_test_wait(sm.bar(barid), (parity)) &&                                   \
+        !mbar_wait_spin(sm.bar(barid), (parity), sm.abort_flag(), (code)))            \
+    return
 
 // Record ring schedule.  Fill kc of a tile carries map chunk kc (64 features of all 128 envs)
 // and lands in slot kc % 4.  Even chunks are expanded by worker warpgroup 1, odd chunks and
@@ -385,6 +413,7 @@ __device__ __forceinline__ void l2_prefetch_rows(const uint8_t* base, uint32_t b
     if (o < bytes) bulk_prefetch_l2(base + o, min(kL2Piece, bytes - o));
 }
 __device__ __forceinline__ void l2_prefetch_for_box(const Params& P, int tile, int l, int j) {
+    if (tile >= P.num_tiles) return;   // the filler tile of an odd pair
     if (l < P.L - 1) {
         const int rows = min(kTile, P.n - tile * kTile);
         l2_prefetch_rows(reinterpret_cast<const uint8_t*>(
@@ -401,19 +430,22 @@ __device__ __forceinline__ void l2_prefetch_for_box(const Params& P, int tile, i
 }
 
 // ------------------------------------------------------------------ producer roles
-// Weight stages: the image is laid out in consumption order, so the source pointer just
-// advances; every tile replays the same sequence (it stays L2 resident).
 // Weight stages: the image is laid out in consumption order, so stage s of a tile starts
 // where stage s-1 ended; every tile replays the same sequence (it stays L2 resident).
-// One lane per ring slot.
-__device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& P, int lane) {
+// One lane per ring slot.  In a CTA pair every CTA stages its own half of the rows of each
+// stage (the halves are contiguous in the image); the odd CTA waits for its copy to land and
+// then arrives on the even CTA's "full" barrier, where the MMA thread waits.
+template <bool PAIR>
+__device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& P, int lane,
+                                                  uint32_t rank, uint32_t bar0_cta0) {
+    using C = Cfg<PAIR>;
     const int stages_gate = P.L * kSlices * kKBlocks;
     const size_t enc_bytes = (size_t)kEncStages * kEncStageBytes;
     uint32_t cnt = 0;
     TL_INIT(3);
-    for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x) {
+    for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x) {
         for (int s = 0; s < kEncChunks + stages_gate + 1; s++, cnt++) {
-            if ((int)(cnt % kWLanes) != lane) continue;
+            if ((int)(cnt % C::kWLanes) != lane) continue;
             uint32_t bytes;
             size_t off;
             if (s < kEncChunks) {
@@ -421,17 +453,27 @@ __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& 
             } else if (s < kEncChunks + stages_gate) {
                 bytes = kGateCopyBytes; off = enc_bytes + (size_t)(s - kEncChunks) * kGateCopyBytes;
             } else {
-                bytes = kHeadCopyBytes; off = enc_bytes + (size_t)stages_gate * kGateCopyBytes;
+                bytes = PAIR ? kHeadPairBytes : kHeadCopyBytes;
+                off = enc_bytes + (size_t)stages_gate * kGateCopyBytes;
             }
-            const int slot = cnt % kNB;
-            CFX_WAIT(B_EMPTY + slot, ((cnt / kNB) & 1) ^ 1, W_B_EMPTY);
+            if (PAIR) {
+                bytes >>= 1;
+                off += (size_t)rank * bytes;
+            }
+            const int slot = cnt % C::kNB;
+            CFX_WAIT(B_EMPTY + slot, ((cnt / C::kNB) & 1) ^ 1, W_B_EMPTY);
             if (lane == 0) TLB(1, 0x10000 | s);
 #ifdef CFX_ABL_NOWEIGHTS
             mbar_arrive(sm.bar(B_FULL + slot));
 #else
             mbar_arrive_expect_tx(sm.bar(B_FULL + slot), bytes);
-            bulk_g2s(smem_u32(sm.b_slot(slot)), P.image + off, bytes, sm.bar(B_FULL + slot));
+            bulk_g2s(smem_u32(sm.b_ring() + slot * C::kBSlot), P.image + off, bytes, sm.bar(B_FULL + slot));
 #endif
+            if (PAIR && rank != 0) {
+                // local barrier (one arrival per phase here): wait for the copy, tell the even CTA
+                CFX_WAIT(B_FULL + slot, (cnt / C::kNB) & 1, W_B_FULL);
+                mbar_arrive_cluster(bar0_cta0 + 8u * (uint32_t)(B_FULL + slot));
+            }
         }
     }
 }
@@ -445,7 +487,7 @@ __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& 
     if (lane < kNR) {
         // lane `lane` owns ring slot `lane` and issues all four boxes of the fills that land on it
         const uint32_t slot_addr = smem_u32(sm.r_slot(lane));
-        for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x, it++) {
+        for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
             // first fill of the tile: the previous tile's last state box has left this slot
             CFX_WAIT(S_DONE + lane, (it & 1) ^ 1, W_S_DONE);
             for (int kc = 0; kc < kRecFills; kc++) {
@@ -466,7 +508,7 @@ __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& 
         // the tail lane: three box sets cover the 51 raw floats (204 bytes from byte 792) of
         // every record; they go to a buffer of their own, read by warpgroup 0 only
         const uint32_t dst = smem_u32(sm.t_buf());
-        for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x, it++) {
+        for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
             CFX_WAIT(T_EMPTY, (it & 1) ^ 1, W_T_EMPTY);
 #ifdef CFX_ABL_NOREC
             mbar_arrive(sm.bar(T_FULL));
@@ -492,7 +534,7 @@ __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& 
 __device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P, int lane) {
     uint32_t cnt = 0, uses = 0, it = 0;
     const uint32_t slot_addr = smem_u32(sm.s_slot(lane));
-    for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x, it++) {
+    for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
         for (int l = 0; l < P.L; l++) {
             for (int j = 0; j < kStateItems; j++, cnt++) {
                 if ((int)(cnt % kNS) != lane) continue;
@@ -531,18 +573,30 @@ __device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P,
 #ifdef CFX_ABL_NOMMA
 #define MMA_TS(...) ((void)0)
 #else
-#define MMA_TS(...) mma_f16_ts(__VA_ARGS__)
+#define MMA_TS(...)                                  \
+    do {                                             \
+        if (PAIR) mma_f16_ts_pair(__VA_ARGS__);      \
+        else mma_f16_ts(__VA_ARGS__);                \
+    } while (0)
 #endif
-template <typename T16>
+// commits: in a pair they arrive on the barrier of BOTH CTAs
+#define MMA_COMMIT(bar)                  \
+    do {                                 \
+        if (PAIR) mma_commit_pair(bar);  \
+        else mma_commit(bar);            \
+    } while (0)
+template <typename T16, bool PAIR>
 __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32_t tmem) {
+    using C = Cfg<PAIR>;
+    constexpr int kNB = C::kNB, kBSlot = C::kBSlot;
     constexpr uint32_t fmt = Op16<T16>::kFmt;
-    constexpr uint32_t idesc_enc = make_idesc(fmt, 128, kH);
-    constexpr uint32_t idesc_gate = make_idesc(fmt, 128, 3 * kSliceUnits);
-    constexpr uint32_t idesc_head = make_idesc(fmt, 128, kHeadN);
-    const uint64_t bdesc0 = smem_desc_sw128(smem_u32(sm.b_slot(0)));
+    constexpr uint32_t idesc_enc = make_idesc(fmt, C::kM, kH);
+    constexpr uint32_t idesc_gate = make_idesc(fmt, C::kM, 3 * kSliceUnits);
+    constexpr uint32_t idesc_head = make_idesc(fmt, C::kM, C::kHeadRows);
+    const uint64_t bdesc0 = smem_desc_sw128(smem_u32(sm.b_ring()));
     uint32_t bcnt = 0, acnt = 0, akb_use = 0, gcnt = 0, tcnt = 0;
     TL_INIT(0);
-    for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x, tcnt++) {
+    for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, tcnt++) {
         TLB(0, 0x1000000);
         // the encoder accumulator overlaps the head accumulator of the previous tile:
         // wait until the sampler threads have read it
@@ -553,7 +607,11 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
             const int slot = bcnt % kNB;
             CFX_WAIT_LEADER(AEXP_FULL + as, (acnt / kAexpSlots) & 1, W_AEXP_FULL);
             TLB(2, 0x20000 | kc);
+#ifdef CFX_PROFILE
+            while (!mbar_test_wait(sm.bar(B_FULL + slot), (bcnt / kNB) & 1)) pf_[10]++;
+#else
             CFX_WAIT_LEADER(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
+#endif
             TLB(3, 0x30000 | kc);
             tc_fence_after_sync();
             const uint32_t a_col = tmem + kColAexp + as * 32;
@@ -566,13 +624,13 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
                     MMA_TS(tmem + kColAcc, a_col + 16, bd + 4, idesc_enc, 1);
                     MMA_TS(tmem + kColAcc, a_col + 24, bd + 6, idesc_enc, 1);
                 }
-                mma_commit(sm.bar(B_EMPTY + slot));
-                mma_commit(sm.bar(AEXP_EMPTY + as));
+                MMA_COMMIT(sm.bar(B_EMPTY + slot));
+                MMA_COMMIT(sm.bar(AEXP_EMPTY + as));
                 TLB(4, 0x38000 | kc);
             }
             
         }
-        mma_commit(sm.bar(ACC_FULL));
+        MMA_COMMIT(sm.bar(ACC_FULL));
         
         // ---- MinGRU layers: 4 slices of 64 units, one stage per K block, N = 192 (zh|zg|zp)
         for (int l = 0; l < P.L; l++, akb_use++) {
@@ -587,7 +645,11 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
                         TLB(9, 0x48000 | (l << 8) | kb);
                     }
                     const int slot = bcnt % kNB;
+#ifdef CFX_PROFILE
+                    while (!mbar_test_wait(sm.bar(B_FULL + slot), (bcnt / kNB) & 1)) pf_[11]++;
+#else
                     CFX_WAIT_LEADER(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
+#endif
                     TLB(6, 0x50000 | (l << 8) | (j << 2) | kb);
                     tc_fence_after_sync();
                     const uint64_t bd = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
@@ -596,12 +658,12 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
                         for (int ks = 0; ks < 4; ks++)
                             MMA_TS(tmem + kColG, a_cur + kb * 32 + ks * 8, bd + (uint64_t)(2 * ks),
                                        idesc_gate, (kb | ks) != 0 ? 1u : 0u);
-                        mma_commit(sm.bar(B_EMPTY + slot));
+                        MMA_COMMIT(sm.bar(B_EMPTY + slot));
                         TLB(7, 0x58000 | (l << 8) | (j << 2) | kb);
                     }
                     
                 }
-                mma_commit(sm.bar(G_FULL));
+                MMA_COMMIT(sm.bar(G_FULL));
                 
             }
         }
@@ -621,10 +683,10 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
 #pragma unroll
                     for (int ks = 0; ks < 4; ks++)
                         MMA_TS(tmem + kColHead, a_cur + kb * 32 + ks * 8,
-                                   bd + (uint64_t)((kb * kHeadStageBytes + ks * 32) >> 4), idesc_head,
+                                   bd + (uint64_t)((kb * C::kHeadKbBytes + ks * 32) >> 4), idesc_head,
                                    (kb | ks) != 0 ? 1u : 0u);
-                mma_commit(sm.bar(B_EMPTY + slot));
-                mma_commit(sm.bar(H_FULL));
+                MMA_COMMIT(sm.bar(B_EMPTY + slot));
+                MMA_COMMIT(sm.bar(H_FULL));
                 TLB(8, 0x60000);
             }
             
@@ -637,10 +699,15 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
 // ------------------------------------------------------------------ worker role
 // Eight warps, two per TMEM lane quarter (wg 0 / wg 1); thread (quarter, lane) owns env row
 // quarter*32 + lane of the tile in every phase.
-template <typename T16>
+template <typename T16, bool PAIR>
 __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uint32_t tmem,
-                                            int warp, int lane) {
+                                            int warp, int lane, uint32_t bar0_cta0) {
     using Op = Op16<T16>;
+    // barriers the MMA thread waits on live in the even CTA of a pair
+    auto arrive_mma = [&](int barid) {
+        if (PAIR) mbar_arrive_cluster(bar0_cta0 + 8u * (uint32_t)barid);
+        else mbar_arrive(sm.bar(barid));
+    };
     const int wg = (warp - kWorkerWarp0) >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
@@ -651,7 +718,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
     uint32_t tcnt = 0, gcnt = 0, it = 0;
     TL_INIT(1 + wg);
     const bool tl_on = (quarter == 0 && lane == 0);
-    for (int tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x, it++, tcnt++) {
+    for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++, tcnt++) {
         if (tl_on) TLB(0, 0x1000000);
         const int env = tile * kTile + row;
         const bool valid = env < P.n;
@@ -720,7 +787,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
             tmem_wait_st();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(sm.bar(AEXP_FULL + as));
+            if (lane == 0) arrive_mma(AEXP_FULL + as);
             if (tl_on) TLB(4, 0x90000 | kc);
         }
 
@@ -744,10 +811,10 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
-            mbar_arrive(sm.bar(A_KB + 2 * wg));
-            mbar_arrive(sm.bar(A_KB + 2 * wg));
-            mbar_arrive(sm.bar(A_KB + 2 * wg + 1));
-            mbar_arrive(sm.bar(A_KB + 2 * wg + 1));
+            arrive_mma(A_KB + 2 * wg);
+            arrive_mma(A_KB + 2 * wg);
+            arrive_mma(A_KB + 2 * wg + 1);
+            arrive_mma(A_KB + 2 * wg + 1);
         }
         if (tl_on) TLB(1, 0xA8000);
 
@@ -788,7 +855,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 }
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(sm.bar(G_EMPTY));
+                if (lane == 0) arrive_mma(G_EMPTY);
                 if (tl_on) TLB(7, 0xB8000 | (l << 8) | j);
                 CFX_WAITW(S_FULL + slot, (scnt / kNS) & 1, W_S_FULL);
                 if (tl_on) TLB(8, 0xC0000 | (l << 8) | j);
@@ -829,7 +896,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(sm.bar(A_KB + j));
+                    arrive_mma(A_KB + j);
                     mbar_arrive(sm.bar(ST_READY + slot));
                 }
                 if (tl_on) TLB(9, 0xD0000 | (l << 8) | j);
@@ -853,7 +920,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
             tmem_wait_ld();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(sm.bar(H_EMPTY));
+            if (lane == 0) arrive_mma(H_EMPTY);
 #ifdef CFX_ABL_NOSAMPLER
             if (valid && hv[0] == 0x7fc12345u) {
 #else
@@ -892,33 +959,41 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
 }
 
 // ------------------------------------------------------------------ kernel
-template <typename T16>
+// PAIR = false: one CTA per 128-env tile.  PAIR = true: launched as clusters of two CTAs; CTA r
+// of a pair owns tile 2 c + r in every respect (records, state, expand, cell, sampler) except
+// that the MMA thread of the even CTA issues one 256-row MMA for both tiles and every CTA
+// stages only its half of the weight rows.
+template <typename T16, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 k_policy_fused(const __grid_constant__ Params P) {
+    using C = Cfg<PAIR>;
     extern __shared__ uint8_t smem_raw[];
     Smem sm;
     sm.base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+    // arrivals per phase on the barriers the MMA thread waits on: both CTAs' workers in a pair
+    const uint32_t both = (PAIR && rank == 0) ? 2u : 1u;
 
     if (tid == 0) {
         auto init = [&](int first, int count, uint32_t arrivals) {
             for (int i = 0; i < count; i++) mbar_init(sm.bar(first + i), arrivals);
         };
-        init(B_FULL, kNB, 1);
-        init(B_EMPTY, kNB, 1);
+        init(B_FULL, C::kNB, both);
+        init(B_EMPTY, C::kNB, 1);
         init(S_FULL, kNS, 1);
         init(S_DONE, kNS, 1);
         init(ST_READY, kNS, 4);
         init(R_FULL, kNR, 1);
         init(R_EMPTY, kNR, 4);
-        init(AEXP_FULL, kAexpSlots, 4);
+        init(AEXP_FULL, kAexpSlots, 4 * both);
         init(AEXP_EMPTY, kAexpSlots, 1);
         init(ACC_FULL, 1, 1);
-        init(A_KB, kKBlocks, 8);
+        init(A_KB, kKBlocks, 8 * both);
         init(G_FULL, 1, 1);
-        init(G_EMPTY, 1, 8);
+        init(G_EMPTY, 1, 8 * both);
         init(H_FULL, 1, 1);
-        init(H_EMPTY, 1, 4);
+        init(H_EMPTY, 1, 4 * both);
         init(REC_DONE, 1, 8);
         init(T_FULL, 1, 1);
         init(T_EMPTY, 1, 4);
@@ -926,8 +1001,13 @@ k_policy_fused(const __grid_constant__ Params P) {
         fence_mbar_init();
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(sm.tmem_base()), 512);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_pair(smem_u32(sm.tmem_base()), 512);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(smem_u32(sm.tmem_base()), 512);
+            tmem_relinquish();
+        }
     }
     if (warp == 3 && lane == 31) {
         prefetch_tensormap(&P.rec_map);
@@ -941,26 +1021,31 @@ k_policy_fused(const __grid_constant__ Params P) {
         sm.bias()[i] = v;
     }
     tc_fence_before_sync();
-    __syncthreads();
+    // in a pair the peer's barriers must be initialised before anybody arrives on them
+    if (PAIR) cluster_sync_all();
+    else __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *sm.tmem_base();
+    const uint32_t bar0_cta0 = PAIR ? map_to_cta(sm.bar(0), 0u) : 0u;
 
     if (warp == 0) {
-        if (lane < kWLanes) role_weight_loads(sm, P, lane);
+        if (lane < C::kWLanes) role_weight_loads<PAIR>(sm, P, lane, rank, bar0_cta0);
     } else if (warp == 1) {
-        if (lane == 0) role_mma<T16>(sm, P, tmem);
+        if (lane == 0 && rank == 0) role_mma<T16, PAIR>(sm, P, tmem);
     } else if (warp == 2) {
         if (lane < kNR + 1) role_record_loads(sm, P, lane);
     } else if (warp == 3) {
         if (lane < kNS) role_state_ring(sm, P, lane);
     } else {
-        role_worker<T16>(sm, P, tmem, warp, lane);
+        role_worker<T16, PAIR>(sm, P, tmem, warp, lane, bar0_cta0);
     }
 
-    // common exit: every role ends here, also after a timed-out wait
+    // common exit: every role ends here, also after a timed-out wait.  In a pair neither CTA
+    // may release its shared and tensor memory while the peer can still signal or read it.
     __syncwarp();
     tc_fence_before_sync();
-    __syncthreads();
+    if (PAIR) cluster_sync_all();
+    else __syncthreads();
     const uint32_t aborted = *sm.abort_flag();
     if (aborted != 0) {
         if (tid == 0) atomicCAS(P.status, 0u, aborted | ((uint32_t)blockIdx.x << 8));
@@ -968,7 +1053,10 @@ k_policy_fused(const __grid_constant__ Params P) {
         for (int i = 0; i < 64; i++) __nanosleep(1000);
         __syncthreads();
     }
-    if (warp == 1) tmem_dealloc(tmem, 512);
+    if (warp == 1) {
+        if (PAIR) tmem_dealloc_pair(tmem, 512);
+        else tmem_dealloc(tmem, 512);
+    }
 }
 
 }  // namespace fused
@@ -982,6 +1070,8 @@ struct FusedPlan {
     const float* params = nullptr;
     CUtensorMap state_map[fused::kMaxLayers];
     int sm_count = 0;
+    int pair = 0;        // 1: launch as clusters of two CTAs (cta_group::2 MMAs)
+    int max_pairs = 0;   // co-resident clusters of two
     long long* timeline = nullptr;
 };
 
@@ -1022,14 +1112,34 @@ int fused_create(FusedPlan** out, int device, int n, int H, int L, int A, int pr
             return CFX_ERR_CUDA;
         }
     }
-    e = cudaFuncSetAttribute(fused::k_policy_fused<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             fused::kSmemBytes);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(fused::k_policy_fused<__nv_bfloat16>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, fused::kSmemBytes);
+    const void* kernels[4] = {(const void*)fused::k_policy_fused<__half, false>,
+                              (const void*)fused::k_policy_fused<__nv_bfloat16, false>,
+                              (const void*)fused::k_policy_fused<__half, true>,
+                              (const void*)fused::k_policy_fused<__nv_bfloat16, true>};
+    for (int k = 0; k < 4 && e == cudaSuccess; k++)
+        e = cudaFuncSetAttribute(kernels[k], cudaFuncAttributeMaxDynamicSharedMemorySize, fused::kSmemBytes);
     if (e != cudaSuccess) {
         fused_destroy(p);
         return cuda_fail(e, "cudaFuncSetAttribute", __FILE__, __LINE__);
+    }
+    // CTA pairs are opt-in (CFX_FUSED_PAIR=1); they need two co-resident CTAs per cluster
+    const char* pe = getenv("CFX_FUSED_PAIR");
+    if (pe != nullptr && atoi(pe) != 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * (unsigned)(p->sm_count / 2));
+        cfg.blockDim = dim3(fused::kThreads);
+        cfg.dynamicSmemBytes = fused::kSmemBytes;
+        cudaLaunchAttribute at;
+        at.id = cudaLaunchAttributeClusterDimension;
+        at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+        cfg.attrs = &at; cfg.numAttrs = 1;
+        int nc = 0;
+        if (cudaOccupancyMaxActiveClusters(&nc, kernels[precision == CFX_PREC_F16 ? 2 : 3], &cfg) == cudaSuccess && nc > 0) {
+            p->pair = 1;
+            p->max_pairs = nc;
+        } else {
+            cudaGetLastError();
+        }
     }
     *out = p;
     return CFX_OK;
@@ -1041,9 +1151,9 @@ int fused_refresh(FusedPlan* p, const float* params, cudaStream_t st) {
     const size_t total = fused::image_bytes(p->L) / 2;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (p->precision == CFX_PREC_F16)
-        fused::k_pack_image<__half><<<blocks, 256, 0, st>>>(params, p->image, p->L, o.w_gru, o.w_a, o.w_v);
+        fused::k_pack_image<__half><<<blocks, 256, 0, st>>>(params, p->image, p->L, o.w_gru, o.w_a, o.w_v, p->pair);
     else
-        fused::k_pack_image<__nv_bfloat16><<<blocks, 256, 0, st>>>(params, p->image, p->L, o.w_gru, o.w_a, o.w_v);
+        fused::k_pack_image<__nv_bfloat16><<<blocks, 256, 0, st>>>(params, p->image, p->L, o.w_gru, o.w_a, o.w_v, p->pair);
     CFX_CUDA(cudaGetLastError());
     return CFX_OK;
 }
@@ -1088,11 +1198,30 @@ int fused_forward(FusedPlan* p, const FusedArgs& a, cudaStream_t st, int* launch
     P.off_b_a = o.b_a;
     P.off_b_v = o.b_v;
     P.timeline = p->timeline;
-    const int grid = P.num_tiles < p->sm_count ? P.num_tiles : p->sm_count;
-    if (p->precision == CFX_PREC_F16)
-        fused::k_policy_fused<__half><<<grid, fused::kThreads, fused::kSmemBytes, st>>>(P);
-    else
-        fused::k_policy_fused<__nv_bfloat16><<<grid, fused::kThreads, fused::kSmemBytes, st>>>(P);
+    if (p->pair) {
+        const int pairs = (P.num_tiles + 1) / 2;
+        P.num_tiles_loop = 2 * pairs;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2u * (unsigned)(pairs < p->max_pairs ? pairs : p->max_pairs));
+        cfg.blockDim = dim3(fused::kThreads);
+        cfg.dynamicSmemBytes = fused::kSmemBytes;
+        cfg.stream = st;
+        cudaLaunchAttribute at;
+        at.id = cudaLaunchAttributeClusterDimension;
+        at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+        cfg.attrs = &at; cfg.numAttrs = 1;
+        if (p->precision == CFX_PREC_F16)
+            CFX_CUDA(cudaLaunchKernelEx(&cfg, fused::k_policy_fused<__half, true>, P));
+        else
+            CFX_CUDA(cudaLaunchKernelEx(&cfg, fused::k_policy_fused<__nv_bfloat16, true>, P));
+    } else {
+        P.num_tiles_loop = P.num_tiles;
+        const int grid = P.num_tiles < p->sm_count ? P.num_tiles : p->sm_count;
+        if (p->precision == CFX_PREC_F16)
+            fused::k_policy_fused<__half, false><<<grid, fused::kThreads, fused::kSmemBytes, st>>>(P);
+        else
+            fused::k_policy_fused<__nv_bfloat16, false><<<grid, fused::kThreads, fused::kSmemBytes, st>>>(P);
+    }
     CFX_CUDA(cudaGetLastError());
     if (launches) *launches = 1;
     return CFX_OK;
