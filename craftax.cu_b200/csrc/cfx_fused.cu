@@ -51,20 +51,18 @@ constexpr int kEncChunks = 14;   // 12 full map chunks, 1 partial (24 bytes), 1 
 constexpr int kRecFills = 13;    // record ring fills per tile: one per map chunk (the tail has its own buffer)
 constexpr int kHeadN = 48;       // 43 logits + value, padded to a multiple of 16
 
-// Weight ring: 128 KB.  One CTA per tile: 4 slots of 32 KB (a whole stage).  CTA pairs
-// (cta_group::2): 8 slots of 16 KB, every CTA stages its half of the rows of each B tile.
-constexpr int kBRingBytes = 131072, kNBMax = 8;
-template <bool PAIR> struct Cfg {
-    static constexpr int kNB = PAIR ? 8 : 4;
-    static constexpr int kBSlot = kBRingBytes / kNB;
-    static constexpr int kWLanes = kNB;                  // one lane per slot
-    static constexpr int kHeadRows = PAIR ? 64 : 48;     // N of the head MMA (pairs need N % 32 == 0)
-    static constexpr int kHeadKbBytes = (PAIR ? 32 : 48) * 128;   // one K block of the head rows a CTA stages
-    static constexpr int kM = PAIR ? 256 : 128;
-    static constexpr int kCtas = PAIR ? 2 : 1;
-};
+constexpr int kNBMax = 8;        // weight ring slots (one stage each): see Cfg
+#ifndef CFX_PAIR_NB
+#define CFX_PAIR_NB 8
+#endif
+#ifndef CFX_PAIR_ALIAS
+#define CFX_PAIR_ALIAS 1
+#endif
+#ifndef CFX_PAIR_NR
+#define CFX_PAIR_NR 4
+#endif
 constexpr int kSSlot = 16384, kNS = 4;
-constexpr int kRBoxBytes = 32 * 80, kRSlot = 4 * kRBoxBytes, kNR = 4;
+constexpr int kRBoxBytes = 32 * 80, kRSlot = 4 * kRBoxBytes, kNRMax = 6;
 constexpr int kAexpSlots = 8;
 
 // Image blocks (one K block of 64 columns each) and the ring stages that carry them:
@@ -96,29 +94,45 @@ __host__ __device__ constexpr size_t image_bytes(int L) {   // room for either h
 constexpr uint32_t kColA0 = 0, kColA1 = 128, kColG = 256, kColHead = 448;
 constexpr uint32_t kColAexp = 0, kColAcc = 256;
 
-// shared memory map (offsets from a 1024-byte aligned base)
-constexpr int kOffB = 0;
-constexpr int kOffS = kOffB + kBRingBytes;
-// The record ring lives INSIDE the state slots (record slot k = the first 10 KB of state slot
-// k): records are needed only while the encoder runs, state boxes only while the gate layers
-// run.  Two per-tile hand-offs order the two uses of the memory (REC_DONE, S_DONE below).
-constexpr int kOffR = kOffS, kRStride = kSSlot;   // record slot k = the first 10 KB of state slot k
-static_assert(kNR * kRSlot <= kNS * kSSlot && kStateItems == 2 * kNS,
-              "the record slots lie inside the state slots; a state lane's last box per tile is fixed");
-constexpr int kOffT = kOffS + kNS * kSSlot;        // the 204 tail bytes of every record: 3 box sets
-constexpr int kTailBytes = 3 * kRSlot;
-constexpr int kOffBias = kOffT + kTailBytes;       // b_enc[256] fp32, b_av[48] fp32
-constexpr int kOffBars = kOffBias + (kH + kHeadN) * 4;
+constexpr int kTailBytes = 3 * kRSlot;   // the 204 tail bytes of every record: 3 box sets
 enum Bar {
     B_FULL = 0, B_EMPTY = B_FULL + kNBMax, S_FULL = B_EMPTY + kNBMax, S_DONE = S_FULL + kNS,
-    ST_READY = S_DONE + kNS, R_FULL = ST_READY + kNS, R_EMPTY = R_FULL + kNR,
-    AEXP_FULL = R_EMPTY + kNR, AEXP_EMPTY = AEXP_FULL + kAexpSlots,
+    ST_READY = S_DONE + kNS, R_FULL = ST_READY + kNS, R_EMPTY = R_FULL + kNRMax,
+    AEXP_FULL = R_EMPTY + kNRMax, AEXP_EMPTY = AEXP_FULL + kAexpSlots,
     ACC_FULL = AEXP_EMPTY + kAexpSlots, A_KB = ACC_FULL + 1, G_FULL = A_KB + kKBlocks,
     G_EMPTY = G_FULL + 1, H_FULL = G_EMPTY + 1, H_EMPTY = H_FULL + 1, REC_DONE = H_EMPTY + 1,
     T_FULL = REC_DONE + 1, T_EMPTY = T_FULL + 1, NUM_BARS = T_EMPTY + 1
 };
-constexpr int kOffMisc = kOffBars + NUM_BARS * 8;  // tmem base, abort flag
-constexpr int kSmemBytes = kOffMisc + 16 + 1024;   // + alignment slack
+
+// Shared memory map (offsets from a 1024-byte aligned base) and the shapes that depend on the
+// launch mode.
+//  one CTA per tile: weight ring 4 x 32 KB (whole stages); the record ring (4 x 10 KB) lives
+//    INSIDE the state slots (records are needed only while the encoder runs, state boxes only
+//    while the gate layers run; REC_DONE and S_DONE order the two uses per tile);
+//  CTA pair (cta_group::2): every CTA stages half of each weight stage, 4 x 16 KB; the 64 KB
+//    this frees hold a record ring of its own, 6 x 10 KB, that runs ahead into the next tile.
+template <bool PAIR> struct Cfg {
+    static constexpr int kNB = PAIR ? CFX_PAIR_NB : 4;
+    static constexpr int kBSlot = PAIR ? 16384 : 32768;
+    static constexpr int kWLanes = kNB;                  // one lane per slot
+    static constexpr int kHeadRows = PAIR ? 64 : 48;     // N of the head MMA (pairs need N % 32 == 0)
+    static constexpr int kHeadKbBytes = (PAIR ? 32 : 48) * 128;   // one K block of the head rows a CTA stages
+    static constexpr int kM = PAIR ? 256 : 128;
+    static constexpr bool kAlias = PAIR ? (CFX_PAIR_ALIAS != 0) : true;
+    static constexpr int kNR = PAIR ? CFX_PAIR_NR : 4;
+    static constexpr int kRStride = kAlias ? kSSlot : kRSlot;
+    static constexpr int kOffB = 0;
+    static constexpr int kOffS = kOffB + kNB * kBSlot;
+    static constexpr int kOffR = kAlias ? kOffS : kOffS + kNS * kSSlot;
+    static constexpr int kOffT = kAlias ? kOffS + kNS * kSSlot : kOffR + kNR * kRSlot;
+    static constexpr int kOffBias = kOffT + kTailBytes;       // b_enc[256] fp32, b_av[48] fp32
+    static constexpr int kOffBars = kOffBias + (kH + kHeadN) * 4;
+    static constexpr int kOffMisc = kOffBars + NUM_BARS * 8;  // tmem base, abort flag
+    static constexpr int kSmemBytes = kOffMisc + 16 + 1024;   // + alignment slack
+    static_assert(kNB <= kNBMax && kNR <= kNRMax && kNR * kRSlot <= kNS * kSSlot && kSmemBytes <= 232448 &&
+                      (!kAlias || kNR == kNS), "layout");
+};
+static_assert(kStateItems == 2 * kNS, "a state lane's last box per tile is fixed");
 
 constexpr int kWorkerWarp0 = 4, kNumWarps = 12, kThreads = kNumWarps * 32;
 
@@ -297,15 +311,21 @@ __device__ __forceinline__ void mingru_cell(float zh, float zg, float zp, float 
 
 struct Smem {
     uint8_t* base;
-    __device__ __forceinline__ uint32_t bar(int i) const { return smem_u32(base + kOffBars + i * 8); }
-    __device__ __forceinline__ uint8_t* b_ring() const { return base + kOffB; }
-    __device__ __forceinline__ uint8_t* s_slot(int s) const { return base + kOffS + s * kSSlot; }
-    __device__ __forceinline__ uint8_t* r_slot(int s) const { return base + kOffR + s * kRStride; }
-    __device__ __forceinline__ uint8_t* t_buf() const { return base + kOffT; }
-    __device__ __forceinline__ float* bias() const { return reinterpret_cast<float*>(base + kOffBias); }
-    __device__ __forceinline__ uint32_t* tmem_base() const { return reinterpret_cast<uint32_t*>(base + kOffMisc); }
+    int off_s, off_r, r_stride, off_t, off_bias, off_bars, off_misc, b_slot_bytes;
+    template <bool PAIR> __device__ __forceinline__ void layout() {
+        using C = Cfg<PAIR>;
+        off_s = C::kOffS; off_r = C::kOffR; r_stride = C::kRStride; off_t = C::kOffT;
+        off_bias = C::kOffBias; off_bars = C::kOffBars; off_misc = C::kOffMisc; b_slot_bytes = C::kBSlot;
+    }
+    __device__ __forceinline__ uint32_t bar(int i) const { return smem_u32(base + off_bars + i * 8); }
+    __device__ __forceinline__ uint8_t* b_ring() const { return base; }
+    __device__ __forceinline__ uint8_t* s_slot(int s) const { return base + off_s + s * kSSlot; }
+    __device__ __forceinline__ uint8_t* r_slot(int s) const { return base + off_r + s * r_stride; }
+    __device__ __forceinline__ uint8_t* t_buf() const { return base + off_t; }
+    __device__ __forceinline__ float* bias() const { return reinterpret_cast<float*>(base + off_bias); }
+    __device__ __forceinline__ uint32_t* tmem_base() const { return reinterpret_cast<uint32_t*>(base + off_misc); }
     __device__ __forceinline__ volatile uint32_t* abort_flag() const {
-        return reinterpret_cast<volatile uint32_t*>(base + kOffMisc + 4);
+        return reinterpret_cast<volatile uint32_t*>(base + off_misc + 4);
     }
 };
 
@@ -383,20 +403,21 @@ __device__ __forceinline__ T* chk_ptr(T* p, const char* what) {
     return
 
 // Record ring schedule.  Fill kc of a tile carries map chunk kc (64 features of all 128 envs)
-// and lands in slot kc % 4.  Even chunks are expanded by worker warpgroup 1, odd chunks and
-// the tail by warpgroup 0, so even slots belong to wg 1 and odd slots to wg 0 for the whole
-// launch.  That is what makes the phase-parity waits sound: a waiter may be at most one phase
-// ahead of its barrier, and the warpgroup that waits for a fill has itself consumed the
-// previous fill of the same slot.  (A schedule in which the other warpgroup consumed a slot's
-// next fill raised a launch failure: it passed its wait two phases early and arrived on the
-// slot's "empty" barrier out of turn.)  Slot 0 takes four fills per tile, the others three.
+// and lands in slot kc % NR (NR = 4 or 6).  Even chunks are expanded by worker warpgroup 1, odd
+// chunks and the tail by warpgroup 0, so even slots belong to wg 1 and odd slots to wg 0 for
+// the whole launch.  That is what makes the phase-parity waits sound: a waiter may be at most
+// one phase ahead of its barrier, and the warpgroup that waits for a fill has itself consumed
+// the previous fill of the same slot.  (A schedule in which the other warpgroup consumed a
+// slot's next fill raised a launch failure: it passed its wait two phases early and arrived on
+// the slot's "empty" barrier out of turn.)  Slot 0 takes one fill per tile more than the others.
 __device__ __forceinline__ int rec_owner(int kc) { return (kc & 1) ^ 1; }
-__device__ __forceinline__ int rec_slot(int kc) { return kc & (kNR - 1); }
-__device__ __forceinline__ uint32_t rec_phase(uint32_t it, int kc) {   // phase index of fill kc
-    return ((kc & (kNR - 1)) == 0 ? 4u : 3u) * it + (uint32_t)(kc >> 2);
+template <int NR> __device__ __forceinline__ int rec_slot(int kc) { return kc % NR; }
+template <int NR> __device__ __forceinline__ uint32_t rec_phase(uint32_t it, int kc) {   // phase index of fill kc
+    constexpr uint32_t fills0 = (kRecFills + NR - 1) / NR, fills = kRecFills / NR;
+    static_assert(NR % 2 == 0 && fills0 == fills + 1 && kRecFills % NR == 1, "slot 0 takes the odd fill");
+    return ((kc % NR) == 0 ? fills0 : fills) * it + (uint32_t)(kc / NR);
 }
 constexpr int kLastWg1 = 12;
-static_assert(kNR == 4 && kRecFills == 13, "schedule above");
 
 // Software prefetch into L2.  The rings are far too small to cover HBM latency at the rate the
 // encoder and the cell consume, so every byte a ring will load is requested from HBM ahead of
@@ -482,17 +503,20 @@ __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& 
 // aligned row); env 4g+i of a tile sits in row g at byte 996 i.  A 64-byte feature chunk of
 // all 128 envs is fetched as four boxes (one per i) of 32 rows x 80 bytes starting at the
 // 16-byte boundary below 996 i + 64 c; the 204 tail bytes take three more such box sets.
+template <bool PAIR>
 __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& P, int lane) {
+    using C = Cfg<PAIR>;
+    constexpr int kNR = C::kNR;
     uint32_t it = 0;
     if (lane < kNR) {
         // lane `lane` owns ring slot `lane` and issues all four boxes of the fills that land on it
         const uint32_t slot_addr = smem_u32(sm.r_slot(lane));
         for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
-            // first fill of the tile: the previous tile's last state box has left this slot
-            CFX_WAIT(S_DONE + lane, (it & 1) ^ 1, W_S_DONE);
-            for (int kc = 0; kc < kRecFills; kc++) {
-                if (rec_slot(kc) != lane) continue;
-                CFX_WAIT(R_EMPTY + lane, (rec_phase(it, kc) & 1) ^ 1, W_R_EMPTY);
+            // ring inside the state slots: before the first fill of the tile the previous
+            // tile's last state box must have left this slot
+            if (C::kAlias) CFX_WAIT(S_DONE + lane, (it & 1) ^ 1, W_S_DONE);
+            for (int kc = lane; kc < kRecFills; kc += kNR) {
+                CFX_WAIT(R_EMPTY + lane, (rec_phase<kNR>(it, kc) & 1) ^ 1, W_R_EMPTY);
 #ifdef CFX_ABL_NOREC
                 mbar_arrive(sm.bar(R_FULL + lane));
                 continue;
@@ -531,7 +555,9 @@ __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& 
 // replaced the contents with the new state, write it back (rows beyond n are clipped by the
 // tensor map), and only then load the next box into the slot.  One lane per slot needs no
 // "slot empty" barrier and saves a hand-off.
+template <bool PAIR>
 __device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P, int lane) {
+    using C = Cfg<PAIR>;
     uint32_t cnt = 0, uses = 0, it = 0;
     const uint32_t slot_addr = smem_u32(sm.s_slot(lane));
     for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
@@ -539,7 +565,7 @@ __device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P,
             for (int j = 0; j < kStateItems; j++, cnt++) {
                 if ((int)(cnt % kNS) != lane) continue;
                 // first box of the tile: every record of the tile has been expanded
-                if (l == 0 && j == lane) CFX_WAIT(REC_DONE, it & 1, W_REC_DONE);
+                if (C::kAlias && l == 0 && j == lane) CFX_WAIT(REC_DONE, it & 1, W_REC_DONE);
 #ifdef CFX_ABL_NOSTATE
                 mbar_arrive(sm.bar(S_FULL + lane));
                 CFX_WAIT(ST_READY + lane, uses & 1, W_ST_READY);
@@ -557,7 +583,7 @@ __device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P,
                 bulk_commit_group();
                 bulk_wait_group_read<0>();
 #endif
-                if (l == P.L - 1 && j == lane + kNS) mbar_arrive(sm.bar(S_DONE + lane));
+                if (C::kAlias && l == P.L - 1 && j == lane + kNS) mbar_arrive(sm.bar(S_DONE + lane));
             }
         }
     }
@@ -737,8 +763,8 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
             tc_fence_after_sync();
             uint32_t regs[32];
             if (kc < 13) {
-                const int slot = rec_slot(kc);
-                CFX_WAITW(R_FULL + slot, rec_phase(it, kc) & 1, W_R_FULL);
+                const int slot = rec_slot<Cfg<PAIR>::kNR>(kc);
+                CFX_WAITW(R_FULL + slot, rec_phase<Cfg<PAIR>::kNR>(it, kc) & 1, W_R_FULL);
                 if (tl_on) TLB(3, 0x80000 | kc);
                 const uint8_t* src = sm.r_slot(slot) + rec_row_off + ((kRec * ii) & 15);
 #ifdef CFX_ABL_NOEXPAND
@@ -776,7 +802,8 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sm.bar(T_EMPTY));
             }
-            if ((kc == kLastWg1 || kc == kEncChunks - 1) && lane == 0) mbar_arrive(sm.bar(REC_DONE));
+            if (Cfg<PAIR>::kAlias && (kc == kLastWg1 || kc == kEncChunks - 1) && lane == 0)
+                mbar_arrive(sm.bar(REC_DONE));
             {
                 uint32_t lo[16], hi[16];
 #pragma unroll
@@ -970,6 +997,7 @@ k_policy_fused(const __grid_constant__ Params P) {
     extern __shared__ uint8_t smem_raw[];
     Smem sm;
     sm.base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    sm.layout<PAIR>();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
     // arrivals per phase on the barriers the MMA thread waits on: both CTAs' workers in a pair
@@ -984,8 +1012,8 @@ k_policy_fused(const __grid_constant__ Params P) {
         init(S_FULL, kNS, 1);
         init(S_DONE, kNS, 1);
         init(ST_READY, kNS, 4);
-        init(R_FULL, kNR, 1);
-        init(R_EMPTY, kNR, 4);
+        init(R_FULL, C::kNR, 1);
+        init(R_EMPTY, C::kNR, 4);
         init(AEXP_FULL, kAexpSlots, 4 * both);
         init(AEXP_EMPTY, kAexpSlots, 1);
         init(ACC_FULL, 1, 1);
@@ -1033,9 +1061,9 @@ k_policy_fused(const __grid_constant__ Params P) {
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) role_mma<T16, PAIR>(sm, P, tmem);
     } else if (warp == 2) {
-        if (lane < kNR + 1) role_record_loads(sm, P, lane);
+        if (lane < C::kNR + 1) role_record_loads<PAIR>(sm, P, lane);
     } else if (warp == 3) {
-        if (lane < kNS) role_state_ring(sm, P, lane);
+        if (lane < kNS) role_state_ring<PAIR>(sm, P, lane);
     } else {
         role_worker<T16, PAIR>(sm, P, tmem, warp, lane, bar0_cta0);
     }
@@ -1117,18 +1145,20 @@ int fused_create(FusedPlan** out, int device, int n, int H, int L, int A, int pr
                               (const void*)fused::k_policy_fused<__half, true>,
                               (const void*)fused::k_policy_fused<__nv_bfloat16, true>};
     for (int k = 0; k < 4 && e == cudaSuccess; k++)
-        e = cudaFuncSetAttribute(kernels[k], cudaFuncAttributeMaxDynamicSharedMemorySize, fused::kSmemBytes);
+        e = cudaFuncSetAttribute(kernels[k], cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 k < 2 ? fused::Cfg<false>::kSmemBytes : fused::Cfg<true>::kSmemBytes);
     if (e != cudaSuccess) {
         fused_destroy(p);
         return cuda_fail(e, "cudaFuncSetAttribute", __FILE__, __LINE__);
     }
-    // CTA pairs are opt-in (CFX_FUSED_PAIR=1); they need two co-resident CTAs per cluster
+    // CTA pairs are the default (CFX_FUSED_PAIR=0 selects one CTA per tile); they need two
+    // co-resident CTAs per cluster, otherwise the single-CTA kernel is used
     const char* pe = getenv("CFX_FUSED_PAIR");
-    if (pe != nullptr && atoi(pe) != 0) {
+    if (pe == nullptr || atoi(pe) != 0) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * (unsigned)(p->sm_count / 2));
         cfg.blockDim = dim3(fused::kThreads);
-        cfg.dynamicSmemBytes = fused::kSmemBytes;
+        cfg.dynamicSmemBytes = fused::Cfg<true>::kSmemBytes;
         cudaLaunchAttribute at;
         at.id = cudaLaunchAttributeClusterDimension;
         at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
@@ -1204,7 +1234,7 @@ int fused_forward(FusedPlan* p, const FusedArgs& a, cudaStream_t st, int* launch
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2u * (unsigned)(pairs < p->max_pairs ? pairs : p->max_pairs));
         cfg.blockDim = dim3(fused::kThreads);
-        cfg.dynamicSmemBytes = fused::kSmemBytes;
+        cfg.dynamicSmemBytes = fused::Cfg<true>::kSmemBytes;
         cfg.stream = st;
         cudaLaunchAttribute at;
         at.id = cudaLaunchAttributeClusterDimension;
@@ -1218,9 +1248,9 @@ int fused_forward(FusedPlan* p, const FusedArgs& a, cudaStream_t st, int* launch
         P.num_tiles_loop = P.num_tiles;
         const int grid = P.num_tiles < p->sm_count ? P.num_tiles : p->sm_count;
         if (p->precision == CFX_PREC_F16)
-            fused::k_policy_fused<__half, false><<<grid, fused::kThreads, fused::kSmemBytes, st>>>(P);
+            fused::k_policy_fused<__half, false><<<grid, fused::kThreads, fused::Cfg<false>::kSmemBytes, st>>>(P);
         else
-            fused::k_policy_fused<__nv_bfloat16, false><<<grid, fused::kThreads, fused::kSmemBytes, st>>>(P);
+            fused::k_policy_fused<__nv_bfloat16, false><<<grid, fused::kThreads, fused::Cfg<false>::kSmemBytes, st>>>(P);
     }
     CFX_CUDA(cudaGetLastError());
     if (launches) *launches = 1;

@@ -139,3 +139,26 @@ def test_fused_rejects_what_it_cannot_do(cfx, gpu, oracle):
     d = pol.forward_host(rec, None, None)
     assert np.isfinite(d["logits_av"]).all()
     pol.close()
+
+
+@pytest.mark.parametrize("n,layers", [(64, 2), (128 * 7, 2), (128 * 300 + 96, 3)])
+def test_fused_single_cta_mode_equals_pair_mode(cfx, gpu, oracle, monkeypatch, n, layers):
+    """The kernel runs as clusters of two CTAs (one 256-row MMA per pair) by default and as one
+    CTA per tile with CFX_FUSED_PAIR=0 (read when the policy is created).  Both modes issue the
+    same products in the same order for every row, so they must agree bit for bit; odd tile
+    counts exercise the filler tile of the last pair."""
+    rng = np.random.default_rng(n)
+    base = oracle.synthetic_records(min(n, 4096), seed=9)
+    rec = base[rng.integers(0, base.shape[0], n)]
+    params = oracle.init_weights(H, layers, A, seed=3)
+    state = rng.normal(0, 1, (layers, n, H)).astype(np.float32)
+    prev_t = (rng.random(n) < 0.1).astype(np.float32)
+    out = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("CFX_FUSED_PAIR", mode)
+        out[mode] = _run(cfx, n, layers, "f16", params, rec, prev_t, None, state, seed=11)
+    (d1, st1, _), (d0, st0, _) = out["1"], out["0"]
+    assert np.array_equal(d1["logits_av"], d0["logits_av"])
+    assert np.array_equal(st1, st0)
+    assert np.array_equal(d1["actions"], d0["actions"])
+    assert np.array_equal(d1["logprobs"], d0["logprobs"])
