@@ -339,12 +339,50 @@ def run_ref_cublas(args):
     ref.close()
 
 
+def run_ref_rollout(args):
+    """Whole rollouts on one B200: the reference's own `run` loop (env kernels + its cuBLAS
+    policy, graph replay), its env kernels alone, and the same loop with the policy half
+    swapped for this library's forward (the drop-in binding of INTEGRATION.md).  The three
+    ratios of the target sentence are printed: R1 forward-only vs forward-only comes from
+    `--impl cfx` and `--impl ref-cublas`; R2 = this library's forward-only env-steps/s over the
+    reference's full-rollout SPS; R3 = swapped rollout over reference rollout."""
+    rank, _, local = dist_env()
+    if rank != 0:
+        return
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import ctypes as C
+    import cfx
+    import oracle as O
+    n, L = args.envs, args.layers
+    if cfx.device_count() < 1 or args.hidden != 256 or not O.RefCuda.available(L):
+        print(json.dumps({"impl": "ref-rollout", "unavailable":
+                          f"needs a GPU and oracle/_ref/libcfref_cuda_l{L}.so (reference sources absent)"}))
+        return
+    cfx.lib()   # libcfx.so first: the reference shim links against it
+    lib = C.CDLL(O.RefCuda.path(L))
+    for f in ("refcu_rollout_sps", "refcu_env_only_sps"):
+        getattr(lib, f).restype = C.c_double
+        getattr(lib, f).argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_int]
+    iters = max(20, args.steps)
+    out = {"impl": "ref-rollout", "unit": "env-steps/s", "envs": n, "layers": L, "iters": iters,
+           "reference_rollout": lib.refcu_rollout_sps(n, iters, 1, 1),
+           "reference_env_only": lib.refcu_env_only_sps(n, iters, 1, 1)}
+    if hasattr(lib, "refcu_rollout_swap_sps"):
+        lib.refcu_rollout_swap_sps.restype = C.c_double
+        lib.refcu_rollout_swap_sps.argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_int, C.c_int]
+        prec = {"f16": cfx.PREC_F16, "bf16": cfx.PREC_BF16, "fp32": cfx.PREC_FP32}[args.precision or DEFAULT_PRECISION]
+        out["swapped_rollout"] = lib.refcu_rollout_swap_sps(n, iters, 1, 1, prec)
+        out["R3_swapped_over_reference"] = out["swapped_rollout"] / out["reference_rollout"]
+        out["amdahl_cap_env_only_over_reference"] = out["reference_env_only"] / out["reference_rollout"]
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="cfx", choices=["cfx", "reference", "ref-cublas"])
+    ap.add_argument("--impl", default="cfx", choices=["cfx", "reference", "ref-cublas", "ref-rollout"])
     ap.add_argument("--ref-mode", default="bf16", choices=["bf16", "tf32", "fp32"])
     ap.add_argument("--envs", type=int, default=262144, help="envs per GPU")
     ap.add_argument("--hidden", type=int, default=256)
@@ -360,6 +398,8 @@ def main():
         run_reference(args)
     elif args.impl == "ref-cublas":
         run_ref_cublas(args)
+    elif args.impl == "ref-rollout":
+        run_ref_rollout(args)
     else:
         run_cfx(args)
 

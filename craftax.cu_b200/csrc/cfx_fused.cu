@@ -53,15 +53,18 @@ constexpr int kHeadN = 48;       // 43 logits + value, padded to a multiple of 1
 
 constexpr int kNBMax = 8;        // weight ring slots (one stage each): see Cfg
 #ifndef CFX_PAIR_NB
-#define CFX_PAIR_NB 8
+#define CFX_PAIR_NB 6
+#endif
+#ifndef CFX_PAIR_NS
+#define CFX_PAIR_NS 6
 #endif
 #ifndef CFX_PAIR_ALIAS
 #define CFX_PAIR_ALIAS 1
 #endif
 #ifndef CFX_PAIR_NR
-#define CFX_PAIR_NR 4
+#define CFX_PAIR_NR 6
 #endif
-constexpr int kSSlot = 16384, kNS = 4;
+constexpr int kSSlot = 16384, kNSMax = 6;
 constexpr int kRBoxBytes = 32 * 80, kRSlot = 4 * kRBoxBytes, kNRMax = 6;
 constexpr int kAexpSlots = 8;
 
@@ -75,7 +78,7 @@ constexpr int kHeadPairBytes = 2 * kKBlocks * 32 * 128;  // pair layout: [half][
 constexpr int kEncStages = kEncChunks * 2;           // encoder blocks in the image
 constexpr int kEncCopyBytes = 2 * kEncStageBytes, kGateCopyBytes = kGateStageBytes,
               kHeadCopyBytes = kKBlocks * kHeadStageBytes;
-constexpr int kSLanes = 4;
+
 // A lane that handles every G-th item of an N-slot ring waits on its slot's "empty" barrier
 // by phase parity; that is only sound while it cannot run two phases ahead of the slot,
 // i.e. while G <= N (its previous item, G back, already needed the slot use N+G back).
@@ -83,7 +86,7 @@ constexpr int kSLanes = 4;
 // same consumer (a consumer that skips slots owned by others could otherwise be two phases
 // off): the record ring (4 slots, fills alternate between the worker warpgroups) and the
 // state ring (4 slots, slices alternate) satisfy this; each weight ring has one consumer.
-static_assert(kSLanes <= kNS && kNS == 4, "ring ownership");
+
 
 __host__ __device__ constexpr size_t image_bytes(int L) {   // room for either head layout
     return (size_t)kEncStages * kEncStageBytes + (size_t)L * kSlices * kKBlocks * kGateStageBytes +
@@ -96,8 +99,8 @@ constexpr uint32_t kColAexp = 0, kColAcc = 256;
 
 constexpr int kTailBytes = 3 * kRSlot;   // the 204 tail bytes of every record: 3 box sets
 enum Bar {
-    B_FULL = 0, B_EMPTY = B_FULL + kNBMax, S_FULL = B_EMPTY + kNBMax, S_DONE = S_FULL + kNS,
-    ST_READY = S_DONE + kNS, R_FULL = ST_READY + kNS, R_EMPTY = R_FULL + kNRMax,
+    B_FULL = 0, B_EMPTY = B_FULL + kNBMax, S_FULL = B_EMPTY + kNBMax, S_DONE = S_FULL + kNSMax,
+    ST_READY = S_DONE + kNSMax, R_FULL = ST_READY + kNSMax, R_EMPTY = R_FULL + kNRMax,
     AEXP_FULL = R_EMPTY + kNRMax, AEXP_EMPTY = AEXP_FULL + kAexpSlots,
     ACC_FULL = AEXP_EMPTY + kAexpSlots, A_KB = ACC_FULL + 1, G_FULL = A_KB + kKBlocks,
     G_EMPTY = G_FULL + 1, H_FULL = G_EMPTY + 1, H_EMPTY = H_FULL + 1, REC_DONE = H_EMPTY + 1,
@@ -118,6 +121,7 @@ template <bool PAIR> struct Cfg {
     static constexpr int kHeadRows = PAIR ? 64 : 48;     // N of the head MMA (pairs need N % 32 == 0)
     static constexpr int kHeadKbBytes = (PAIR ? 32 : 48) * 128;   // one K block of the head rows a CTA stages
     static constexpr int kM = PAIR ? 256 : 128;
+    static constexpr int kNS = PAIR ? CFX_PAIR_NS : 4;     // state ring slots: even, so that slot parity = warpgroup
     static constexpr bool kAlias = PAIR ? (CFX_PAIR_ALIAS != 0) : true;
     static constexpr int kNR = PAIR ? CFX_PAIR_NR : 4;
     static constexpr int kRStride = kAlias ? kSSlot : kRSlot;
@@ -129,10 +133,9 @@ template <bool PAIR> struct Cfg {
     static constexpr int kOffBars = kOffBias + (kH + kHeadN) * 4;
     static constexpr int kOffMisc = kOffBars + NUM_BARS * 8;  // tmem base, abort flag
     static constexpr int kSmemBytes = kOffMisc + 16 + 1024;   // + alignment slack
-    static_assert(kNB <= kNBMax && kNR <= kNRMax && kNR * kRSlot <= kNS * kSSlot && kSmemBytes <= 232448 &&
-                      (!kAlias || kNR == kNS), "layout");
+    static_assert(kNB <= kNBMax && kNR <= kNRMax && kNS <= kNSMax && kNS % 2 == 0 && kNS <= kStateItems &&
+                      kNR * kRSlot <= kNS * kSSlot && kSmemBytes <= 232448 && (!kAlias || kNR == kNS), "layout");
 };
-static_assert(kStateItems == 2 * kNS, "a state lane's last box per tile is fixed");
 
 constexpr int kWorkerWarp0 = 4, kNumWarps = 12, kThreads = kNumWarps * 32;
 
@@ -558,14 +561,17 @@ __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& 
 template <bool PAIR>
 __device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P, int lane) {
     using C = Cfg<PAIR>;
+    constexpr int kNS = C::kNS;
     uint32_t cnt = 0, uses = 0, it = 0;
     const uint32_t slot_addr = smem_u32(sm.s_slot(lane));
     for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
         for (int l = 0; l < P.L; l++) {
             for (int j = 0; j < kStateItems; j++, cnt++) {
                 if ((int)(cnt % kNS) != lane) continue;
-                // first box of the tile: every record of the tile has been expanded
-                if (C::kAlias && l == 0 && j == lane) CFX_WAIT(REC_DONE, it & 1, W_REC_DONE);
+                // this lane's first box of the tile (every slot gets at least one box per tile):
+                // every record of the tile has been expanded
+                const int b = l * kStateItems + j;
+                if (C::kAlias && b < kNS) CFX_WAIT(REC_DONE, it & 1, W_REC_DONE);
 #ifdef CFX_ABL_NOSTATE
                 mbar_arrive(sm.bar(S_FULL + lane));
                 CFX_WAIT(ST_READY + lane, uses & 1, W_ST_READY);
@@ -583,7 +589,8 @@ __device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P,
                 bulk_commit_group();
                 bulk_wait_group_read<0>();
 #endif
-                if (C::kAlias && l == P.L - 1 && j == lane + kNS) mbar_arrive(sm.bar(S_DONE + lane));
+                // this lane's last box of the tile has left the slot: records may come in
+                if (C::kAlias && b >= P.L * kStateItems - kNS) mbar_arrive(sm.bar(S_DONE + lane));
             }
         }
     }
@@ -856,6 +863,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 tc_fence_after_sync();
                 const int box = 2 * j + wg;
                 const uint32_t scnt = (it * P.L + l) * kStateItems + box;
+                constexpr int kNS = Cfg<PAIR>::kNS;
                 const int slot = scnt % kNS;
                 const uint32_t gcol = tmem + lane_base + kColG + kHalfUnits * wg;
                 uint8_t* rbase = sm.s_slot(slot) + (row >> 3) * 1024 + (row & 7) * 128;
@@ -1009,9 +1017,9 @@ k_policy_fused(const __grid_constant__ Params P) {
         };
         init(B_FULL, C::kNB, both);
         init(B_EMPTY, C::kNB, 1);
-        init(S_FULL, kNS, 1);
-        init(S_DONE, kNS, 1);
-        init(ST_READY, kNS, 4);
+        init(S_FULL, C::kNS, 1);
+        init(S_DONE, C::kNS, 1);
+        init(ST_READY, C::kNS, 4);
         init(R_FULL, C::kNR, 1);
         init(R_EMPTY, C::kNR, 4);
         init(AEXP_FULL, kAexpSlots, 4 * both);
@@ -1063,7 +1071,7 @@ k_policy_fused(const __grid_constant__ Params P) {
     } else if (warp == 2) {
         if (lane < C::kNR + 1) role_record_loads<PAIR>(sm, P, lane);
     } else if (warp == 3) {
-        if (lane < kNS) role_state_ring<PAIR>(sm, P, lane);
+        if (lane < C::kNS) role_state_ring<PAIR>(sm, P, lane);
     } else {
         role_worker<T16, PAIR>(sm, P, tmem, warp, lane, bar0_cta0);
     }

@@ -259,4 +259,143 @@ void refcu_scalar_forward(void* h, const uint8_t* d_rec, const float* d_prev_ter
     if (values) CU_CHECK(cudaMemcpy(values, p->d_value, n * sizeof(float), cudaMemcpyDeviceToHost));
 }
 
+/* ---- whole rollouts on the GPU (reference env kernels + a policy forward) ----
+ * refcu_rollout_sps: the reference's own `run` loop (cu_rollout_step_plain, :12089) with its
+ *   default GEMM mode (bf16 at >= 4096 envs on sm_100, :11325), CUDA-graph replay as in
+ *   cu_run_rollout_bench (:12127); returns env-steps per second measured with CUDA events.
+ * refcu_env_only_sps: env kernels only (what remains of a step when the policy costs nothing).
+ * refcu_rollout_swap_sps (built with -DCFX_REF_WITH_CFX): the same loop with the policy half of
+ *   cu_rollout_step (:12022-12050: expand, encoder GEMM, bias, GRU chain, head GEMM, sampler)
+ *   replaced by one cfx_policy_forward call - the binding a maintainer would add. */
+static double refcu_time_steps(CuPolicy* p, int n, int iters, int graph, void (*step)(void*), void* ctx) {
+    int warm = iters / 20 > 10 ? 10 : (iters / 20 > 0 ? iters / 20 : 1);
+    for (int k = 0; k < warm; k++) step(ctx);
+    CU_CHECK(cudaStreamSynchronize(p->stream));
+    cudaGraph_t g = NULL;
+    cudaGraphExec_t ge = NULL;
+    if (graph) {
+        CU_CHECK(cudaStreamBeginCapture(p->stream, cudaStreamCaptureModeGlobal));
+        step(ctx);
+        CU_CHECK(cudaStreamEndCapture(p->stream, &g));
+        if (cudaGraphInstantiate(&ge, g, NULL, NULL, 0) != cudaSuccess) { cudaGetLastError(); ge = NULL; }
+    }
+    cudaEvent_t a, b;
+    CU_CHECK(cudaEventCreate(&a));
+    CU_CHECK(cudaEventCreate(&b));
+    CU_CHECK(cudaEventRecord(a, p->stream));
+    for (int k = 0; k < iters; k++) {
+        if (ge) CU_CHECK(cudaGraphLaunch(ge, p->stream));
+        else step(ctx);
+    }
+    CU_CHECK(cudaEventRecord(b, p->stream));
+    CU_CHECK(cudaStreamSynchronize(p->stream));
+    float ms = 0.f;
+    CU_CHECK(cudaEventElapsedTime(&ms, a, b));
+    cudaEventDestroy(a); cudaEventDestroy(b);
+    if (ge) cudaGraphExecDestroy(ge);
+    if (g) cudaGraphDestroy(g);
+    return (double)n * (double)iters / ((double)ms * 1e-3);
+}
+
+typedef struct { CuVec* v; CuPolicy* p; uint64_t seed; void* cfx; } refcu_roll;
+
+static void refcu_step_reference(void* c) {
+    refcu_roll* r = (refcu_roll*)c;
+    cu_rollout_step_plain(r->v, r->p, r->seed);
+}
+
+static void refcu_step_env_only(void* c) {
+    refcu_roll* r = (refcu_roll*)c;
+    CuVec* v = r->v; CuPolicy* p = r->p;
+    int n = v->num_envs;
+    cudaStream_t st = p->stream;
+    CU_CHECK(cudaMemsetAsync(v->d_reset_count, 0, sizeof(int), st));
+    CU_CHECK(cudaMemsetAsync(v->d_spawn_count, 0, sizeof(int), st));
+    cu_launch_step_run(v->d_envs, n, v->d_resets, NULL, st);
+    int tail_blocks = (n * 32 + 255) / 256;
+    if (tail_blocks > 512) tail_blocks = 512;
+    k_spawn_tail<<<tail_blocks, 256, 0, st>>>();
+    if (v->lazy) cu_launch_reset_list_warp(v->d_envs, v->d_resets, n, st);
+    else k_reset_list<<<(n + 63) / 64, 64, 0, st>>>(v->d_envs, v->d_resets);
+    CU_CHECK(cudaGetLastError());
+}
+
+double refcu_rollout_sps(int n, int iters, unsigned long long seed, int graph) {
+    CuVec v; CuPolicy p;
+    cu_vec_init(&v, n, seed);
+    cu_policy_init(&p, n);
+    refcu_roll r = {&v, &p, seed, NULL};
+    double sps = refcu_time_steps(&p, n, iters, graph, refcu_step_reference, &r);
+    cu_policy_free(&p);
+    cu_vec_free(&v);
+    return sps;
+}
+
+double refcu_env_only_sps(int n, int iters, unsigned long long seed, int graph) {
+    CuVec v; CuPolicy p;
+    cu_vec_init(&v, n, seed);
+    cu_policy_init(&p, n);
+    CU_CHECK(cudaMemset(v.d_actions, 0, (size_t)n * sizeof(float)));   /* every env plays action 0 */
+    refcu_roll r = {&v, &p, seed, NULL};
+    double sps = refcu_time_steps(&p, n, iters, graph, refcu_step_env_only, &r);
+    cu_policy_free(&p);
+    cu_vec_free(&v);
+    return sps;
+}
+
+#ifdef CFX_REF_WITH_CFX
+#include "cfx.h"
+static void refcu_step_swapped(void* c) {
+    refcu_roll* r = (refcu_roll*)c;
+    CuVec* v = r->v; CuPolicy* p = r->p;
+    int n = v->num_envs;
+    cudaStream_t st = p->stream;
+    k_record_obs<<<(int)(((size_t)n * 32 + 255) / 256), 256, 0, st>>>(p->rec, n);
+    CU_CHECK(cudaMemsetAsync(v->d_reset_count, 0, sizeof(int), st));
+    CU_CHECK(cudaMemsetAsync(v->d_spawn_count, 0, sizeof(int), st));
+    cfx_forward_io io;
+    memset(&io, 0, sizeof(io));
+    io.records = p->rec;
+    io.prev_terminals = v->d_terminals;
+    io.env_actions = v->d_actions;
+    io.actions = p->d_act; io.logprobs = p->d_logprob; io.values = p->d_value;
+    io.seed = r->seed;
+    io.bump_step = 1;
+    if (cfx_policy_forward((cfx_policy*)r->cfx, &io, st) != CFX_OK) {
+        fprintf(stderr, "cfx: %s\n", cfx_last_error());
+        exit(1);
+    }
+    cu_launch_step_run(v->d_envs, n, v->d_resets, NULL, st);
+    int tail_blocks = (n * 32 + 255) / 256;
+    if (tail_blocks > 512) tail_blocks = 512;
+    k_spawn_tail<<<tail_blocks, 256, 0, st>>>();
+    if (v->lazy) cu_launch_reset_list_warp(v->d_envs, v->d_resets, n, st);
+    else k_reset_list<<<(n + 63) / 64, 64, 0, st>>>(v->d_envs, v->d_resets);
+    CU_CHECK(cudaGetLastError());
+}
+
+/* precision: a CFX_PREC_* code.  The reference policy is created too (its init allocates the
+ * record scratch and the sampler outputs the loop writes); its weights are handed over. */
+double refcu_rollout_swap_sps(int n, int iters, unsigned long long seed, int graph, int precision) {
+    CuVec v; CuPolicy p;
+    cu_vec_init(&v, n, seed);
+    cu_policy_init(&p, n);
+    int dev = 0;
+    CU_CHECK(cudaGetDevice(&dev));
+    cfx_policy* cp = NULL;
+    if (cfx_policy_create(&cp, dev, n, CF_NN_HIDDEN, CF_NN_LAYERS, CRAFTAX_NUM_ACTIONS, precision) != CFX_OK ||
+        cfx_policy_set_weights(cp, p.params, CF_NN_PARAM_COUNT, 1) != CFX_OK) {
+        fprintf(stderr, "cfx: %s\n", cfx_last_error());
+        exit(1);
+    }
+    CU_CHECK(cudaDeviceSynchronize());
+    refcu_roll r = {&v, &p, seed, cp};
+    double sps = refcu_time_steps(&p, n, iters, graph, refcu_step_swapped, &r);
+    cfx_policy_destroy(cp);
+    cu_policy_free(&p);
+    cu_vec_free(&v);
+    return sps;
+}
+#endif
+
 } /* extern "C" */
