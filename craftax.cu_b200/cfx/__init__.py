@@ -16,6 +16,7 @@ PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.environ.get("CFX_LIB") or os.path.join(PKG, "libcfx.so")
 
 OBS, MAP, TAIL, REC = 843, 792, 51, 996
+CLASSIC_OBS, CLASSIC_REC = 1345, 148
 PREC_FP32, PREC_F16, PREC_BF16, PREC_TF32 = 0, 1, 2, 3
 PREC_NAMES = {"fp32": 0, "f16": 1, "bf16": 2, "tf32": 3}
 
@@ -57,6 +58,10 @@ _SIGS = {
     "cfx_policy_check": (C.c_int, [C.c_void_p, C.c_void_p]),
     "cfx_strict_forward_static": (C.c_int, [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                             C.c_void_p, C.POINTER(ForwardIO), C.c_void_p, C.c_void_p]),
+    "cfx_classic_param_count": (C.c_size_t, [C.c_int] * 3),
+    "cfx_policy_create_classic": (C.c_int, [C.POINTER(C.c_void_p)] + [C.c_int] * 5),
+    "cfx_classic_expand_obs": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "cfx_classic_done_to_terminals": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "cfx_expand_obs": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "cfx_sample_actions": (C.c_int, [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int,
                                      C.c_void_p, C.c_void_p, C.c_void_p]),
@@ -221,11 +226,17 @@ class Policy:
     """Mirror of the reference's CuPolicy for one GPU: weights, recurrent state,
     step counter, and the batched forward."""
 
-    def __init__(self, n, hidden=256, layers=2, actions=43, precision="fp32", device=0):
+    def __init__(self, n, hidden=256, layers=2, actions=43, precision="fp32", device=0, game="full"):
         self.n, self.H, self.L, self.A, self.device = n, hidden, layers, actions, device
+        self.game = game
+        self.rec_bytes = CLASSIC_REC if game == "classic" else REC
         prec = PREC_NAMES[precision] if isinstance(precision, str) else int(precision)
         h = C.c_void_p()
-        check(lib().cfx_policy_create(C.byref(h), device, n, hidden, layers, actions, prec))
+        if game == "classic":     # 148-byte records, gather encoder; fp32 only
+            assert prec == PREC_FP32, "the classic game is built for precision fp32 only"
+            check(lib().cfx_policy_create_classic(C.byref(h), device, n, hidden, layers, actions))
+        else:
+            check(lib().cfx_policy_create(C.byref(h), device, n, hidden, layers, actions, prec))
         self.h = h.value
         self.stream = lib().cfx_policy_stream(self.h)
         self._out = None
@@ -233,7 +244,8 @@ class Policy:
     # -- weights ---------------------------------------------------------
     @property
     def param_count(self):
-        return int(lib().cfx_param_count(self.H, self.L, self.A))
+        f = lib().cfx_classic_param_count if self.game == "classic" else lib().cfx_param_count
+        return int(f(self.H, self.L, self.A))
 
     def set_weights(self, arena):
         a = np.ascontiguousarray(arena, np.float32)
@@ -315,7 +327,7 @@ class Policy:
         arrays.  `out` may hold preallocated (pinned) arrays to reuse."""
         n, A = self.n, self.A
         rec = np.ascontiguousarray(records, np.uint8)
-        assert rec.size == n * REC
+        assert rec.size == n * self.rec_bytes
         o = out if out is not None else {}
         o.setdefault("env_actions", np.empty(n, np.float32))
         o.setdefault("actions", np.empty(n, np.int32))
@@ -355,6 +367,24 @@ def expand_obs(records, device=0):
     d_rec = DeviceBuffer.from_host(rec, device)
     d_out = DeviceBuffer((n, OBS), np.float32, device)
     check(lib().cfx_expand_obs(device, d_rec.ptr, d_out.ptr, n, None))
+    return d_out.download()
+
+
+def classic_expand_obs(records, device=0):
+    """classic records uint8 [n][148] (host) -> fp32 features [n][1345] via the device kernel."""
+    rec = np.ascontiguousarray(records, np.uint8).reshape(-1, CLASSIC_REC)
+    n = rec.shape[0]
+    d_rec = DeviceBuffer.from_host(rec, device)
+    d_out = DeviceBuffer((n, CLASSIC_OBS), np.float32, device)
+    check(lib().cfx_classic_expand_obs(device, d_rec.ptr, d_out.ptr, n, None))
+    return d_out.download()
+
+
+def classic_done_to_terminals(done, device=0):
+    d = np.ascontiguousarray(done, np.int8)
+    d_in = DeviceBuffer.from_host(d, device)
+    d_out = DeviceBuffer((d.size,), np.float32, device)
+    check(lib().cfx_classic_done_to_terminals(device, d_in.ptr, d_out.ptr, d.size, None))
     return d_out.download()
 
 

@@ -71,3 +71,48 @@ def synthetic_records(n, seed=4):
     t[:, 49:51] = rng.integers(0, 2, (n, 2))
     rec[:, MAP:] = t.view(np.uint8).reshape(n, TAIL * 4)
     return rec
+
+
+# ---- classic game (148-byte records, 1345 features; reference craftax_classic.cu:38-59) ----
+CLASSIC_OBS, CLASSIC_REC, CLASSIC_CELLS = 1345, 148, 63
+
+
+def classic_offsets(H, L, A):
+    o = {"w_enc": 0, "b_enc": CLASSIC_OBS * H}
+    o["w_gru"] = o["b_enc"] + H
+    o["w_a"] = o["w_gru"] + L * 3 * H * H
+    o["b_a"] = o["w_a"] + A * H
+    o["w_v"] = o["b_a"] + A
+    o["b_v"] = o["w_v"] + H
+    o["count"] = o["b_v"] + 1
+    return o
+
+
+def classic_init_weights(H=256, L=3, A=17, seed=0):
+    """N(0, 1/fan_in) weights; biases drawn too (small) so that every arena segment matters."""
+    rng = np.random.default_rng(seed)
+    o = classic_offsets(H, L, A)
+    p = np.empty(o["count"], np.float32)
+    p[:o["b_enc"]] = rng.normal(0, 1 / np.sqrt(85.0), CLASSIC_OBS * H)     # ~85 active features per record
+    p[o["b_enc"]:o["w_gru"]] = rng.normal(0, 0.05, H)
+    p[o["w_gru"]:o["w_a"]] = rng.normal(0, 1 / np.sqrt(H), L * 3 * H * H)
+    p[o["w_a"]:o["b_a"]] = rng.normal(0, 1 / np.sqrt(H), A * H)
+    p[o["b_a"]:o["w_v"]] = rng.normal(0, 0.05, A)
+    p[o["w_v"]:o["b_v"]] = rng.normal(0, 1 / np.sqrt(H), H)
+    p[o["b_v"]] = 0.1
+    return p
+
+
+def classic_synthetic_records(n, seed=0):
+    """Seeded records over the valid ranges of the classic layout: block ids 0..16, mob masks
+    with each of the four bits set with probability 0.05, inventory and intrinsics 0..9,
+    direction 1..4, sleeping 0/1, light in [0, 1] as raw fp32."""
+    rng = np.random.default_rng(seed)
+    rec = np.zeros((n, CLASSIC_REC), np.uint8)
+    rec[:, :63] = rng.integers(0, 17, (n, 63))
+    rec[:, 63:126] = (rng.random((n, 63, 4)) < 0.05).astype(np.uint8) @ np.array([1, 2, 4, 8], np.uint8)
+    rec[:, 126:142] = rng.integers(0, 10, (n, 16))
+    rec[:, 142] = rng.integers(1, 5, n)
+    rec[:, 143] = rng.integers(0, 2, n)
+    rec[:, 144:148] = rng.random(n, dtype=np.float32).reshape(n, 1).view(np.uint8)
+    return rec

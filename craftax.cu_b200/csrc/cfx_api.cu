@@ -32,6 +32,7 @@ using namespace cfx;
 struct cfx_policy {
     int device = 0;
     int n = 0, H = 0, L = 0, A = 0;
+    int game = CFX_GAME_FULL, obs = kObs, rec_bytes = kRec;
     int precision = CFX_PREC_FP32;
     size_t param_count = 0;
     float* params = nullptr;        // fp32 arena (device)
@@ -60,7 +61,7 @@ static void free_dev(void* p) {
 }
 
 static int policy_refresh_mirrors(cfx_policy* p, cudaStream_t st) {
-    const ArenaLayout o = ArenaLayout::make(p->H, p->L, p->A);
+    const ArenaLayout o = ArenaLayout::make(p->H, p->L, p->A, p->obs);
     int rc = launch_transpose_gates(p->params + o.w_gru, p->gates_t, p->H, p->L, st);
     if (rc) return rc;
     if (p->fused) {
@@ -72,7 +73,7 @@ static int policy_refresh_mirrors(cfx_policy* p, cudaStream_t st) {
 
 static int policy_ensure_fused(cfx_policy* p) {
     if (p->precision == CFX_PREC_FP32) return CFX_OK;
-    if (!fused_supported(p->H, p->L, p->A, p->precision)) {
+    if (p->game != CFX_GAME_FULL || !fused_supported(p->H, p->L, p->A, p->precision)) {
         set_error("precision %d is not built for hidden=%d layers=%d actions=%d", p->precision,
                   p->H, p->L, p->A);
         return CFX_ERR_UNSUPPORTED;
@@ -94,8 +95,39 @@ size_t cfx_param_count(int hidden, int layers, int num_actions) {
     return ArenaLayout::make(hidden, layers, num_actions).count;
 }
 
+static int policy_create(cfx_policy** out, int device, int num_envs, int hidden, int layers,
+                         int num_actions, int precision, int game);
+
 int cfx_policy_create(cfx_policy** out, int device, int num_envs, int hidden, int layers,
                       int num_actions, int precision) {
+    return policy_create(out, device, num_envs, hidden, layers, num_actions, precision, CFX_GAME_FULL);
+}
+
+int cfx_policy_create_classic(cfx_policy** out, int device, int num_envs, int hidden, int layers,
+                              int num_actions) {
+    return policy_create(out, device, num_envs, hidden, layers, num_actions, CFX_PREC_FP32,
+                         CFX_GAME_CLASSIC);
+}
+
+size_t cfx_classic_param_count(int hidden, int layers, int num_actions) {
+    if (hidden <= 0 || layers <= 0 || num_actions <= 0) return 0;
+    return ArenaLayout::make(hidden, layers, num_actions, kClassicObs).count;
+}
+
+int cfx_classic_expand_obs(int device, const uint8_t* records, float* out, int num_envs, void* stream) {
+    CFX_REQUIRE(records && out && num_envs > 0, "cfx_classic_expand_obs: bad arguments");
+    DeviceGuard g(device);
+    return launch_classic_expand(records, out, num_envs, (cudaStream_t)stream);
+}
+
+int cfx_classic_done_to_terminals(int device, const int8_t* done, float* out, int num_envs, void* stream) {
+    CFX_REQUIRE(done && out && num_envs > 0, "cfx_classic_done_to_terminals: bad arguments");
+    DeviceGuard g(device);
+    return launch_done_to_terminals(done, out, num_envs, (cudaStream_t)stream);
+}
+
+static int policy_create(cfx_policy** out, int device, int num_envs, int hidden, int layers,
+                         int num_actions, int precision, int game) {
     CFX_REQUIRE(out != nullptr, "cfx_policy_create: out is NULL");
     *out = nullptr;
     CFX_REQUIRE(num_envs > 0 && num_envs % 32 == 0,
@@ -119,7 +151,10 @@ int cfx_policy_create(cfx_policy** out, int device, int num_envs, int hidden, in
     p->L = layers;
     p->A = num_actions;
     p->precision = precision;
-    p->param_count = ArenaLayout::make(hidden, layers, num_actions).count;
+    p->game = game;
+    p->obs = game == CFX_GAME_CLASSIC ? kClassicObs : kObs;
+    p->rec_bytes = game == CFX_GAME_CLASSIC ? kClassicRec : kRec;
+    p->param_count = ArenaLayout::make(hidden, layers, num_actions, p->obs).count;
     const size_t hn = (size_t)hidden * num_envs;
     int rc = CFX_OK;
     auto fail = [&](int code) {
@@ -209,10 +244,10 @@ int cfx_policy_get_weights(cfx_policy* p, float* host_arena, size_t count) {
 int cfx_policy_init_weights(cfx_policy* p, uint64_t seed) {
     CFX_REQUIRE(p, "cfx_policy_init_weights: NULL handle");
     DeviceGuard g(p->device);
-    const ArenaLayout o = ArenaLayout::make(p->H, p->L, p->A);
-    const float be = 1.0f / sqrtf((float)kObs), bh = 1.0f / sqrtf((float)p->H);
+    const ArenaLayout o = ArenaLayout::make(p->H, p->L, p->A, p->obs);
+    const float be = 1.0f / sqrtf((float)p->obs), bh = 1.0f / sqrtf((float)p->H);
     const struct { size_t off; size_t count; float bound; } segs[7] = {
-        {o.w_enc, (size_t)kObs * p->H, be}, {o.b_enc, (size_t)p->H, be},
+        {o.w_enc, (size_t)p->obs * p->H, be}, {o.b_enc, (size_t)p->H, be},
         {o.w_gru, (size_t)p->L * 3 * p->H * p->H, bh}, {o.w_a, (size_t)p->A * p->H, bh},
         {o.b_a, (size_t)p->A, bh}, {o.w_v, (size_t)p->H, bh}, {o.b_v, 1, bh}};
     for (int s = 0; s < 7; s++) {
@@ -372,6 +407,7 @@ int cfx_policy_forward(cfx_policy* p, const cfx_forward_io* io, void* stream) {
     if (p->precision == CFX_PREC_FP32) {
         StrictArgs a;
         a.n = p->n; a.H = p->H; a.L = p->L; a.A = p->A;
+        a.game = p->game;
         a.params = p->params;
         a.gates_t = p->gates_t;
         a.records = io->records;
@@ -455,7 +491,7 @@ int cfx_policy_forward_host(cfx_policy* p, const cfx_forward_io* h) {
     const size_t n = (size_t)p->n;
     const size_t lav = n * (size_t)(p->A + 1), rs = (size_t)p->L * n * p->H;
     int rc;
-    if ((rc = ensure_staging(&p->st_records, n * kRec))) return rc;
+    if ((rc = ensure_staging(&p->st_records, n * (size_t)p->rec_bytes))) return rc;
     if ((rc = ensure_staging(&p->st_actions, n))) return rc;
     if (h->prev_terminals && (rc = ensure_staging(&p->st_terminals, n))) return rc;
     if (h->uniforms && (rc = ensure_staging(&p->st_uniforms, n))) return rc;
@@ -465,7 +501,7 @@ int cfx_policy_forward_host(cfx_policy* p, const cfx_forward_io* h) {
     if (h->logits_av && (rc = ensure_staging(&p->st_logits, lav))) return rc;
     if (h->r_state && (rc = ensure_staging(&p->st_r_state, rs))) return rc;
 
-    CFX_CUDA(cudaMemcpyAsync(p->st_records, h->records, n * kRec, cudaMemcpyHostToDevice, st));
+    CFX_CUDA(cudaMemcpyAsync(p->st_records, h->records, n * (size_t)p->rec_bytes, cudaMemcpyHostToDevice, st));
     if (h->prev_terminals)
         CFX_CUDA(cudaMemcpyAsync(p->st_terminals, h->prev_terminals, n * sizeof(float),
                                  cudaMemcpyHostToDevice, st));

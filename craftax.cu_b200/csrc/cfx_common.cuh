@@ -14,14 +14,17 @@ constexpr int kMap = CFX_OBS_MAP;        // 792 one-byte map features
 constexpr int kTail = CFX_OBS_TAIL;      // 51 raw fp32 tail features
 constexpr int kRec = CFX_RECORD_BYTES;   // 996-byte record
 constexpr int kMaxActions = 63;
+// classic game (reference craftax_classic.cu:38-59): 148-byte record, 1345 features
+constexpr int kClassicRec = CFX_CLASSIC_RECORD_BYTES, kClassicObs = CFX_CLASSIC_OBS_FEATURES;
+constexpr int kClassicCells = 63, kClassicBlocks = 17, kClassicInv = 12;
 
 // Arena offsets in floats (reference order, craftax_full.cu:9094-9102).
 struct ArenaLayout {
     size_t w_enc, b_enc, w_gru, w_a, b_a, w_v, b_v, count;
-    __host__ __device__ static ArenaLayout make(int H, int L, int A) {
+    __host__ __device__ static ArenaLayout make(int H, int L, int A, int obs = kObs) {
         ArenaLayout o;
         o.w_enc = 0;
-        o.b_enc = (size_t)kObs * H;
+        o.b_enc = (size_t)obs * H;
         o.w_gru = o.b_enc + H;
         o.w_a = o.w_gru + (size_t)L * 3 * H * H;
         o.b_a = o.w_a + (size_t)A * H;

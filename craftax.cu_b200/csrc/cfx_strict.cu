@@ -77,6 +77,76 @@ __global__ void k_encoder_fp32(const uint8_t* __restrict__ rec, const float* __r
         if (e0 + e < n) h_out[(size_t)(e0 + e) * H + k] = acc[e];
 }
 
+// ---------------------------------------------------------------- classic game
+// Record -> 1345 features, reference expand_obs_kernel (craftax_classic.cu:1265-1301).
+__global__ void k_classic_expand(const uint8_t* __restrict__ rec, float* __restrict__ out, int n) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n) return;
+    const uint8_t* c = rec + (size_t)e * kClassicRec;
+    float* o = out + (size_t)e * kClassicObs;
+    int k = 0;
+    for (int cell = 0; cell < kClassicCells; cell++) {
+        const int8_t blk = (int8_t)c[cell];
+        for (int b = 0; b < kClassicBlocks; b++) o[k++] = (blk == b) ? 1.0f : 0.0f;
+        const uint8_t m = c[kClassicCells + cell];
+        for (int j = 0; j < 4; j++) o[k++] = (m & (1 << j)) ? 1.0f : 0.0f;
+    }
+    int i2 = 2 * kClassicCells;
+    for (int j = 0; j < kClassicInv + 4; j++) o[k++] = (float)(int8_t)c[i2++] / 10.0f;
+    const int8_t dir = (int8_t)c[i2++];
+    for (int d = 1; d <= 4; d++) o[k++] = (dir == d) ? 1.0f : 0.0f;
+    const uint8_t sleeping = c[i2++];
+    float light;
+    memcpy(&light, c + i2, 4);
+    o[k++] = light;
+    o[k++] = sleeping ? 1.0f : 0.0f;
+}
+
+// Gather encoder in the order of the reference's encode_obs_kernel (craftax_classic.cu:1714-1751):
+// bias, then per cell the block column and the set mob bits, then the 22 scalar features, every
+// term as fmaf(x, W, acc).  One thread per (env, unit); the block's threads read a W_enc row
+// coalesced.  Block ids outside [0,16] (never written by the game) are skipped.
+__global__ void k_classic_encoder_fp32(const uint8_t* __restrict__ rec, const float* __restrict__ W_enc,
+                                       const float* __restrict__ b_enc, float* __restrict__ h_out,
+                                       int n, int H) {
+    __shared__ uint8_t rs[kClassicRec];
+    const int e = blockIdx.x;
+    const int k = threadIdx.x;
+    for (int i = threadIdx.x; i < kClassicRec; i += blockDim.x) rs[i] = rec[(size_t)e * kClassicRec + i];
+    __syncthreads();
+    const float* Wk = W_enc + k;
+    float hv = b_enc[k];
+    for (int cell = 0; cell < kClassicCells; cell++) {
+        const int blk = (int8_t)rs[cell];
+        if (blk >= 0 && blk < kClassicBlocks)
+            hv = fmaf(1.0f, Wk[(size_t)(cell * (kClassicBlocks + 4) + blk) * H], hv);
+        const uint8_t m = rs[kClassicCells + cell];
+        const int fm = cell * (kClassicBlocks + 4) + kClassicBlocks;
+        for (int j = 0; j < 4; j++)
+            if (m & (1 << j)) hv = fmaf(1.0f, Wk[(size_t)(fm + j) * H], hv);
+    }
+    int oi = 2 * kClassicCells;
+    int f = kClassicCells * (kClassicBlocks + 4);
+    for (int j = 0; j < kClassicInv + 4; j++, f++)
+        hv = fmaf((float)(int8_t)rs[oi++] / 10.0f, Wk[(size_t)f * H], hv);
+    const int8_t dir = (int8_t)rs[oi++];
+    for (int d = 1; d <= 4; d++, f++) hv = fmaf((dir == d) ? 1.0f : 0.0f, Wk[(size_t)f * H], hv);
+    const uint8_t sleeping = rs[oi++];
+    float light;
+    memcpy(&light, rs + oi, 4);
+    hv = fmaf(light, Wk[(size_t)f * H], hv);
+    f++;
+    hv = fmaf(sleeping ? 1.0f : 0.0f, Wk[(size_t)f * H], hv);
+    h_out[(size_t)e * H + k] = hv;
+}
+
+// r_done int8 flags of the classic rollout (main_classic.cu:436-443) -> the float flags the
+// MinGRU kernel takes
+__global__ void k_done_to_terminals(const int8_t* __restrict__ done, float* __restrict__ out, int n) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e < n) out[e] = done[e] != 0 ? 1.0f : 0.0f;
+}
+
 // ---------------------------------------------------------------- MinGRU layer
 // One layer: gate dots (ascending j, fmaf) + cell (k_mingru_epi_fwd,
 // craftax_full.cu:9350-9395).  Wt is the layer's gate matrix transposed to
@@ -209,6 +279,18 @@ int launch_expand(const uint8_t* rec, float* out, int n, cudaStream_t st) {
     return CFX_OK;
 }
 
+int launch_classic_expand(const uint8_t* rec, float* out, int n, cudaStream_t st) {
+    k_classic_expand<<<(n + 127) / 128, 128, 0, st>>>(rec, out, n);
+    CFX_CUDA(cudaGetLastError());
+    return CFX_OK;
+}
+
+int launch_done_to_terminals(const int8_t* done, float* out, int n, cudaStream_t st) {
+    k_done_to_terminals<<<(n + 255) / 256, 256, 0, st>>>(done, out, n);
+    CFX_CUDA(cudaGetLastError());
+    return CFX_OK;
+}
+
 int launch_sample(const float* logits, int ld, int A, const float* u, uint64_t seed,
                   uint64_t env_offset, const unsigned long long* step_ctr, int n,
                   float* env_actions, int32_t* actions, float* logprobs, float* values,
@@ -247,10 +329,14 @@ int launch_init_uniform(float* w, int count, float bound, uint64_t seed, int sub
 // Full strict forward.  scratch_h: two [n][H] fp32 buffers; logits_av [n][A+1].
 int strict_forward(const StrictArgs& a, cudaStream_t st, int* launches) {
     const int H = a.H, L = a.L, A = a.A, n = a.n;
-    const ArenaLayout o = ArenaLayout::make(H, L, A);
+    const ArenaLayout o = ArenaLayout::make(H, L, A, a.game == CFX_GAME_CLASSIC ? kClassicObs : kObs);
     int cnt = 0;
-    k_encoder_fp32<<<(n + ENC_ENVS - 1) / ENC_ENVS, H, 0, st>>>(
-        a.records, a.params + o.w_enc, a.params + o.b_enc, a.scratch_h[0], n, H);
+    if (a.game == CFX_GAME_CLASSIC)
+        k_classic_encoder_fp32<<<n, H, 0, st>>>(a.records, a.params + o.w_enc, a.params + o.b_enc,
+                                                a.scratch_h[0], n, H);
+    else
+        k_encoder_fp32<<<(n + ENC_ENVS - 1) / ENC_ENVS, H, 0, st>>>(
+            a.records, a.params + o.w_enc, a.params + o.b_enc, a.scratch_h[0], n, H);
     cnt++;
     const float* x = a.scratch_h[0];
     for (int l = 0; l < L; l++) {

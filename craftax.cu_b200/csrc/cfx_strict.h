@@ -7,6 +7,7 @@ namespace cfx {
 
 struct StrictArgs {
     int n, H, L, A;
+    int game = 0;           // CFX_GAME_FULL or CFX_GAME_CLASSIC (148-byte records, gather encoder)
     const float* params;    // fp32 arena
     const float* gates_t;   // [L][H][3H] transposed gate matrices
     const uint8_t* records;
@@ -26,6 +27,8 @@ struct StrictArgs {
 
 int strict_forward(const StrictArgs& a, cudaStream_t st, int* launches);
 int launch_expand(const uint8_t* rec, float* out, int n, cudaStream_t st);
+int launch_classic_expand(const uint8_t* rec, float* out, int n, cudaStream_t st);
+int launch_done_to_terminals(const int8_t* done, float* out, int n, cudaStream_t st);
 int launch_sample(const float* logits, int ld, int A, const float* u, uint64_t seed,
                   uint64_t env_offset, const unsigned long long* step_ctr, int n,
                   float* env_actions, int32_t* actions, float* logprobs, float* values,

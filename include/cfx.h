@@ -29,6 +29,11 @@ extern "C" {
 #define CFX_OBS_MAP 792      /* CF_NN_MAP,     craftax_full.cu:9091  */
 #define CFX_OBS_TAIL 51      /* CF_NN_TAIL,    craftax_full.cu:9092  */
 #define CFX_RECORD_BYTES 996 /* CF_TRAIN_OBS,  craftax_full.cu:9111  */
+/* classic game: record and feature count (OBS_DIM_COMPACT, OBS_DIM; craftax_classic.cu:59, :40) */
+#define CFX_CLASSIC_RECORD_BYTES 148
+#define CFX_CLASSIC_OBS_FEATURES 1345
+#define CFX_GAME_FULL 0
+#define CFX_GAME_CLASSIC 1
 
 typedef enum cfx_status {
     CFX_OK = 0,
@@ -215,6 +220,27 @@ int cfx_timer_elapsed_ms(void* timer, float* ms); /* synchronises on the stop ev
 
 const char* cfx_last_error(void);
 const char* cfx_version(void);
+
+/* ---- classic game (reference craftax_classic.cu, boundary Rollout::step in
+ * main_classic.cu:439-474) ------------------------------------------------------------
+ * Same handle type and the same calls as the full game (set_weights, state, step counter,
+ * forward, forward_host); what differs is the record (148 bytes: 63 block ids, 63 mob bit
+ * masks, 12 inventory counts, health/food/drink/energy, direction, sleeping flag, light as
+ * raw fp32; craftax_classic.cu:50-59), the encoder (a gather of W_enc rows in the order of
+ * encode_obs_kernel, :1714-1751) and the arena, whose W_enc has 1345 rows (:1526-1533).
+ * Only CFX_PREC_FP32 is built for it; the fused kernel returns CFX_ERR_UNSUPPORTED.
+ * cfx_forward_io.records then holds uint8 [n][148]; prev_terminals holds float flags
+ * (cfx_classic_done_to_terminals converts the rollout's int8 r_done row). */
+size_t cfx_classic_param_count(int hidden, int layers, int num_actions);
+int cfx_policy_create_classic(cfx_policy** out, int device, int num_envs, int hidden,
+                              int layers, int num_actions);
+/* Replaces expand_obs_kernel (craftax_classic.cu:1265-1301): uint8 [n][148] -> fp32 [n][1345]
+ * (device pointers). */
+int cfx_classic_expand_obs(int device, const uint8_t* records, float* out, int num_envs,
+                           void* stream);
+/* int8 done flags -> float terminal flags (device pointers). */
+int cfx_classic_done_to_terminals(int device, const int8_t* done, float* out, int num_envs,
+                                  void* stream);
 
 #ifdef __cplusplus
 }

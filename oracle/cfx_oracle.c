@@ -191,6 +191,145 @@ void cfxo_forward(const float* params, int H, int L, int A,
     }
 }
 
+/* ------------------------------------------------------------------------------------
+ * Classic game (reference craftax_classic.cu).  Record: uint8[148] = 63 block ids (int8,
+ * 0..16), 63 mob bit masks (1 zombie, 2 cow, 4 skeleton, 8 arrow), 12 inventory counts and
+ * health, food, drink, energy (int8, 0..9), direction (1..4), sleeping flag, light level as
+ * raw fp32 (craftax_classic.cu:50-59, writer :1574-1604).  Features: 63 cells x (17 block
+ * one-hot + 4 mob bits) = 1323, then inventory/10 x12, intrinsics/10 x4, direction one-hot
+ * x4, light, sleeping = 1345 (expand_obs_kernel :1265-1301).  Arena: same order as the full
+ * game with 1345 encoder rows (:1526-1533).  Policy: 3 MinGRU layers, 17 actions.
+ * ------------------------------------------------------------------------------------ */
+#define CFXO_C_CELLS 63
+#define CFXO_C_BLOCKS 17
+#define CFXO_C_INV 12
+#define CFXO_C_OBS 1345
+#define CFXO_C_REC 148
+
+size_t cfxo_classic_param_count(int H, int L, int A) {
+    return (size_t)CFXO_C_OBS * H + H + (size_t)L * 3 * H * H + (size_t)A * H + A + H + 1;
+}
+
+/* expand_obs_kernel (:1265-1301): out is [n][1345]. */
+void cfxo_classic_expand(const uint8_t* rec, float* out, int n) {
+    for (int e = 0; e < n; e++) {
+        const uint8_t* c = rec + (size_t)e * CFXO_C_REC;
+        float* o = out + (size_t)e * CFXO_C_OBS;
+        int k = 0;
+        for (int cell = 0; cell < CFXO_C_CELLS; cell++) {
+            int8_t blk = (int8_t)c[cell];
+            for (int b = 0; b < CFXO_C_BLOCKS; b++) o[k++] = (blk == b) ? 1.0f : 0.0f;
+            uint8_t m = c[CFXO_C_CELLS + cell];
+            for (int j = 0; j < 4; j++) o[k++] = (m & (1 << j)) ? 1.0f : 0.0f;
+        }
+        int i2 = 2 * CFXO_C_CELLS;
+        for (int j = 0; j < CFXO_C_INV + 4; j++) o[k++] = (float)(int8_t)c[i2++] / 10.0f;
+        int8_t dir = (int8_t)c[i2++];
+        for (int d = 1; d <= 4; d++) o[k++] = (dir == d) ? 1.0f : 0.0f;
+        uint8_t sleeping = c[i2++];
+        float light;
+        memcpy(&light, c + i2, 4);
+        o[k++] = light;
+        o[k++] = sleeping ? 1.0f : 0.0f;
+    }
+}
+
+/* Forward in the order of encode_obs_kernel (:1714-1751) for the encoder - bias first, then
+ * per cell the block column and the set mob bits, then the 22 scalar features, every term
+ * as fmaf(x, W, acc) - and of ref_policy_l3_kernel (:2016-2047) for the layers and the heads
+ * (logits = b_a + dot, value = b_v + dot).  prev_done: int8 flags or NULL.  State [L][n][H]. */
+void cfxo_classic_forward(const float* params, int H, int L, int A,
+                          const uint8_t* rec, const int8_t* prev_done,
+                          float* state, int n, float* logits_av, float* h_enc_out) {
+    const float* W_enc = params;
+    const float* b_enc = W_enc + (size_t)CFXO_C_OBS * H;
+    const float* W_gru = b_enc + H;
+    const float* W_a = W_gru + (size_t)L * 3 * H * H;
+    const float* b_a = W_a + (size_t)A * H;
+    const float* W_v = b_a + A;
+    const float* b_v = W_v + H;
+#pragma omp parallel
+    {
+        float* h = (float*)malloc(sizeof(float) * H);
+        float* h2 = (float*)malloc(sizeof(float) * H);
+#pragma omp for schedule(static)
+        for (int e = 0; e < n; e++) {
+            const uint8_t* c = rec + (size_t)e * CFXO_C_REC;
+            for (int i = 0; i < H; i++) h[i] = b_enc[i];
+            for (int cell = 0; cell < CFXO_C_CELLS; cell++) {
+                const float* col = W_enc + (size_t)(cell * (CFXO_C_BLOCKS + 4) + (int8_t)c[cell]) * H;
+                for (int i = 0; i < H; i++) h[i] = fmaf(1.0f, col[i], h[i]);
+                uint8_t m = c[CFXO_C_CELLS + cell];
+                int fm = cell * (CFXO_C_BLOCKS + 4) + CFXO_C_BLOCKS;
+                for (int j = 0; j < 4; j++)
+                    if (m & (1 << j)) {
+                        const float* mc = W_enc + (size_t)(fm + j) * H;
+                        for (int i = 0; i < H; i++) h[i] = fmaf(1.0f, mc[i], h[i]);
+                    }
+            }
+            int oi = 2 * CFXO_C_CELLS, f = CFXO_C_CELLS * (CFXO_C_BLOCKS + 4);
+            for (int j = 0; j < CFXO_C_INV + 4; j++, f++) {
+                float x = (float)(int8_t)c[oi++] / 10.0f;
+                const float* col = W_enc + (size_t)f * H;
+                for (int i = 0; i < H; i++) h[i] = fmaf(x, col[i], h[i]);
+            }
+            int8_t dir = (int8_t)c[oi++];
+            for (int d = 1; d <= 4; d++, f++) {
+                float x = (dir == d) ? 1.0f : 0.0f;
+                const float* col = W_enc + (size_t)f * H;
+                for (int i = 0; i < H; i++) h[i] = fmaf(x, col[i], h[i]);
+            }
+            uint8_t sleeping = c[oi++];
+            float light;
+            memcpy(&light, c + oi, 4);
+            {
+                const float* col = W_enc + (size_t)f * H; f++;
+                for (int i = 0; i < H; i++) h[i] = fmaf(light, col[i], h[i]);
+                col = W_enc + (size_t)f * H;
+                float x = sleeping ? 1.0f : 0.0f;
+                for (int i = 0; i < H; i++) h[i] = fmaf(x, col[i], h[i]);
+            }
+            if (h_enc_out) memcpy(h_enc_out + (size_t)e * H, h, sizeof(float) * H);
+            int dz = prev_done != NULL && prev_done[e] != 0;
+            for (int l = 0; l < L; l++) {
+                const float* Wl = W_gru + (size_t)l * 3 * H * H;
+                float* st_row = state + ((size_t)l * n + e) * H;
+                for (int k = 0; k < H; k++) {
+                    float st = dz ? 0.0f : st_row[k];
+                    float zh = 0.0f, zg = 0.0f, zp = 0.0f;
+                    const float* wh = Wl + (size_t)k * H;
+                    const float* wg = Wl + (size_t)(H + k) * H;
+                    const float* wp = Wl + (size_t)(2 * H + k) * H;
+                    for (int j = 0; j < H; j++) {
+                        zh = fmaf(wh[j], h[j], zh);
+                        zg = fmaf(wg[j], h[j], zg);
+                        zp = fmaf(wp[j], h[j], zp);
+                    }
+                    float out = st + cfxo_sigmoid(zg) * (cfxo_g(zh) - st);
+                    float p = cfxo_sigmoid(zp);
+                    h2[k] = p * out + (1.0f - p) * h[k];
+                    st_row[k] = out;
+                }
+                memcpy(h, h2, sizeof(float) * H);
+            }
+            if (logits_av) {
+                float* lo = logits_av + (size_t)e * (A + 1);
+                for (int a = 0; a < A; a++) {
+                    float z = b_a[a];
+                    const float* wa = W_a + (size_t)a * H;
+                    for (int j = 0; j < H; j++) z = fmaf(wa[j], h[j], z);
+                    lo[a] = z;
+                }
+                float v = b_v[0];
+                for (int j = 0; j < H; j++) v = fmaf(W_v[j], h[j], v);
+                lo[A] = v;
+            }
+        }
+        free(h);
+        free(h2);
+    }
+}
+
 int cfxo_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -15,6 +15,8 @@ import numpy as np
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
                                 "craftax.cu_b200"))
 from cfx.synth import MAP, OBS, REC, TAIL, init_weights, offsets, synthetic_records  # noqa: E402,F401
+from cfx.synth import (CLASSIC_OBS, CLASSIC_REC, classic_init_weights, classic_offsets,  # noqa: E402,F401
+                       classic_synthetic_records)
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
@@ -42,6 +44,11 @@ def lib():
         L.cfxo_forward.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                    C.c_void_p, C.c_void_p, C.c_int, C.c_void_p,
                                    C.c_void_p, C.c_void_p]
+        L.cfxo_classic_param_count.restype = C.c_size_t
+        L.cfxo_classic_param_count.argtypes = [C.c_int] * 3
+        L.cfxo_classic_expand.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+        L.cfxo_classic_forward.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                           C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
         L.cfxo_max_threads.restype = C.c_int
         L.cfxo_set_threads.argtypes = [C.c_int]
         _lib = L
@@ -95,6 +102,28 @@ def forward(params, rec, prev_terminals, state, H=256, L=2, A=43, want_h=False,
     if want_r_state:
         out.append(rs)
     return out[0] if len(out) == 1 else tuple(out)
+
+
+def classic_expand(rec):
+    rec = np.ascontiguousarray(rec, np.uint8).reshape(-1, CLASSIC_REC)
+    out = np.empty((rec.shape[0], CLASSIC_OBS), np.float32)
+    lib().cfxo_classic_expand(_p(rec), _p(out), rec.shape[0])
+    return out
+
+
+def classic_forward(params, rec, prev_done, state, H=256, L=3, A=17, want_h_enc=False):
+    """Classic-game forward (gather encoder in the reference's order).  prev_done: int8 flags
+    or None; state [L][n][H] is updated in place.  Returns logits_av [n][A+1]."""
+    rec = np.ascontiguousarray(rec, np.uint8).reshape(-1, CLASSIC_REC)
+    n = rec.shape[0]
+    params = np.ascontiguousarray(params, np.float32)
+    assert params.size == int(lib().cfxo_classic_param_count(H, L, A))
+    assert state.dtype == np.float32 and state.shape == (L, n, H) and state.flags.c_contiguous
+    pd = None if prev_done is None else np.ascontiguousarray(prev_done, np.int8)
+    lav = np.empty((n, A + 1), np.float32)
+    he = np.empty((n, H), np.float32) if want_h_enc else None
+    lib().cfxo_classic_forward(_p(params), H, L, A, _p(rec), _p(pd), _p(state), n, _p(lav), _p(he))
+    return (lav, he) if want_h_enc else lav
 
 
 def max_threads():
@@ -157,6 +186,38 @@ class RefEnv:
         if self.h:
             self.L.refenv_destroy(self.h)
             self.h = None
+
+
+class RefClassic:
+    """The reference's classic-game kernels (expand, gather encoder, MinGRU epilogue, sampler;
+    compiled from craftax_classic.cu by oracle/Makefile into ``_ref/libcfref_classic.so``) with
+    cuBLAS fp32 products between them.  Runs only on a GPU box."""
+
+    path = os.path.join(HERE, "_ref", "libcfref_classic.so")
+
+    @classmethod
+    def available(cls):
+        return os.path.exists(cls.path)
+
+    def __init__(self):
+        L = C.CDLL(self.path)
+        L.refcl_expand.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+        L.refcl_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                    C.c_ulonglong, C.c_ulonglong] + [C.c_void_p] * 4
+        self.L = L
+        self.H, self.layers, self.A = L.refcl_hidden(), L.refcl_layers(), L.refcl_actions()
+        assert L.refcl_obs() == CLASSIC_OBS and L.refcl_record_bytes() == CLASSIC_REC
+        self.param_count = L.refcl_param_count()
+
+    def expand(self, d_rec_ptr, d_out_ptr, n):
+        self.L.refcl_expand(d_rec_ptr, d_out_ptr, n)
+
+    def forward(self, d_params_ptr, d_rec_ptr, d_prev_done_ptr, d_state_ptr, n, seed, step):
+        o = {"logits_av": np.empty((n, self.A + 1), np.float32), "h_enc": np.empty((n, self.H), np.float32),
+             "actions": np.empty(n, np.int32), "logprobs": np.empty(n, np.float32)}
+        self.L.refcl_forward(d_params_ptr, d_rec_ptr, d_prev_done_ptr, d_state_ptr, n, seed, step,
+                             _p(o["logits_av"]), _p(o["h_enc"]), _p(o["actions"]), _p(o["logprobs"]))
+        return o
 
 
 class RefCuda:
