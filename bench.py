@@ -339,6 +339,51 @@ def run_ref_cublas(args):
     ref.close()
 
 
+def run_sweep(args):
+    """Synthetic fused-forward sweep on one GPU: batch x MinGRU depth x operand type at hidden
+    256 (the instantiations built), one JSON line per point with the fused-roofline fraction.
+    Points of the published sweep that are not built (hidden 128 / 512, tf32 operands) are
+    listed once as unavailable."""
+    import cfx
+    from cfx.synth import synthetic_records, init_weights
+    rank, _, local = dist_env()
+    if rank != 0:
+        return
+    peaks = load_peaks()
+    base = synthetic_records(8192, seed=4)
+    for n in (8192, 65536, 262144, 1048576, 2097152):
+        rec = np.tile(base, (n // 8192, 1))
+        d_rec = cfx.DeviceBuffer.from_host(rec, local)
+        del rec
+        d_act = cfx.DeviceBuffer((n,), np.int32, local)
+        d_lav = cfx.DeviceBuffer((n, A + 1), np.float32, local)
+        for L in (2, 3):
+            for prec in ("f16", "bf16"):
+                pol = cfx.Policy(n, 256, L, A, prec, device=local)
+                pol.set_weights(init_weights(256, L, A, seed=0))
+                for _ in range(3):
+                    pol.forward_device(d_rec, None, None, actions=d_act, logits_av=d_lav, seed=1, bump_step=True)
+                pol.check()
+                steps = 20 if n <= 262144 else 8
+                t = cfx.Timer(local)
+                t.start(pol.stream)
+                for _ in range(steps):
+                    pol.forward_device(d_rec, None, None, actions=d_act, logits_av=d_lav, seed=1, bump_step=True)
+                t.stop(pol.stream)
+                pol.check()
+                ms = t.elapsed_ms() / steps
+                flops, byts = algorithmic_work(256, L)
+                t_roof = max(n * byts / (peaks["hbm_gbs"] * 1e9), n * flops / (peaks["bf16_tflops"] * 1e12))
+                print(json.dumps({"sweep": "fused forward", "envs": n, "hidden": 256, "layers": L,
+                                  "operands": prec, "ms_per_step": ms, "env_steps_per_s": n / (ms * 1e-3),
+                                  "fused_roofline_ms": t_roof * 1e3, "fused_roofline_frac": t_roof * 1e3 / ms,
+                                  "peak_source": peaks["source"]}), flush=True)
+                pol.close()
+        d_rec.free(); d_act.free(); d_lav.free()
+    print(json.dumps({"sweep": "fused forward", "unavailable":
+                      "hidden 128 and 512 and tf32 operands are not instantiated in this library"}), flush=True)
+
+
 def run_ref_rollout(args):
     """Whole rollouts on one B200: the reference's own `run` loop (env kernels + its cuBLAS
     policy, graph replay), its env kernels alone, and the same loop with the policy half
@@ -382,7 +427,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="cfx", choices=["cfx", "reference", "ref-cublas", "ref-rollout"])
+    ap.add_argument("--impl", default="cfx", choices=["cfx", "reference", "ref-cublas", "ref-rollout", "sweep"])
     ap.add_argument("--ref-mode", default="bf16", choices=["bf16", "tf32", "fp32"])
     ap.add_argument("--envs", type=int, default=262144, help="envs per GPU")
     ap.add_argument("--hidden", type=int, default=256)
@@ -400,6 +445,8 @@ def main():
         run_ref_cublas(args)
     elif args.impl == "ref-rollout":
         run_ref_rollout(args)
+    elif args.impl == "sweep":
+        run_sweep(args)
     else:
         run_cfx(args)
 
