@@ -628,25 +628,40 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
     constexpr uint32_t idesc_head = make_idesc(fmt, C::kM, C::kHeadRows);
     const uint64_t bdesc0 = smem_desc_sw128(smem_u32(sm.b_ring()));
     uint32_t bcnt = 0, acnt = 0, akb_use = 0, gcnt = 0, tcnt = 0;
+    // The "full" barriers of the NEXT stage are probed before the current stage's MMAs are
+    // issued, so that the probe's shared-memory round trip (~150 cycles on this thread) runs
+    // under the MMA issue; only a failed probe falls into the bounded wait.  Probing one stage
+    // early is sound: the previous use of that slot has already been consumed by this thread,
+    // so its barrier is at most one phase behind.
+    auto probe_b = [&](uint32_t cnt) -> bool {
+        return mbar_test_wait(sm.bar(B_FULL + (int)(cnt % kNB)), (cnt / kNB) & 1);
+    };
+    auto probe_a = [&](uint32_t cnt) -> bool {
+        return mbar_test_wait(sm.bar(AEXP_FULL + (int)(cnt % kAexpSlots)), (cnt / kAexpSlots) & 1);
+    };
+#define CFX_WAIT_PROBED(ready, barid, parity, code) \
+    if (!(ready) && !mbar_wait_spin(sm.bar(barid), (parity), sm.abort_flag(), (code))) return
     TL_INIT(0);
+#ifdef CFX_PROFILE
+    if (blockIdx.x == 0 && P.timeline != nullptr) P.timeline[4 * 4096 + 3] = (long long)global_timer_ns();
+#endif
     for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, tcnt++) {
         TLB(0, 0x1000000);
         // the encoder accumulator overlaps the head accumulator of the previous tile:
         // wait until the sampler threads have read it
         CFX_WAIT_LEADER(H_EMPTY, (tcnt & 1) ^ 1, W_H_EMPTY);
+        bool a_ready = probe_a(acnt), b_ready = probe_b(bcnt);
         // ---- encoder: 14 operand chunks, N = 256 units
         for (int kc = 0; kc < kEncChunks; kc++, acnt++, bcnt++) {
             const int as = acnt % kAexpSlots;
             const int slot = bcnt % kNB;
-            CFX_WAIT_LEADER(AEXP_FULL + as, (acnt / kAexpSlots) & 1, W_AEXP_FULL);
+            CFX_WAIT_PROBED(a_ready, AEXP_FULL + as, (acnt / kAexpSlots) & 1, W_AEXP_FULL);
             TLB(2, 0x20000 | kc);
-#ifdef CFX_PROFILE
-            while (!mbar_test_wait(sm.bar(B_FULL + slot), (bcnt / kNB) & 1)) pf_[10]++;
-#else
-            CFX_WAIT_LEADER(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
-#endif
+            CFX_WAIT_PROBED(b_ready, B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
             TLB(3, 0x30000 | kc);
             tc_fence_after_sync();
+            a_ready = kc + 1 < kEncChunks ? probe_a(acnt + 1) : false;
+            b_ready = probe_b(bcnt + 1);
             const uint32_t a_col = tmem + kColAexp + as * 32;
             const uint64_t bd = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
             {
@@ -678,13 +693,10 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
                         TLB(9, 0x48000 | (l << 8) | kb);
                     }
                     const int slot = bcnt % kNB;
-#ifdef CFX_PROFILE
-                    while (!mbar_test_wait(sm.bar(B_FULL + slot), (bcnt / kNB) & 1)) pf_[11]++;
-#else
-                    CFX_WAIT_LEADER(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
-#endif
+                    CFX_WAIT_PROBED(b_ready, B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
                     TLB(6, 0x50000 | (l << 8) | (j << 2) | kb);
                     tc_fence_after_sync();
+                    b_ready = probe_b(bcnt + 1);
                     const uint64_t bd = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
                     {
 #pragma unroll
@@ -707,7 +719,7 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
             for (int kb = 0; kb < kKBlocks; kb++) CFX_WAIT_LEADER(A_KB + kb, akb_use & 1, W_A_KB);
             akb_use++;
             const int slot = bcnt % kNB;
-            CFX_WAIT_LEADER(B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
+            CFX_WAIT_PROBED(b_ready, B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
             tc_fence_after_sync();
             const uint64_t bd = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
             {
@@ -727,6 +739,9 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
         }
     }
     TL_FLUSH();
+#ifdef CFX_PROFILE
+    if (blockIdx.x == 0 && P.timeline != nullptr) P.timeline[4 * 4096 + 4] = (long long)global_timer_ns();
+#endif
 }
 
 // ------------------------------------------------------------------ worker role
@@ -1007,6 +1022,9 @@ k_policy_fused(const __grid_constant__ Params P) {
     sm.base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     sm.layout<PAIR>();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef CFX_PROFILE
+    const uint64_t pf_entry = global_timer_ns();
+#endif
     const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
     // arrivals per phase on the barriers the MMA thread waits on: both CTAs' workers in a pair
     const uint32_t both = (PAIR && rank == 0) ? 2u : 1u;
@@ -1063,6 +1081,9 @@ k_policy_fused(const __grid_constant__ Params P) {
     tc_fence_after_sync();
     const uint32_t tmem = *sm.tmem_base();
     const uint32_t bar0_cta0 = PAIR ? map_to_cta(sm.bar(0), 0u) : 0u;
+#ifdef CFX_PROFILE
+    const uint64_t pf_roles = global_timer_ns();
+#endif
 
     if (warp == 0) {
         if (lane < C::kWLanes) role_weight_loads<PAIR>(sm, P, lane, rank, bar0_cta0);
@@ -1082,6 +1103,12 @@ k_policy_fused(const __grid_constant__ Params P) {
     tc_fence_before_sync();
     if (PAIR) cluster_sync_all();
     else __syncthreads();
+#ifdef CFX_PROFILE
+    if (tid == 0 && P.timeline != nullptr && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) {
+        long long* t = P.timeline + 4 * 4096 + (blockIdx.x == 0 ? 0 : 8);
+        t[0] = (long long)pf_entry; t[1] = (long long)pf_roles; t[2] = (long long)global_timer_ns();
+    }
+#endif
     const uint32_t aborted = *sm.abort_flag();
     if (aborted != 0) {
         if (tid == 0) atomicCAS(P.status, 0u, aborted | ((uint32_t)blockIdx.x << 8));

@@ -109,3 +109,26 @@ def test_expand_matches_reference_kernel_through_its_pipeline(cfx, oracle, refcu
             h = half * quarter + half * h
         assert np.array_equal(r["h3"].view(np.uint32), h.astype(np.float32).view(np.uint32)), base
         ref.close()
+
+
+def test_reference_run_loop_with_the_forward_swapped_in(cfx, oracle, refcu):
+    """The reference's `run` loop (its env kernels, CUDA-graph replay) with the policy half
+    replaced by cfx_policy_forward: the binding must capture into a graph, replay and leave no
+    error behind; the unmodified loop runs beside it."""
+    import ctypes as C
+    if not refcu.available(2):
+        pytest.skip("oracle/_ref/libcfref_cuda_l2.so not built")
+    cfx.lib()
+    lib = C.CDLL(refcu.path(2))
+    if not hasattr(lib, "refcu_rollout_swap_sps"):
+        pytest.skip("reference shim built without the swapped loop")
+    lib.refcu_rollout_sps.restype = C.c_double
+    lib.refcu_rollout_sps.argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_int]
+    lib.refcu_rollout_swap_sps.restype = C.c_double
+    lib.refcu_rollout_swap_sps.argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_int, C.c_int]
+    ref_sps = lib.refcu_rollout_sps(4096, 40, 3, 1)
+    for prec in (cfx.PREC_F16, cfx.PREC_FP32):
+        sps = lib.refcu_rollout_swap_sps(4096, 40, 3, 1, prec)
+        assert np.isfinite(sps) and sps > 0
+        print(f"rollout 4096 envs: reference {ref_sps / 1e6:.1f} M SPS, swapped (precision {prec}) {sps / 1e6:.1f} M SPS")
+    assert ref_sps > 0
