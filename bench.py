@@ -452,7 +452,7 @@ def main():
 
 
 DEFAULT_PRECISION = "f16"
-NCU_DRAM_BYTES_PER_ENV = (206.87e6 + 90.29e6) / 65536   # ncu capture at 65,536 envs, see profiles/
+NCU_DRAM_BYTES_PER_ENV = (208.01e6 + 92.44e6) / 65536   # ncu capture at 65,536 envs, see profiles/
 
 if __name__ == "__main__":
     main()

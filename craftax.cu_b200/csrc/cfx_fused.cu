@@ -159,6 +159,7 @@ struct Params {
     float* logprobs;
     float* values;
     float* logits_av;
+    float* r_state;                      // optional [L][n][256] record of the post-zero input state
     const unsigned long long* step_ctr;
     uint32_t* status;
     uint64_t seed, env_offset;
@@ -924,6 +925,11 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
 #endif
                         float4 st = *sp;
                         if (zero_state) st = make_float4(0.f, 0.f, 0.f, 0.f);
+                        // optional BPTT record of the post-zero input state (what the reference's
+                        // k_mingru_epi_fwd stores, craftax_full.cu:9370-9375): [L][n][256] fp32
+                        if (P.r_state != nullptr && valid)
+                            *reinterpret_cast<float4*>(P.r_state + ((size_t)l * P.n + env) * kH +
+                                                       kSliceUnits * j + kHalfUnits * wg + u) = st;
                         const float2 x01 = Op::unpack(xin[u / 2]), x23 = Op::unpack(xin[u / 2 + 1]);
                         float4 out;
                         float h0, h1, h2, h3;
@@ -1224,9 +1230,9 @@ int fused_refresh(FusedPlan* p, const float* params, cudaStream_t st) {
 }
 
 int fused_forward(FusedPlan* p, const FusedArgs& a, cudaStream_t st, int* launches) {
-    if (a.r_state != nullptr) {
-        set_error("fused forward: r_state recording is only available with precision fp32");
-        return CFX_ERR_UNSUPPORTED;
+    if (a.r_state != nullptr && ((uintptr_t)a.r_state & 15) != 0) {
+        set_error("fused forward: r_state must be 16-byte aligned");
+        return CFX_ERR_INVALID;
     }
     if (a.logits_av != nullptr && ((uintptr_t)a.logits_av & 15) != 0) {
         set_error("fused forward: logits_av must be 16-byte aligned");
@@ -1252,6 +1258,7 @@ int fused_forward(FusedPlan* p, const FusedArgs& a, cudaStream_t st, int* launch
     P.logprobs = a.logprobs;
     P.values = a.values;
     P.logits_av = a.logits_av;
+    P.r_state = a.r_state;
     P.step_ctr = a.step_ctr;
     P.status = p->status;
     P.seed = a.seed;

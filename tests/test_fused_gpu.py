@@ -127,18 +127,28 @@ def test_fused_expand_is_exact_for_every_map_feature(cfx, gpu, oracle):
 def test_fused_rejects_what_it_cannot_do(cfx, gpu, oracle):
     with pytest.raises(cfx.CfxError):
         cfx.Policy(64, 128, 2, A, "f16")        # hidden 128 is not instantiated
-    pol = cfx.Policy(64, H, L, A, "f16")
-    pol.set_weights(oracle.init_weights(H, L, A, seed=1))
-    rec = oracle.synthetic_records(64, seed=1)
     with pytest.raises(cfx.CfxError):
-        pol.forward_host(rec, None, None, want_r_state=True)
-    pol.set_precision("fp32")                    # the strict path records r_state
-    d = pol.forward_host(rec, None, None, want_r_state=True)
-    assert d["r_state"].shape == (L, 64, H)
-    pol.set_precision("f16")
-    d = pol.forward_host(rec, None, None)
-    assert np.isfinite(d["logits_av"]).all()
-    pol.close()
+        cfx.Policy(64, H, L, A, "tf32")         # tf32 operands are not built
+
+
+def test_fused_records_r_state(cfx, gpu, oracle):
+    """The optional BPTT record holds the post-zero INPUT state of every layer: the previous
+    state, zeroed where prev_terminals is set - exactly, in every precision."""
+    n = 128 * 3 + 64
+    rng = np.random.default_rng(5)
+    rec = oracle.synthetic_records(n, seed=2)
+    params = oracle.init_weights(H, 3, A, seed=4)
+    state = rng.normal(0, 1, (3, n, H)).astype(np.float32)
+    prev_t = (rng.random(n) < 0.3).astype(np.float32)
+    want = state.copy()
+    want[:, prev_t != 0] = 0
+    for prec in ("f16", "fp32"):
+        pol = cfx.Policy(n, H, 3, A, prec)
+        pol.set_weights(params)
+        pol.set_state(state)
+        d = pol.forward_host(rec, prev_t, None, want_r_state=True)
+        assert np.array_equal(d["r_state"], want), prec
+        pol.close()
 
 
 @pytest.mark.parametrize("n,layers", [(64, 2), (128 * 7, 2), (128 * 300 + 96, 3)])
