@@ -56,26 +56,34 @@ class ClockSampler:
         self.index, self.mhz, self.bits, self.max_mhz = index, [], 0, None
         self._stop = threading.Event()
         self.thread = None
-
-    def start(self):
-        try:
+        self._nvml = None
+        try:   # NVML is brought up here, before the warm-up, so that start() costs nothing
             import pynvml
             pynvml.nvmlInit()
-            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
-            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
-
-            def loop():
-                while not self._stop.is_set():
-                    self.mhz.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
-                    try:
-                        self.bits |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
-                    except Exception:
-                        self.bits |= int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
-                    time.sleep(0.0005)
-            self.thread = threading.Thread(target=loop, daemon=True)
-            self.thread.start()
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+            self._nvml = pynvml
         except Exception as e:  # NVML missing: one nvidia-smi sample at stop()
             self.err = str(e)
+
+    def _sample(self):
+        nv, h = self._nvml, self._h
+        self.mhz.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+        try:
+            self.bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
+        except Exception:
+            self.bits |= int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+
+    def start(self):
+        if self._nvml is None:
+            return
+
+        def loop():
+            while not self._stop.is_set():
+                self._sample()
+                time.sleep(0.0005)
+        self.thread = threading.Thread(target=loop, daemon=True)
+        self.thread.start()
 
     def stop(self):
         if self.thread is not None:
@@ -146,11 +154,11 @@ def run_cfx(args):
             torch.cuda.synchronize()
         pol.sync()
 
+    sampler = ClockSampler(dev)
     for _ in range(args.warmup):
         step()
     pol.sync()
     launches_per_step = pol.last_launches
-    sampler = ClockSampler(dev)
     sampler.start()
     timers = [cfx.Timer(dev) for _ in range(args.steps)]
     barrier()
