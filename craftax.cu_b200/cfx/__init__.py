@@ -19,6 +19,7 @@ OBS, MAP, TAIL, REC = 843, 792, 51, 996
 CLASSIC_OBS, CLASSIC_REC = 1345, 148
 PREC_FP32, PREC_F16, PREC_BF16, PREC_TF32 = 0, 1, 2, 3
 PREC_NAMES = {"fp32": 0, "f16": 1, "bf16": 2, "tf32": 3}
+OK, ERR_INVALID, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_IO, ERR_UNSUPPORTED = 0, 1, 2, 3, 4, 5
 
 
 class CfxError(RuntimeError):
@@ -56,6 +57,7 @@ _SIGS = {
     "cfx_policy_forward": (C.c_int, [C.c_void_p, C.POINTER(ForwardIO), C.c_void_p]),
     "cfx_policy_forward_host": (C.c_int, [C.c_void_p, C.POINTER(ForwardIO)]),
     "cfx_policy_check": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "cfx_selftest_wait_timeout": (C.c_int, [C.c_int, C.c_uint]),
     "cfx_strict_forward_static": (C.c_int, [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                             C.c_void_p, C.POINTER(ForwardIO), C.c_void_p, C.c_void_p]),
     "cfx_classic_param_count": (C.c_size_t, [C.c_int] * 3),

@@ -473,6 +473,20 @@ extern "C" int cfx_policy_check(cfx_policy* p, void* stream) {
     return CFX_OK;
 }
 
+extern "C" int cfx_selftest_wait_timeout(int device, unsigned limit_ms) {
+    CFX_REQUIRE(limit_ms >= 1 && limit_ms <= 1000, "cfx_selftest_wait_timeout: limit_ms=%u out of [1,1000]", limit_ms);
+    DeviceGuard g(device);
+    unsigned status = 0;
+    int rc = fused_selftest_wait_timeout(limit_ms, &status);
+    if (rc) return rc;
+    if (status == 0) {
+        set_error("self-test: the bounded wait did not report a timeout");
+        return CFX_ERR_CUDA;
+    }
+    set_error("device-side wait timed out: site %u, block %u (self-test)", status & 0xFF, status >> 8);
+    return CFX_ERR_DEVICE_TIMEOUT;
+}
+
 // ------------------------------------------------------------------ host-buffer forward
 template <typename T>
 static int ensure_staging(T** slot, size_t count) {

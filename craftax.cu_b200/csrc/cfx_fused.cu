@@ -1128,7 +1128,42 @@ k_policy_fused(const __grid_constant__ Params P) {
     }
 }
 
+// Self-test of the bounded wait: one block waits on a barrier on which nothing ever arrives,
+// with a limit of a few milliseconds, gives up, and reports through the same status word
+// protocol as the forward kernel.  The kernel ends normally; the context stays usable.
+constexpr uint32_t kSelftestCode = 0x7E;
+__global__ void k_selftest_wait_timeout(uint32_t* status, unsigned long long limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    mbar_wait(smem_u32(&bar), 0, &abort_flag, kSelftestCode, limit_ns);
+    __syncthreads();
+    if (threadIdx.x == 0 && abort_flag != 0) atomicCAS(status, 0u, abort_flag | ((uint32_t)blockIdx.x << 8));
+}
+
 }  // namespace fused
+
+int fused_selftest_wait_timeout(unsigned limit_ms, unsigned* status_out) {
+    uint32_t* d = nullptr;
+    CFX_CUDA(cudaMalloc((void**)&d, sizeof(uint32_t)));
+    cudaError_t e = cudaMemset(d, 0, sizeof(uint32_t));
+    if (e == cudaSuccess) {
+        fused::k_selftest_wait_timeout<<<1, 64>>>(d, (unsigned long long)limit_ms * 1000000ull);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    uint32_t v = 0;
+    if (e == cudaSuccess) e = cudaMemcpy(&v, d, sizeof(v), cudaMemcpyDeviceToHost);
+    cudaFree(d);
+    if (e != cudaSuccess) return cuda_fail(e, "selftest", __FILE__, __LINE__);
+    *status_out = v;
+    return CFX_OK;
+}
 
 // ------------------------------------------------------------------ host side
 struct FusedPlan {

@@ -33,4 +33,6 @@ int fused_forward(FusedPlan* plan, const FusedArgs& a, cudaStream_t st, int* lau
 int fused_check_status(FusedPlan* plan, cudaStream_t st, unsigned* status);
 void fused_destroy(FusedPlan* plan);
 
+int fused_selftest_wait_timeout(unsigned limit_ms, unsigned* status_out);
+
 }  // namespace cfx

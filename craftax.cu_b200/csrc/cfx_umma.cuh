@@ -117,7 +117,8 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile uint32_t* abort_flag, uint32_t code) {
+                                          volatile uint32_t* abort_flag, uint32_t code,
+                                          uint64_t limit_ns = kWaitLimitNs) {
     // One loop and nothing in front of it: peeling the first probe out of the loop (try_wait
     // or test_wait) made the fused kernel 10 % slower on B200.
     uint64_t t0 = 0;
@@ -136,7 +137,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
             const uint64_t now = global_timer_ns();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > kWaitLimitNs) {
+            } else if (now - t0 > limit_ns) {
                 atomicCAS((uint32_t*)abort_flag, 0u, code);
                 return false;
             }

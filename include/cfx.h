@@ -163,6 +163,13 @@ int cfx_policy_forward(cfx_policy* p, const cfx_forward_io* io, void* stream);
  * out; errors surface through CU_CHECK, craftax_full.cu:8635). */
 int cfx_policy_check(cfx_policy* p, void* stream);
 
+/* Self-test of the device-side timeout path (no reference counterpart): one thread block
+ * waits, with a limit of `limit_ms` milliseconds, on a barrier nothing arrives on, gives up and
+ * reports through the status word.  Returns CFX_ERR_DEVICE_TIMEOUT when the mechanism works
+ * (the expected result), another error otherwise.  The kernel ends normally; the CUDA context
+ * stays usable. */
+int cfx_selftest_wait_timeout(int device, unsigned limit_ms);
+
 /* Same forward with HOST buffers (pinned for full copy speed): copies
  * records/prev_terminals/uniforms to handle-owned device staging, runs
  * cfx_policy_forward, copies every non-NULL output back and synchronises. */

@@ -172,3 +172,18 @@ def test_fused_single_cta_mode_equals_pair_mode(cfx, gpu, oracle, monkeypatch, n
     assert np.array_equal(st1, st0)
     assert np.array_equal(d1["actions"], d0["actions"])
     assert np.array_equal(d1["logprobs"], d0["logprobs"])
+
+
+def test_bounded_wait_reports_a_timeout_and_leaves_the_context_usable(cfx, gpu, oracle):
+    """Every wait in the kernels is bounded.  The self-test kernel waits 5 ms on a barrier that
+    nothing sets, gives up and reports through the status word; afterwards a normal forward
+    runs on the same context."""
+    rc = cfx.lib().cfx_selftest_wait_timeout(0, 5)
+    assert rc == cfx.ERR_DEVICE_TIMEOUT, cfx.lib().cfx_last_error()
+    assert b"timed out" in cfx.lib().cfx_last_error()
+    pol = cfx.Policy(64, H, L, A, "f16")
+    pol.set_weights(oracle.init_weights(H, L, A, seed=1))
+    d = pol.forward_host(oracle.synthetic_records(64, seed=1), None, None)
+    assert np.isfinite(d["logits_av"]).all()
+    pol.check()
+    pol.close()
