@@ -61,7 +61,7 @@ _SIGS = {
     "cfx_strict_forward_static": (C.c_int, [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                             C.c_void_p, C.POINTER(ForwardIO), C.c_void_p, C.c_void_p]),
     "cfx_classic_param_count": (C.c_size_t, [C.c_int] * 3),
-    "cfx_policy_create_classic": (C.c_int, [C.POINTER(C.c_void_p)] + [C.c_int] * 5),
+    "cfx_policy_create_classic": (C.c_int, [C.POINTER(C.c_void_p)] + [C.c_int] * 6),
     "cfx_classic_expand_obs": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "cfx_classic_done_to_terminals": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "cfx_expand_obs": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
@@ -234,9 +234,8 @@ class Policy:
         self.rec_bytes = CLASSIC_REC if game == "classic" else REC
         prec = PREC_NAMES[precision] if isinstance(precision, str) else int(precision)
         h = C.c_void_p()
-        if game == "classic":     # 148-byte records, gather encoder; fp32 only
-            assert prec == PREC_FP32, "the classic game is built for precision fp32 only"
-            check(lib().cfx_policy_create_classic(C.byref(h), device, n, hidden, layers, actions))
+        if game == "classic":     # 148-byte records, 1345 features
+            check(lib().cfx_policy_create_classic(C.byref(h), device, n, hidden, layers, actions, prec))
         else:
             check(lib().cfx_policy_create(C.byref(h), device, n, hidden, layers, actions, prec))
         self.h = h.value

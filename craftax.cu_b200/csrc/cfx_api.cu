@@ -73,7 +73,7 @@ static int policy_refresh_mirrors(cfx_policy* p, cudaStream_t st) {
 
 static int policy_ensure_fused(cfx_policy* p) {
     if (p->precision == CFX_PREC_FP32) return CFX_OK;
-    if (p->game != CFX_GAME_FULL || !fused_supported(p->H, p->L, p->A, p->precision)) {
+    if (!fused_supported(p->H, p->L, p->A, p->precision, p->game)) {
         set_error("precision %d is not built for hidden=%d layers=%d actions=%d", p->precision,
                   p->H, p->L, p->A);
         return CFX_ERR_UNSUPPORTED;
@@ -82,7 +82,7 @@ static int policy_ensure_fused(cfx_policy* p) {
         fused_destroy(p->fused);
         p->fused = nullptr;
     }
-    return fused_create(&p->fused, p->device, p->n, p->H, p->L, p->A, p->precision, p->state);
+    return fused_create(&p->fused, p->device, p->n, p->H, p->L, p->A, p->precision, p->state, p->game);
 }
 
 extern "C" {
@@ -104,9 +104,8 @@ int cfx_policy_create(cfx_policy** out, int device, int num_envs, int hidden, in
 }
 
 int cfx_policy_create_classic(cfx_policy** out, int device, int num_envs, int hidden, int layers,
-                              int num_actions) {
-    return policy_create(out, device, num_envs, hidden, layers, num_actions, CFX_PREC_FP32,
-                         CFX_GAME_CLASSIC);
+                              int num_actions, int precision) {
+    return policy_create(out, device, num_envs, hidden, layers, num_actions, precision, CFX_GAME_CLASSIC);
 }
 
 size_t cfx_classic_param_count(int hidden, int layers, int num_actions) {

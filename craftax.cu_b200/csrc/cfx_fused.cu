@@ -39,7 +39,6 @@ using namespace umma;
 namespace fused {
 
 constexpr int kH = 256;          // hidden units
-constexpr int kA = 43;           // actions
 constexpr int kTile = 128;       // envs per tile
 constexpr int kMaxLayers = 4;
 constexpr int kSliceUnits = 64;  // hidden units per gate slice (N = 192: zh|zg|zp)
@@ -47,9 +46,24 @@ constexpr int kSlices = kH / kSliceUnits;  // 4
 constexpr int kHalfUnits = 32;   // units of a slice handled by one worker warpgroup
 constexpr int kStateItems = kH / kHalfUnits;  // 8 state boxes (128 rows x 32 units) per layer
 constexpr int kKBlocks = kH / 64;          // 4 K blocks of 64 per 256-wide operand
-constexpr int kEncChunks = 14;   // 12 full map chunks, 1 partial (24 bytes), 1 tail (51 floats)
-constexpr int kRecFills = 13;    // record ring fills per tile: one per map chunk (the tail has its own buffer)
-constexpr int kHeadN = 48;       // 43 logits + value, padded to a multiple of 16
+constexpr int kHeadMax = 64;     // head accumulator columns reserved in tensor memory
+
+// What differs between the two games the kernel is instantiated for.
+//  full game (craftax_full.cu): 996-byte record = 792 map bytes + 51 raw floats, 843 features
+//    in 14 chunks of 64 (12 full map chunks, one of 24 bytes, one with the 51 floats), records
+//    fetched chunk by chunk through a ring (13 fills; the tail has a buffer of its own), 43 actions;
+//  classic game (craftax_classic.cu): 148-byte record, 1345 one-hot / scalar features in 22
+//    chunks, the whole tile's records (18.5 KB) fetched by one TMA box, 17 actions.
+template <int GAME> struct Gm;
+template <> struct Gm<CFX_GAME_FULL> {
+    static constexpr int kA = 43, kEncChunks = 14, kRecFills = 13, kRecBytes = kRec;
+    static constexpr int kHeadSingle = 48, kHeadPair = 64;   // head MMA N (pairs need N % 32 == 0)
+};
+template <> struct Gm<CFX_GAME_CLASSIC> {
+    static constexpr int kA = 17, kEncChunks = 22, kRecFills = 0, kRecBytes = kClassicRec;
+    static constexpr int kHeadSingle = 32, kHeadPair = 32;
+};
+constexpr int kMaxEncChunks = 22;
 
 constexpr int kNBMax = 8;        // weight ring slots (one stage each): see Cfg
 #ifndef CFX_PAIR_NB
@@ -73,11 +87,14 @@ constexpr int kAexpSlots = 8;
 // of one 64-unit slice (192 rows, 24 KB); head stage = all four K blocks (24 KB).
 constexpr int kEncStageBytes = 128 * 128;            // block: [128 units][64 K] 16-bit
 constexpr int kGateStageBytes = 3 * kSliceUnits * 128;  // block: [96 rows][64 K]
-constexpr int kHeadStageBytes = kHeadN * 128;        // block: [48 rows][64 K]
-constexpr int kHeadPairBytes = 2 * kKBlocks * 32 * 128;  // pair layout: [half][K block][32 rows][64 K]
-constexpr int kEncStages = kEncChunks * 2;           // encoder blocks in the image
-constexpr int kEncCopyBytes = 2 * kEncStageBytes, kGateCopyBytes = kGateStageBytes,
-              kHeadCopyBytes = kKBlocks * kHeadStageBytes;
+constexpr int kEncCopyBytes = 2 * kEncStageBytes, kGateCopyBytes = kGateStageBytes;
+// head stage: one CTA per tile [K block][rows][64 K]; pairs [half][K block][rows / 2][64 K]
+template <int GAME> __host__ __device__ constexpr int head_bytes(bool pair) {
+    return kKBlocks * (pair ? Gm<GAME>::kHeadPair : Gm<GAME>::kHeadSingle) * 128;
+}
+template <int GAME> __host__ __device__ constexpr size_t enc_bytes() {
+    return (size_t)Gm<GAME>::kEncChunks * kEncCopyBytes;
+}
 
 // A lane that handles every G-th item of an N-slot ring waits on its slot's "empty" barrier
 // by phase parity; that is only sound while it cannot run two phases ahead of the slot,
@@ -88,9 +105,8 @@ constexpr int kEncCopyBytes = 2 * kEncStageBytes, kGateCopyBytes = kGateStageByt
 // state ring (4 slots, slices alternate) satisfy this; each weight ring has one consumer.
 
 
-__host__ __device__ constexpr size_t image_bytes(int L) {   // room for either head layout
-    return (size_t)kEncStages * kEncStageBytes + (size_t)L * kSlices * kKBlocks * kGateStageBytes +
-           (size_t)kHeadPairBytes;
+template <int GAME> __host__ __device__ constexpr size_t image_bytes(int L) {   // room for either head layout
+    return enc_bytes<GAME>() + (size_t)L * kSlices * kKBlocks * kGateStageBytes + (size_t)kKBlocks * kHeadMax * 128;
 }
 
 // TMEM columns
@@ -114,27 +130,29 @@ enum Bar {
 //    while the gate layers run; REC_DONE and S_DONE order the two uses per tile);
 //  CTA pair (cta_group::2): every CTA stages half of each weight stage, 4 x 16 KB; the 64 KB
 //    this frees hold a record ring of its own, 6 x 10 KB, that runs ahead into the next tile.
-template <bool PAIR> struct Cfg {
+template <bool PAIR, int GAME = CFX_GAME_FULL> struct Cfg {
     static constexpr int kNB = PAIR ? CFX_PAIR_NB : 4;
     static constexpr int kBSlot = PAIR ? 16384 : 32768;
     static constexpr int kWLanes = kNB;                  // one lane per slot
-    static constexpr int kHeadRows = PAIR ? 64 : 48;     // N of the head MMA (pairs need N % 32 == 0)
-    static constexpr int kHeadKbBytes = (PAIR ? 32 : 48) * 128;   // one K block of the head rows a CTA stages
+    static constexpr int kHeadRows = PAIR ? Gm<GAME>::kHeadPair : Gm<GAME>::kHeadSingle;   // N of the head MMA
+    static constexpr int kHeadKbBytes = (PAIR ? kHeadRows / 2 : kHeadRows) * 128;   // one K block of the head rows a CTA stages
     static constexpr int kM = PAIR ? 256 : 128;
     static constexpr int kNS = PAIR ? CFX_PAIR_NS : 4;     // state ring slots: even, so that slot parity = warpgroup
-    static constexpr bool kAlias = PAIR ? (CFX_PAIR_ALIAS != 0) : true;
-    static constexpr int kNR = PAIR ? CFX_PAIR_NR : 4;
+    // record ring inside the state slots (full game only: the classic records need no ring)
+    static constexpr bool kAlias = GAME == CFX_GAME_FULL && (PAIR ? (CFX_PAIR_ALIAS != 0) : true);
+    static constexpr int kNR = GAME != CFX_GAME_FULL ? 0 : (PAIR ? CFX_PAIR_NR : 4);
     static constexpr int kRStride = kAlias ? kSSlot : kRSlot;
     static constexpr int kOffB = 0;
     static constexpr int kOffS = kOffB + kNB * kBSlot;
     static constexpr int kOffR = kAlias ? kOffS : kOffS + kNS * kSSlot;
     static constexpr int kOffT = kAlias ? kOffS + kNS * kSSlot : kOffR + kNR * kRSlot;
     static constexpr int kOffBias = kOffT + kTailBytes;       // b_enc[256] fp32, b_av[48] fp32
-    static constexpr int kOffBars = kOffBias + (kH + kHeadN) * 4;
+    static constexpr int kOffBars = kOffBias + (kH + kHeadMax) * 4;
     static constexpr int kOffMisc = kOffBars + NUM_BARS * 8;  // tmem base, abort flag
     static constexpr int kSmemBytes = kOffMisc + 16 + 1024;   // + alignment slack
     static_assert(kNB <= kNBMax && kNR <= kNRMax && kNS <= kNSMax && kNS % 2 == 0 && kNS <= kStateItems &&
-                      kNR * kRSlot <= kNS * kSSlot && kSmemBytes <= 232448 && (!kAlias || kNR == kNS), "layout");
+                      kNR * kRSlot <= kNS * kSSlot && kSmemBytes <= 232448 && (!kAlias || kNR == kNS) &&
+                      kHeadRows <= kHeadMax && 128 * Gm<GAME>::kRecBytes <= kTailBytes + 128 * kRec, "layout");
 };
 
 constexpr int kWorkerWarp0 = 4, kNumWarps = 12, kThreads = kNumWarps * 32;
@@ -164,6 +182,7 @@ struct Params {
     uint32_t* status;
     uint64_t seed, env_offset;
     int n, L, num_tiles;
+    int rec_bytes;        // bytes of one record (996 full game, 148 classic)
     int num_tiles_loop;   // trip bound of the tile loops: num_tiles, rounded up to even for CTA pairs
     size_t off_b_enc, off_b_a, off_b_v;
     long long* timeline;  // debug builds only (CFX_TIMELINE): per-role (tag, clock) log of block 0
@@ -178,7 +197,8 @@ __host__ __device__ inline uint32_t sw128_off(uint32_t row, uint32_t byte_col) {
 
 // Encoder K order: K' in [0,800) = the 792 map bytes then 8 zero columns; K' in [800,864) =
 // the 51 tail floats then 13 zero columns.  Returns the feature index or -1 for padding.
-__host__ __device__ inline int enc_feature(int chunk, int c) {
+template <int GAME> __host__ __device__ inline int enc_feature(int chunk, int c) {
+    if (GAME == CFX_GAME_CLASSIC) return chunk * 64 + c < kClassicObs ? chunk * 64 + c : -1;
     if (chunk < 12) return chunk * 64 + c;
     if (chunk == 12) return c < 24 ? 768 + c : -1;
     return c < kTail ? kMap + c : -1;
@@ -197,49 +217,46 @@ __device__ inline __nv_bfloat16 to16<__nv_bfloat16>(float v) {
 
 // One thread per 16-bit element of the image.  Stage order = consumption order of the
 // kernel: encoder (chunk-major, unit halves), gate layers (layer, slice, K block), head.
-template <typename T16>
+template <typename T16, int GAME>
 __global__ void k_pack_image(const float* __restrict__ params, uint8_t* __restrict__ image, int L,
                              size_t off_w_gru, size_t off_w_a, size_t off_w_v, int pair) {
-    const size_t total = image_bytes(L) / 2;
+    constexpr int kA = Gm<GAME>::kA;
+    const size_t total = image_bytes<GAME>(L) / 2;
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     size_t byte = idx * 2;
-    const size_t enc_bytes = (size_t)kEncStages * kEncStageBytes;
+    const size_t enc_b = enc_bytes<GAME>();
     const size_t gate_bytes = (size_t)L * kSlices * kKBlocks * kGateStageBytes;
     float v = 0.0f;
     uint32_t row, c;
     uint8_t* stage;
-    if (byte < enc_bytes) {
+    if (byte < enc_b) {
         const int s = (int)(byte / kEncStageBytes), e = (int)((byte % kEncStageBytes) / 2);
         row = e / 64; c = e % 64;
         stage = image + (size_t)s * kEncStageBytes;
         const int chunk = s / 2, half = s % 2;
-        const int f = enc_feature(chunk, c);
+        const int f = enc_feature<GAME>(chunk, c);
         if (f >= 0) v = params[(size_t)f * kH + half * 128 + row];
-    } else if (byte < enc_bytes + gate_bytes) {
-        const size_t b = byte - enc_bytes;
+    } else if (byte < enc_b + gate_bytes) {
+        const size_t b = byte - enc_b;
         const int s = (int)(b / kGateStageBytes), e = (int)((b % kGateStageBytes) / 2);
         row = e / 64; c = e % 64;
-        stage = image + enc_bytes + (size_t)s * kGateStageBytes;
+        stage = image + enc_b + (size_t)s * kGateStageBytes;
         const int kb = s % kKBlocks, j = (s / kKBlocks) % kSlices, l = s / (kKBlocks * kSlices);
         const int gate = row / kSliceUnits, unit = j * kSliceUnits + row % kSliceUnits;
         v = params[off_w_gru + ((size_t)l * 3 * kH + gate * kH + unit) * kH + kb * 64 + c];
-    } else if (!pair) {
-        const size_t b = byte - enc_bytes - gate_bytes;
-        if (b >= (size_t)kKBlocks * kHeadStageBytes) return;
-        const int kb = (int)(b / kHeadStageBytes), e = (int)((b % kHeadStageBytes) / 2);
-        row = e / 64; c = e % 64;
-        stage = image + enc_bytes + gate_bytes + (size_t)kb * kHeadStageBytes;
-        if (row < kA) v = params[off_w_a + (size_t)row * kH + kb * 64 + c];
-        else if (row == kA) v = params[off_w_v + kb * 64 + c];
     } else {
-        // pair layout: CTA r of a pair stages head rows [32 r, 32 r + 32): [r][K block][32][64 K]
-        const size_t b = byte - enc_bytes - gate_bytes;
-        const int blk = (int)(b / 4096), e = (int)((b % 4096) / 2);
-        const int r = blk / kKBlocks, kb = blk % kKBlocks;
+        // head.  One CTA per tile: [K block][rows][64 K].  CTA pairs: CTA r stages head rows
+        // [r rows/2, (r + 1) rows/2): [r][K block][rows / 2][64 K].
+        const size_t b = byte - enc_b - gate_bytes;
+        if (b >= (size_t)head_bytes<GAME>(pair != 0)) return;
+        const int rows = pair ? Gm<GAME>::kHeadPair / 2 : Gm<GAME>::kHeadSingle;   // rows of one block
+        const int blk_bytes = rows * 128;
+        const int blk = (int)(b / blk_bytes), e = (int)((b % blk_bytes) / 2);
+        const int r = pair ? blk / kKBlocks : 0, kb = blk % kKBlocks;
         row = e / 64; c = e % 64;
-        stage = image + enc_bytes + gate_bytes + (size_t)blk * 4096;
-        const int grow = 32 * r + (int)row;
+        stage = image + enc_b + gate_bytes + (size_t)blk * blk_bytes;
+        const int grow = rows * r + (int)row;
         if (grow < kA) v = params[off_w_a + (size_t)grow * kH + kb * 64 + c];
         else if (grow == kA) v = params[off_w_v + kb * 64 + c];
     }
@@ -252,6 +269,7 @@ struct Op16;
 template <>
 struct Op16<__half> {
     static constexpr uint32_t kFmt = kFmtF16;
+    static constexpr uint32_t kOne = 0x3C00u;   // 1.0
     // two floats -> packed pair, `lo` in the low half (even K index)
     static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
         uint32_t r;
@@ -275,6 +293,7 @@ struct Op16<__half> {
 template <>
 struct Op16<__nv_bfloat16> {
     static constexpr uint32_t kFmt = kFmtBF16;
+    static constexpr uint32_t kOne = 0x3F80u;   // 1.0
     static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
         uint32_t r;
         asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
@@ -316,8 +335,8 @@ __device__ __forceinline__ void mingru_cell(float zh, float zg, float zp, float 
 struct Smem {
     uint8_t* base;
     int off_s, off_r, r_stride, off_t, off_bias, off_bars, off_misc, b_slot_bytes;
-    template <bool PAIR> __device__ __forceinline__ void layout() {
-        using C = Cfg<PAIR>;
+    template <bool PAIR, int GAME> __device__ __forceinline__ void layout() {
+        using C = Cfg<PAIR, GAME>;
         off_s = C::kOffS; off_r = C::kOffR; r_stride = C::kRStride; off_t = C::kOffT;
         off_bias = C::kOffBias; off_bars = C::kOffBars; off_misc = C::kOffMisc; b_slot_bytes = C::kBSlot;
     }
@@ -417,6 +436,7 @@ __device__ __forceinline__ T* chk_ptr(T* p, const char* what) {
 __device__ __forceinline__ int rec_owner(int kc) { return (kc & 1) ^ 1; }
 template <int NR> __device__ __forceinline__ int rec_slot(int kc) { return kc % NR; }
 template <int NR> __device__ __forceinline__ uint32_t rec_phase(uint32_t it, int kc) {   // phase index of fill kc
+    constexpr int kRecFills = Gm<CFX_GAME_FULL>::kRecFills;
     constexpr uint32_t fills0 = (kRecFills + NR - 1) / NR, fills = kRecFills / NR;
     static_assert(NR % 2 == 0 && fills0 == fills + 1 && kRecFills % NR == 1, "slot 0 takes the odd fill");
     return ((kc % NR) == 0 ? fills0 : fills) * it + (uint32_t)(kc / NR);
@@ -448,7 +468,7 @@ __device__ __forceinline__ void l2_prefetch_for_box(const Params& P, int tile, i
         const int t = tile + gridDim.x;
         if (t >= P.num_tiles) return;
         const int rows = min(kTile, P.n - t * kTile);
-        l2_prefetch_rows(P.records + (size_t)t * kTile * kRec, (uint32_t)rows * kRec, j);
+        l2_prefetch_rows(P.records + (size_t)t * kTile * P.rec_bytes, (uint32_t)rows * P.rec_bytes, j);
         l2_prefetch_rows(reinterpret_cast<const uint8_t*>(P.state + (size_t)t * kTile * kH),
                          (uint32_t)rows * kH * 4, j);
     }
@@ -460,12 +480,13 @@ __device__ __forceinline__ void l2_prefetch_for_box(const Params& P, int tile, i
 // One lane per ring slot.  In a CTA pair every CTA stages its own half of the rows of each
 // stage (the halves are contiguous in the image); the odd CTA waits for its copy to land and
 // then arrives on the even CTA's "full" barrier, where the MMA thread waits.
-template <bool PAIR>
+template <bool PAIR, int GAME>
 __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& P, int lane,
                                                   uint32_t rank, uint32_t bar0_cta0) {
-    using C = Cfg<PAIR>;
+    using C = Cfg<PAIR, GAME>;
+    constexpr int kEncChunks = Gm<GAME>::kEncChunks;
     const int stages_gate = P.L * kSlices * kKBlocks;
-    const size_t enc_bytes = (size_t)kEncStages * kEncStageBytes;
+    const size_t enc_bytes = fused::enc_bytes<GAME>();
     uint32_t cnt = 0;
     TL_INIT(3);
     for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x) {
@@ -478,7 +499,7 @@ __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& 
             } else if (s < kEncChunks + stages_gate) {
                 bytes = kGateCopyBytes; off = enc_bytes + (size_t)(s - kEncChunks) * kGateCopyBytes;
             } else {
-                bytes = PAIR ? kHeadPairBytes : kHeadCopyBytes;
+                bytes = head_bytes<GAME>(PAIR);
                 off = enc_bytes + (size_t)stages_gate * kGateCopyBytes;
             }
             if (PAIR) {
@@ -507,12 +528,22 @@ __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& 
 // aligned row); env 4g+i of a tile sits in row g at byte 996 i.  A 64-byte feature chunk of
 // all 128 envs is fetched as four boxes (one per i) of 32 rows x 80 bytes starting at the
 // 16-byte boundary below 996 i + 64 c; the 204 tail bytes take three more such box sets.
-template <bool PAIR>
+template <bool PAIR, int GAME>
 __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& P, int lane) {
-    using C = Cfg<PAIR>;
+    using C = Cfg<PAIR, GAME>;
     constexpr int kNR = C::kNR;
+    constexpr int kRecFills = Gm<GAME>::kRecFills;
     uint32_t it = 0;
-    if (lane < kNR) {
+    if constexpr (GAME == CFX_GAME_CLASSIC) {
+        // classic: the records of the whole tile are one box, 32 rows of four 148-byte records
+        // (a [n/4][148] array of 32-bit words), into the buffer the full game uses for its tail
+        const uint32_t dst = smem_u32(sm.t_buf());
+        for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
+            CFX_WAIT(T_EMPTY, (it & 1) ^ 1, W_T_EMPTY);
+            mbar_arrive_expect_tx(sm.bar(T_FULL), 128 * kClassicRec);
+            tensor_g2s_2d(dst, &P.rec_map, 0, tile * 32, sm.bar(T_FULL));
+        }
+    } else if (lane < kNR) {
         // lane `lane` owns ring slot `lane` and issues all four boxes of the fills that land on it
         const uint32_t slot_addr = smem_u32(sm.r_slot(lane));
         for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
@@ -559,9 +590,9 @@ __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& 
 // replaced the contents with the new state, write it back (rows beyond n are clipped by the
 // tensor map), and only then load the next box into the slot.  One lane per slot needs no
 // "slot empty" barrier and saves a hand-off.
-template <bool PAIR>
+template <bool PAIR, int GAME>
 __device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P, int lane) {
-    using C = Cfg<PAIR>;
+    using C = Cfg<PAIR, GAME>;
     constexpr int kNS = C::kNS;
     uint32_t cnt = 0, uses = 0, it = 0;
     const uint32_t slot_addr = smem_u32(sm.s_slot(lane));
@@ -619,9 +650,10 @@ __device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P,
         if (PAIR) mma_commit_pair(bar);  \
         else mma_commit(bar);            \
     } while (0)
-template <typename T16, bool PAIR>
+template <typename T16, bool PAIR, int GAME>
 __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32_t tmem) {
-    using C = Cfg<PAIR>;
+    using C = Cfg<PAIR, GAME>;
+    constexpr int kEncChunks = Gm<GAME>::kEncChunks;
     constexpr int kNB = C::kNB, kBSlot = C::kBSlot;
     constexpr uint32_t fmt = Op16<T16>::kFmt;
     constexpr uint32_t idesc_enc = make_idesc(fmt, C::kM, kH);
@@ -668,8 +700,11 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
             {
                 if (kc == 0) MMA_TS(tmem + kColAcc, a_col, bd, idesc_enc, 0);
                 else MMA_TS(tmem + kColAcc, a_col, bd, idesc_enc, 1);
-                MMA_TS(tmem + kColAcc, a_col + 8, bd + 2, idesc_enc, 1);
-                if (kc != 12) {  // chunk 12 carries 24 map bytes: two K steps
+                // short chunks: full game chunk 12 carries 24 map bytes (two K steps), the classic
+                // game's last chunk one feature (one K step)
+                const int ksteps = GAME == CFX_GAME_FULL ? (kc == 12 ? 2 : 4) : (kc == kEncChunks - 1 ? 1 : 4);
+                if (ksteps > 1) MMA_TS(tmem + kColAcc, a_col + 8, bd + 2, idesc_enc, 1);
+                if (ksteps > 2) {
                     MMA_TS(tmem + kColAcc, a_col + 16, bd + 4, idesc_enc, 1);
                     MMA_TS(tmem + kColAcc, a_col + 24, bd + 6, idesc_enc, 1);
                 }
@@ -748,10 +783,12 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
 // ------------------------------------------------------------------ worker role
 // Eight warps, two per TMEM lane quarter (wg 0 / wg 1); thread (quarter, lane) owns env row
 // quarter*32 + lane of the tile in every phase.
-template <typename T16, bool PAIR>
+template <typename T16, bool PAIR, int GAME>
 __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uint32_t tmem,
                                             int warp, int lane, uint32_t bar0_cta0) {
     using Op = Op16<T16>;
+    constexpr int kA = Gm<GAME>::kA, kEncChunks = Gm<GAME>::kEncChunks, kRecFills = Gm<GAME>::kRecFills;
+    constexpr int kHeadCols = (kA + 1 + 15) / 16 * 16;   // head accumulator columns that are read
     // barriers the MMA thread waits on live in the even CTA of a pair
     auto arrive_mma = [&](int barid) {
         if (PAIR) mbar_arrive_cluster(bar0_cta0 + 8u * (uint32_t)barid);
@@ -778,16 +815,60 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
         // wg 1 converts the even chunks, wg 0 the odd ones and the tail; a warp writes all 32
         // columns of its rows.
         for (int kc = 0; kc < kEncChunks; kc++) {
-            if ((kc < kRecFills ? rec_owner(kc) : 0) != wg) continue;
+            // even chunks: wg 1, odd chunks: wg 0; the full game's tail chunk: wg 0
+            if ((GAME == CFX_GAME_CLASSIC || kc < kRecFills ? rec_owner(kc) : 0) != wg) continue;
             const uint32_t acnt = it * kEncChunks + kc;
             const int as = acnt % kAexpSlots;
             CFX_WAITW(AEXP_EMPTY + as, ((acnt / kAexpSlots) & 1) ^ 1, W_AEXP_EMPTY);
             if (tl_on) TLB(2, 0x70000 | kc);
             tc_fence_after_sync();
             uint32_t regs[32];
-            if (kc < 13) {
-                const int slot = rec_slot<Cfg<PAIR>::kNR>(kc);
-                CFX_WAITW(R_FULL + slot, rec_phase<Cfg<PAIR>::kNR>(it, kc) & 1, W_R_FULL);
+            if constexpr (GAME == CFX_GAME_CLASSIC) {
+                // The tile's records are one buffer.  The 1323 one-hot features of a record are
+                // a bit stream, 21 bits per view cell (17 block ids + 4 mob bits); a chunk is a
+                // 64-bit window of it, built from at most four cells, and every bit becomes
+                // 1.0 or 0.0 in the operand type.  Chunk 20 ends with the 21 scalar features
+                // (feature order of expand_obs_kernel, craftax_classic.cu:1265-1301), chunk 21
+                // holds the sleeping flag alone.
+                if (kc <= 1) CFX_WAITW(T_FULL, it & 1, W_T_FULL);   // first chunk of either warpgroup
+                const uint8_t* rp = sm.t_buf() + gi * (4 * kClassicRec) + ii * kClassicRec;
+                auto cell_bits = [&](int cell) -> uint64_t {
+                    if (cell >= kClassicCells) return 0ull;
+                    const uint32_t blk = rp[cell], mob = rp[kClassicCells + cell];
+                    return (uint64_t)((blk < (uint32_t)kClassicBlocks ? (1u << blk) : 0u) | ((mob & 15u) << kClassicBlocks));
+                };
+                const int cell0 = (64 * kc) / 21, off0 = 64 * kc - 21 * cell0;
+                uint64_t w = 0;
+                if (kc < kEncChunks - 1)
+                    w = (cell_bits(cell0) >> off0) | (cell_bits(cell0 + 1) << (21 - off0)) |
+                        (cell_bits(cell0 + 2) << (42 - off0)) | (cell_bits(cell0 + 3) << (63 - off0));
+                const uint32_t wlo = (uint32_t)w, whi = (uint32_t)(w >> 32);
+#pragma unroll
+                for (int q = 0; q < 16; q++) {
+                    regs[q] = ((wlo >> (2 * q)) & 1u) * Op::kOne | ((wlo >> (2 * q + 1)) & 1u) * (Op::kOne << 16);
+                    regs[16 + q] = ((whi >> (2 * q)) & 1u) * Op::kOne | ((whi >> (2 * q + 1)) & 1u) * (Op::kOne << 16);
+                }
+                if (kc == kEncChunks - 2) {   // features 1280..1343: 43 one-hot bits, then 21 scalars
+                    float sc[22];
+#pragma unroll
+                    for (int j2 = 0; j2 < 16; j2++) sc[j2] = (float)(int8_t)rp[2 * kClassicCells + j2] / 10.0f;
+                    const int dir = (int8_t)rp[2 * kClassicCells + 16];
+#pragma unroll
+                    for (int d = 0; d < 4; d++) sc[16 + d] = dir == d + 1 ? 1.0f : 0.0f;
+                    sc[20] = *reinterpret_cast<const float*>(rp + 2 * kClassicCells + 18);
+                    sc[21] = 0.0f;
+                    regs[21] = (regs[21] & 0xFFFFu) | (Op::pack(0.0f, sc[0]) & 0xFFFF0000u);
+#pragma unroll
+                    for (int q = 22; q < 32; q++) regs[q] = Op::pack(sc[2 * (q - 22) + 1], sc[2 * (q - 22) + 2]);
+                } else if (kc == kEncChunks - 1) {   // feature 1344: sleeping
+                    regs[0] = rp[2 * kClassicCells + 17] != 0 ? Op::kOne : 0u;
+                }
+                __syncwarp();
+                if (kc >= kEncChunks - 2 && lane == 0) mbar_arrive(sm.bar(T_EMPTY));   // last chunk of this warp
+            } else if (kc < 13) {
+                constexpr int kNRw = Cfg<PAIR, GAME>::kNR;
+                const int slot = rec_slot<kNRw>(kc);
+                CFX_WAITW(R_FULL + slot, rec_phase<kNRw>(it, kc) & 1, W_R_FULL);
                 if (tl_on) TLB(3, 0x80000 | kc);
                 const uint8_t* src = sm.r_slot(slot) + rec_row_off + ((kRec * ii) & 15);
 #ifdef CFX_ABL_NOEXPAND
@@ -825,7 +906,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sm.bar(T_EMPTY));
             }
-            if (Cfg<PAIR>::kAlias && (kc == kLastWg1 || kc == kEncChunks - 1) && lane == 0)
+            if (Cfg<PAIR, GAME>::kAlias && (kc == kLastWg1 || kc == kEncChunks - 1) && lane == 0)
                 mbar_arrive(sm.bar(REC_DONE));
             {
                 uint32_t lo[16], hi[16];
@@ -879,7 +960,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 tc_fence_after_sync();
                 const int box = 2 * j + wg;
                 const uint32_t scnt = (it * P.L + l) * kStateItems + box;
-                constexpr int kNS = Cfg<PAIR>::kNS;
+                constexpr int kNS = Cfg<PAIR, GAME>::kNS;
                 const int slot = scnt % kNS;
                 const uint32_t gcol = tmem + lane_base + kColG + kHalfUnits * wg;
                 uint8_t* rbase = sm.s_slot(slot) + (row >> 3) * 1024 + (row & 7) * 128;
@@ -965,9 +1046,9 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
         if (tl_on) TLB(10, 0xE0000);
         tc_fence_after_sync();
         if (wg == 0) {
-            uint32_t hv[kHeadN];
+            uint32_t hv[kHeadCols];
 #pragma unroll
-            for (int b = 0; b < kHeadN / 16; b++) {
+            for (int b = 0; b < kHeadCols / 16; b++) {
                 uint32_t t[16];
                 tmem_ld16(tmem + lane_base + kColHead + 16 * b, t);
 #pragma unroll
@@ -986,7 +1067,12 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
 #pragma unroll
                 for (int a = 0; a < kA; a++) logits[a] = __uint_as_float(hv[a]) + bias[kH + a];
                 const float value = __uint_as_float(hv[kA]) + bias[kH + kA];
-                if (P.logits_av != nullptr) {
+                if (P.logits_av != nullptr && (kA + 1) % 4 != 0) {
+                    float* dst = P.logits_av + (size_t)env * (kA + 1);   // rows are not 16-byte aligned
+#pragma unroll
+                    for (int a = 0; a < kA; a++) dst[a] = logits[a];
+                    dst[kA] = value;
+                } else if (P.logits_av != nullptr) {
                     float4* dst = reinterpret_cast<float4*>(P.logits_av + (size_t)env * (kA + 1));
 #pragma unroll
                     for (int q = 0; q < (kA + 1) / 4; q++) {
@@ -1019,14 +1105,15 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
 // of a pair owns tile 2 c + r in every respect (records, state, expand, cell, sampler) except
 // that the MMA thread of the even CTA issues one 256-row MMA for both tiles and every CTA
 // stages only its half of the weight rows.
-template <typename T16, bool PAIR>
+template <typename T16, bool PAIR, int GAME>
 __global__ void __launch_bounds__(kThreads, 1)
 k_policy_fused(const __grid_constant__ Params P) {
-    using C = Cfg<PAIR>;
+    using C = Cfg<PAIR, GAME>;
+    constexpr int kA = Gm<GAME>::kA;
     extern __shared__ uint8_t smem_raw[];
     Smem sm;
     sm.base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    sm.layout<PAIR>();
+    sm.template layout<PAIR, GAME>();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #ifdef CFX_PROFILE
     const uint64_t pf_entry = global_timer_ns();
@@ -1056,7 +1143,7 @@ k_policy_fused(const __grid_constant__ Params P) {
         init(H_EMPTY, 1, 4 * both);
         init(REC_DONE, 1, 8);
         init(T_FULL, 1, 1);
-        init(T_EMPTY, 1, 4);
+        init(T_EMPTY, 1, GAME == CFX_GAME_CLASSIC ? 8 : 4);   // classic: both warpgroups read the buffer
         *sm.abort_flag() = 0;
         fence_mbar_init();
     }
@@ -1073,7 +1160,7 @@ k_policy_fused(const __grid_constant__ Params P) {
         prefetch_tensormap(&P.rec_map);
         for (int l = 0; l < P.L; l++) prefetch_tensormap(&P.state_map[l]);
     }
-    for (int i = tid; i < kH + kHeadN; i += kThreads) {
+    for (int i = tid; i < kH + kHeadMax; i += kThreads) {
         float v = 0.0f;
         if (i < kH) v = P.params[P.off_b_enc + i];
         else if (i - kH < kA) v = P.params[P.off_b_a + (i - kH)];
@@ -1092,15 +1179,15 @@ k_policy_fused(const __grid_constant__ Params P) {
 #endif
 
     if (warp == 0) {
-        if (lane < C::kWLanes) role_weight_loads<PAIR>(sm, P, lane, rank, bar0_cta0);
+        if (lane < C::kWLanes) role_weight_loads<PAIR, GAME>(sm, P, lane, rank, bar0_cta0);
     } else if (warp == 1) {
-        if (lane == 0 && rank == 0) role_mma<T16, PAIR>(sm, P, tmem);
+        if (lane == 0 && rank == 0) role_mma<T16, PAIR, GAME>(sm, P, tmem);
     } else if (warp == 2) {
-        if (lane < C::kNR + 1) role_record_loads<PAIR>(sm, P, lane);
+        if (lane < C::kNR + 1) role_record_loads<PAIR, GAME>(sm, P, lane);
     } else if (warp == 3) {
-        if (lane < C::kNS) role_state_ring<PAIR>(sm, P, lane);
+        if (lane < C::kNS) role_state_ring<PAIR, GAME>(sm, P, lane);
     } else {
-        role_worker<T16, PAIR>(sm, P, tmem, warp, lane, bar0_cta0);
+        role_worker<T16, PAIR, GAME>(sm, P, tmem, warp, lane, bar0_cta0);
     }
 
     // common exit: every role ends here, also after a timed-out wait.  In a pair neither CTA
@@ -1168,6 +1255,7 @@ int fused_selftest_wait_timeout(unsigned limit_ms, unsigned* status_out) {
 // ------------------------------------------------------------------ host side
 struct FusedPlan {
     int device, n, H, L, A, precision;
+    int game = CFX_GAME_FULL;
     uint8_t* image = nullptr;
     uint32_t* status = nullptr;
     float* state = nullptr;
@@ -1179,14 +1267,33 @@ struct FusedPlan {
     long long* timeline = nullptr;
 };
 
-bool fused_supported(int H, int L, int A, int precision) {
-    return H == fused::kH && A == fused::kA && L >= 1 && L <= fused::kMaxLayers &&
+bool fused_supported(int H, int L, int A, int precision, int game) {
+    const int want_a = game == CFX_GAME_CLASSIC ? fused::Gm<CFX_GAME_CLASSIC>::kA : fused::Gm<CFX_GAME_FULL>::kA;
+    return H == fused::kH && A == want_a && L >= 1 && L <= fused::kMaxLayers &&
            (precision == CFX_PREC_F16 || precision == CFX_PREC_BF16);
 }
 
+// kernel instantiation and its shared-memory size for (operand type, launch mode, game)
+static const void* fused_kernel(int precision, int pair, int game, int* smem) {
+    const bool h = precision == CFX_PREC_F16;
+#define CFX_K(T, P, G)                                         \
+    do {                                                       \
+        *smem = fused::Cfg<P, G>::kSmemBytes;                  \
+        return (const void*)fused::k_policy_fused<T, P, G>;    \
+    } while (0)
+    if (game == CFX_GAME_CLASSIC) {
+        if (pair) { if (h) CFX_K(__half, true, CFX_GAME_CLASSIC); else CFX_K(__nv_bfloat16, true, CFX_GAME_CLASSIC); }
+        else { if (h) CFX_K(__half, false, CFX_GAME_CLASSIC); else CFX_K(__nv_bfloat16, false, CFX_GAME_CLASSIC); }
+    }
+    if (pair) { if (h) CFX_K(__half, true, CFX_GAME_FULL); else CFX_K(__nv_bfloat16, true, CFX_GAME_FULL); }
+    if (h) CFX_K(__half, false, CFX_GAME_FULL);
+    CFX_K(__nv_bfloat16, false, CFX_GAME_FULL);
+#undef CFX_K
+}
+
 int fused_create(FusedPlan** out, int device, int n, int H, int L, int A, int precision,
-                 float* state) {
-    if (!fused_supported(H, L, A, precision)) {
+                 float* state, int game) {
+    if (!fused_supported(H, L, A, precision, game)) {
         set_error("fused kernel: unsupported shape/precision");
         return CFX_ERR_UNSUPPORTED;
     }
@@ -1198,9 +1305,11 @@ int fused_create(FusedPlan** out, int device, int n, int H, int L, int A, int pr
     }
     FusedPlan* p = new FusedPlan();
     p->device = device; p->n = n; p->H = H; p->L = L; p->A = A; p->precision = precision;
+    p->game = game;
     p->state = state;
     p->sm_count = prop.multiProcessorCount;
-    cudaError_t e = cudaMalloc((void**)&p->image, fused::image_bytes(L));
+    cudaError_t e = cudaMalloc((void**)&p->image, game == CFX_GAME_CLASSIC ? fused::image_bytes<CFX_GAME_CLASSIC>(L)
+                                                                           : fused::image_bytes<CFX_GAME_FULL>(L));
     if (e == cudaSuccess) e = cudaMalloc((void**)&p->status, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(p->status, 0, sizeof(uint32_t));
     if (e != cudaSuccess) {
@@ -1216,13 +1325,11 @@ int fused_create(FusedPlan** out, int device, int n, int H, int L, int A, int pr
             return CFX_ERR_CUDA;
         }
     }
-    const void* kernels[4] = {(const void*)fused::k_policy_fused<__half, false>,
-                              (const void*)fused::k_policy_fused<__nv_bfloat16, false>,
-                              (const void*)fused::k_policy_fused<__half, true>,
-                              (const void*)fused::k_policy_fused<__nv_bfloat16, true>};
-    for (int k = 0; k < 4 && e == cudaSuccess; k++)
-        e = cudaFuncSetAttribute(kernels[k], cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 k < 2 ? fused::Cfg<false>::kSmemBytes : fused::Cfg<true>::kSmemBytes);
+    for (int pr = 0; pr < 2 && e == cudaSuccess; pr++) {
+        int smem = 0;
+        const void* k = fused_kernel(precision, pr, game, &smem);
+        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    }
     if (e != cudaSuccess) {
         fused_destroy(p);
         return cuda_fail(e, "cudaFuncSetAttribute", __FILE__, __LINE__);
@@ -1234,13 +1341,15 @@ int fused_create(FusedPlan** out, int device, int n, int H, int L, int A, int pr
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * (unsigned)(p->sm_count / 2));
         cfg.blockDim = dim3(fused::kThreads);
-        cfg.dynamicSmemBytes = fused::Cfg<true>::kSmemBytes;
+        int smem = 0;
+        const void* kpair = fused_kernel(precision, 1, game, &smem);
+        cfg.dynamicSmemBytes = smem;
         cudaLaunchAttribute at;
         at.id = cudaLaunchAttributeClusterDimension;
         at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
         cfg.attrs = &at; cfg.numAttrs = 1;
         int nc = 0;
-        if (cudaOccupancyMaxActiveClusters(&nc, kernels[precision == CFX_PREC_F16 ? 2 : 3], &cfg) == cudaSuccess && nc > 0) {
+        if (cudaOccupancyMaxActiveClusters(&nc, kpair, &cfg) == cudaSuccess && nc > 0) {
             p->pair = 1;
             p->max_pairs = nc;
         } else {
@@ -1253,13 +1362,15 @@ int fused_create(FusedPlan** out, int device, int n, int H, int L, int A, int pr
 
 int fused_refresh(FusedPlan* p, const float* params, cudaStream_t st) {
     p->params = params;
-    const ArenaLayout o = ArenaLayout::make(p->H, p->L, p->A);
-    const size_t total = fused::image_bytes(p->L) / 2;
+    const bool classic = p->game == CFX_GAME_CLASSIC;
+    const ArenaLayout o = ArenaLayout::make(p->H, p->L, p->A, classic ? kClassicObs : kObs);
+    const size_t total = (classic ? fused::image_bytes<CFX_GAME_CLASSIC>(p->L) : fused::image_bytes<CFX_GAME_FULL>(p->L)) / 2;
     const unsigned blocks = (unsigned)((total + 255) / 256);
-    if (p->precision == CFX_PREC_F16)
-        fused::k_pack_image<__half><<<blocks, 256, 0, st>>>(params, p->image, p->L, o.w_gru, o.w_a, o.w_v, p->pair);
-    else
-        fused::k_pack_image<__nv_bfloat16><<<blocks, 256, 0, st>>>(params, p->image, p->L, o.w_gru, o.w_a, o.w_v, p->pair);
+    const bool h = p->precision == CFX_PREC_F16;
+#define CFX_PACK(T, G) fused::k_pack_image<T, G><<<blocks, 256, 0, st>>>(params, p->image, p->L, o.w_gru, o.w_a, o.w_v, p->pair)
+    if (classic) { if (h) CFX_PACK(__half, CFX_GAME_CLASSIC); else CFX_PACK(__nv_bfloat16, CFX_GAME_CLASSIC); }
+    else { if (h) CFX_PACK(__half, CFX_GAME_FULL); else CFX_PACK(__nv_bfloat16, CFX_GAME_FULL); }
+#undef CFX_PACK
     CFX_CUDA(cudaGetLastError());
     return CFX_OK;
 }
@@ -1274,15 +1385,22 @@ int fused_forward(FusedPlan* p, const FusedArgs& a, cudaStream_t st, int* launch
         return CFX_ERR_INVALID;
     }
     fused::Params P;
-    if (!make_tmap_2d(&P.rec_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (void*)a.records,
-                      (uint64_t)p->n / 4, (uint64_t)kRec * 4, (uint64_t)kRec * 4, 32, 80,
-                      CU_TENSOR_MAP_SWIZZLE_NONE)) {
+    const bool classic = p->game == CFX_GAME_CLASSIC;
+    // records as rows of four: full game uint8 [n/4][3984], boxes of 32 rows x 80 bytes;
+    // classic uint32 [n/4][148] (592 bytes), one box of 32 rows x 148 words per tile
+    const bool ok_map = classic
+        ? make_tmap_2d(&P.rec_map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (void*)a.records, (uint64_t)p->n / 4,
+                       (uint64_t)kClassicRec, (uint64_t)kClassicRec * 4, 32, kClassicRec, CU_TENSOR_MAP_SWIZZLE_NONE)
+        : make_tmap_2d(&P.rec_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (void*)a.records, (uint64_t)p->n / 4,
+                       (uint64_t)kRec * 4, (uint64_t)kRec * 4, 32, 80, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (!ok_map) {
         set_error("fused forward: cuTensorMapEncodeTiled failed for the records");
         return CFX_ERR_CUDA;
     }
     for (int l = 0; l < p->L; l++) P.state_map[l] = p->state_map[l];
-    const ArenaLayout o = ArenaLayout::make(p->H, p->L, p->A);
+    const ArenaLayout o = ArenaLayout::make(p->H, p->L, p->A, classic ? kClassicObs : kObs);
     P.records = a.records;
+    P.rec_bytes = classic ? kClassicRec : kRec;
     P.state = a.state;
     P.image = p->image;
     P.params = p->params;
@@ -1305,30 +1423,26 @@ int fused_forward(FusedPlan* p, const FusedArgs& a, cudaStream_t st, int* launch
     P.off_b_a = o.b_a;
     P.off_b_v = o.b_v;
     P.timeline = p->timeline;
+    int smem = 0;
+    const void* kern = fused_kernel(p->precision, p->pair, p->game, &smem);
+    void* kargs[1] = {(void*)&P};
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(fused::kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at;
     if (p->pair) {
         const int pairs = (P.num_tiles + 1) / 2;
         P.num_tiles_loop = 2 * pairs;
-        cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2u * (unsigned)(pairs < p->max_pairs ? pairs : p->max_pairs));
-        cfg.blockDim = dim3(fused::kThreads);
-        cfg.dynamicSmemBytes = fused::Cfg<true>::kSmemBytes;
-        cfg.stream = st;
-        cudaLaunchAttribute at;
         at.id = cudaLaunchAttributeClusterDimension;
         at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
         cfg.attrs = &at; cfg.numAttrs = 1;
-        if (p->precision == CFX_PREC_F16)
-            CFX_CUDA(cudaLaunchKernelEx(&cfg, fused::k_policy_fused<__half, true>, P));
-        else
-            CFX_CUDA(cudaLaunchKernelEx(&cfg, fused::k_policy_fused<__nv_bfloat16, true>, P));
     } else {
         P.num_tiles_loop = P.num_tiles;
-        const int grid = P.num_tiles < p->sm_count ? P.num_tiles : p->sm_count;
-        if (p->precision == CFX_PREC_F16)
-            fused::k_policy_fused<__half, false><<<grid, fused::kThreads, fused::Cfg<false>::kSmemBytes, st>>>(P);
-        else
-            fused::k_policy_fused<__nv_bfloat16, false><<<grid, fused::kThreads, fused::Cfg<false>::kSmemBytes, st>>>(P);
+        cfg.gridDim = dim3((unsigned)(P.num_tiles < p->sm_count ? P.num_tiles : p->sm_count));
     }
+    CFX_CUDA(cudaLaunchKernelExC(&cfg, kern, kargs));
     CFX_CUDA(cudaGetLastError());
     if (launches) *launches = 1;
     return CFX_OK;

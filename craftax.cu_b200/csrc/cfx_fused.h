@@ -23,9 +23,9 @@ struct FusedArgs {
 };
 
 // Shapes the fused kernel is instantiated for.
-bool fused_supported(int H, int L, int A, int precision);
+bool fused_supported(int H, int L, int A, int precision, int game);
 int fused_create(FusedPlan** out, int device, int n, int H, int L, int A, int precision,
-                 float* state);
+                 float* state, int game);
 // Rebuilds the operand mirrors from the fp32 arena (device pointer).
 int fused_refresh(FusedPlan* plan, const float* params, cudaStream_t st);
 int fused_forward(FusedPlan* plan, const FusedArgs& a, cudaStream_t st, int* launches);

@@ -235,12 +235,14 @@ const char* cfx_version(void);
  * masks, 12 inventory counts, health/food/drink/energy, direction, sleeping flag, light as
  * raw fp32; craftax_classic.cu:50-59), the encoder (a gather of W_enc rows in the order of
  * encode_obs_kernel, :1714-1751) and the arena, whose W_enc has 1345 rows (:1526-1533).
- * Only CFX_PREC_FP32 is built for it; the fused kernel returns CFX_ERR_UNSUPPORTED.
+ * CFX_PREC_FP32 follows the reference's summation order; CFX_PREC_F16 / CFX_PREC_BF16 run the
+ * fused tcgen05 kernel (hidden 256, 17 actions), whose expand turns the record into one-hot
+ * operand rows in tensor memory and whose encoder is a dense MMA over the 1345 features.
  * cfx_forward_io.records then holds uint8 [n][148]; prev_terminals holds float flags
  * (cfx_classic_done_to_terminals converts the rollout's int8 r_done row). */
 size_t cfx_classic_param_count(int hidden, int layers, int num_actions);
 int cfx_policy_create_classic(cfx_policy** out, int device, int num_envs, int hidden,
-                              int layers, int num_actions);
+                              int layers, int num_actions, int precision);
 /* Replaces expand_obs_kernel (craftax_classic.cu:1265-1301): uint8 [n][148] -> fp32 [n][1345]
  * (device pointers). */
 int cfx_classic_expand_obs(int device, const uint8_t* records, float* out, int num_envs,

@@ -99,11 +99,91 @@ def test_classic_forward_matches_oracle(cfx, gpu, oracle, n):
 
 
 @pytest.mark.gpu
-def test_classic_is_fp32_only(cfx, gpu):
-    pol = cfx.Policy(64, H, L, A, "fp32", game="classic")
-    with pytest.raises(cfx.CfxError):
-        pol.set_precision("f16")
+@pytest.mark.parametrize("prec,n", [("f16", 64), ("f16", 128 * 9 + 32), ("bf16", 256)])
+def test_classic_fused_matches_oracle(cfx, gpu, oracle, prec, n):
+    """Fused tcgen05 kernel on classic records: one-hot expand in tensor memory, dense encoder
+    over the 1345 features, 3 layers, 17 actions; bounds as for the full game."""
+    rng = np.random.default_rng(n)
+    rec = oracle.classic_synthetic_records(n, seed=15)
+    params = oracle.classic_init_weights(H, L, A, seed=16)
+    state = rng.normal(0, 1, (L, n, H)).astype(np.float32)
+    done = (rng.random(n) < 0.2).astype(np.int8)
+    u = rng.random(n, dtype=np.float32)
+    pol = cfx.Policy(n, H, L, A, prec, game="classic")
+    pol.set_weights(params)
+    pol.set_state(state)
+    d = pol.forward_host(rec, done.astype(np.float32), u)
+    assert pol.last_launches == 1
+    want_st = state.copy()
+    lav = oracle.classic_forward(params, rec, done, want_st, H, L, A)
+    tol = 2e-2 if prec == "f16" else 1e-1
+    err = float(np.abs(d["logits_av"] - lav).max())
+    agree = float((d["logits_av"][:, :A].argmax(1) == lav[:, :A].argmax(1)).mean())
+    print(f"[classic {prec} n={n}] max|dlogit|={err:.3e} greedy agreement={agree:.4f}")
+    assert err < tol
+    assert np.abs(pol.get_state() - want_st).max() < tol
+    if prec == "f16":
+        assert agree >= 0.99
+    a, lp = cfx.sample_actions(d["logits_av"], u, num_actions=A)
+    assert np.array_equal(a, d["actions"])
+    assert np.array_equal(lp.view(np.uint32), d["logprobs"].view(np.uint32))
+    assert np.array_equal(d["values"], d["logits_av"][:, A])
     pol.close()
+
+
+@pytest.mark.gpu
+def test_classic_fused_expand_is_exact(cfx, gpu, oracle):
+    """Selection weights route features to the hidden units through exactly representable steps
+    (zero gate weights: per layer h <- 0.125 + 0.5 h), so the in-kernel one-hot expand is checked
+    bit for bit for every one of the 1323 one-hot features and the two flags."""
+    n = 128
+    rec = oracle.classic_synthetic_records(n, seed=17)
+    x = oracle.classic_expand(rec)
+    o = oracle.classic_offsets(H, L, A)
+    pol = cfx.Policy(n, H, L, A, "f16", game="classic")
+    exact = np.ones(1345, bool); exact[1323:1339] = False; exact[1343] = False   # counts / 10 and light round to fp16
+    for base in range(0, 1345, H):
+        for u0 in range(0, H, A):
+            units = np.arange(u0, min(u0 + A, H))
+            feats = base + units
+            feats = feats[feats < 1345]
+            units = units[:feats.size]
+            if feats.size == 0:
+                continue
+            params = np.zeros(o["count"], np.float32)
+            params[:o["b_enc"]].reshape(1345, H)[feats, units] = 1.0
+            params[o["w_a"]:o["b_a"]].reshape(A, H)[np.arange(units.size), units] = 1.0
+            pol.set_weights(params)
+            pol.reset_state()
+            d = pol.forward_host(rec, None, np.full(n, 0.5, np.float32))
+            got = d["logits_av"][:, :units.size]
+            want = 0.21875 + 0.125 * x[:, feats].astype(np.float64)     # three layers: 0.125 (1 + 0.5 + 0.25) + x / 8
+            ex = exact[feats]
+            assert np.array_equal(got[:, ex], want[:, ex].astype(np.float32)), (base, u0)
+            if (~ex).any():
+                assert np.abs(got[:, ~ex] - want[:, ~ex]).max() < 1e-3
+    pol.close()
+
+
+@pytest.mark.gpu
+def test_classic_fused_modes_agree(cfx, gpu, oracle, monkeypatch):
+    n = 128 * 5
+    rng = np.random.default_rng(3)
+    rec = oracle.classic_synthetic_records(n, seed=18)
+    params = oracle.classic_init_weights(H, L, A, seed=19)
+    state = rng.normal(0, 1, (L, n, H)).astype(np.float32)
+    out = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("CFX_FUSED_PAIR", mode)
+        pol = cfx.Policy(n, H, L, A, "f16", game="classic")
+        pol.set_weights(params)
+        pol.set_state(state)
+        d = pol.forward_host(rec, None, None, seed=4)
+        out[mode] = ({k: v.copy() for k, v in d.items()}, pol.get_state())
+        pol.close()
+    assert np.array_equal(out["1"][0]["logits_av"], out["0"][0]["logits_av"])
+    assert np.array_equal(out["1"][1], out["0"][1])
+    assert np.array_equal(out["1"][0]["actions"], out["0"][0]["actions"])
 
 
 @pytest.mark.gpu
