@@ -392,6 +392,71 @@ def run_sweep(args):
                       "hidden 128 and 512 and tf32 operands are not instantiated in this library"}), flush=True)
 
 
+def run_classic(args):
+    """Classic game (148-byte records, 1345 features, 3 MinGRU layers, 17 actions): the fused
+    forward on one GPU at --envs, its fused-roofline fraction, and beside it the reference's own
+    classic kernels with cuBLAS TF32 products (record-driven encoder, its MinGRU epilogue and
+    sampler kernels; built from its sources into oracle/_ref/) on the same inputs."""
+    rank, _, local = dist_env()
+    if rank != 0:
+        return
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import cfx
+    from cfx.synth import classic_synthetic_records, classic_init_weights
+    n, H, L, AC = args.envs, 256, 3, 17
+    prec = args.precision or DEFAULT_PRECISION
+    params = classic_init_weights(H, L, AC, seed=0)
+    rec = np.tile(classic_synthetic_records(8192, seed=4), (n // 8192 + 1, 1))[:n]
+    pol = cfx.Policy(n, H, L, AC, prec, device=local, game="classic")
+    pol.set_weights(params)
+    rng = np.random.default_rng(4)
+    pol.set_state(rng.standard_normal((L, n, H), dtype=np.float32))
+    d_rec = cfx.DeviceBuffer.from_host(rec, local)
+    d_pt = cfx.DeviceBuffer.from_host((rng.random(n) < 1 / 265).astype(np.float32), local)
+    d_act = cfx.DeviceBuffer((n,), np.int32, local)
+    d_lp = cfx.DeviceBuffer((n,), np.float32, local)
+    d_val = cfx.DeviceBuffer((n,), np.float32, local)
+
+    def step():
+        pol.forward_device(d_rec, d_pt, None, actions=d_act, logprobs=d_lp, values=d_val, seed=2, bump_step=True)
+    for _ in range(max(3, args.warmup)):
+        step()
+    pol.check()
+    t = cfx.Timer(local)
+    t.start(pol.stream)
+    for _ in range(args.steps):
+        step()
+    t.stop(pol.stream)
+    pol.check()
+    ms = t.elapsed_ms() / args.steps
+    flops = 2 * 1345 * H + L * 6 * H * H + 2 * (AC + 1) * H
+    byts = 148 + L * H * 8 + 4 + 4 + 4 + 4
+    peaks = load_peaks()
+    t_hbm, t_tensor = n * byts / (peaks["hbm_gbs"] * 1e9), n * flops / (peaks["bf16_tflops"] * 1e12)
+    line = {"impl": "classic", "metric": METRIC, "value": n / (ms * 1e-3), "unit": UNIT, "n_gpus": 1,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+            "dtype": f"{prec} operands, f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"classic policy forward, {n} envs, h{H}x{L}, {AC} actions, 148-B records"},
+            "roofline": {"bound": "tensor" if t_tensor > t_hbm else "hbm",
+                         "fused_roofline_ms": max(t_hbm, t_tensor) * 1e3, "frac": max(t_hbm, t_tensor) * 1e3 / ms,
+                         "flops_per_env": flops, "bytes_per_env": byts, "peak_source": peaks["source"]},
+            "gpu_launches": args.steps * pol.last_launches}
+    try:
+        import oracle as O
+        if O.RefClassic.available():
+            ref = O.RefClassic()
+            d_par = cfx.DeviceBuffer.from_host(params, local)
+            d_st = cfx.DeviceBuffer((L, n, H), np.float32, local, zero=True)
+            d_done = cfx.DeviceBuffer((n,), np.int8, local, zero=True)
+            rms = ref.time_forward(d_par.ptr, d_rec.ptr, d_done.ptr, d_st.ptr, n, 3, max(5, min(args.steps, 20)), 1)
+            line["reference_classic_forward"] = {"ms_per_step": rms, "value": n / (rms * 1e-3),
+                                                 "what": "reference classic kernels + cublasSgemm TF32, record-driven encoder"}
+    except Exception as e:   # the comparison is optional
+        line["reference_classic_forward"] = {"unavailable": str(e)}
+    print(json.dumps(line), flush=True)
+    pol.close()
+
+
 def run_ref_rollout(args):
     """Whole rollouts on one B200: the reference's own `run` loop (env kernels + its cuBLAS
     policy, graph replay), its env kernels alone, and the same loop with the policy half
@@ -435,7 +500,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="cfx", choices=["cfx", "reference", "ref-cublas", "ref-rollout", "sweep"])
+    ap.add_argument("--impl", default="cfx", choices=["cfx", "reference", "ref-cublas", "ref-rollout", "sweep", "classic"])
     ap.add_argument("--ref-mode", default="bf16", choices=["bf16", "tf32", "fp32"])
     ap.add_argument("--envs", type=int, default=262144, help="envs per GPU")
     ap.add_argument("--hidden", type=int, default=256)
@@ -455,6 +520,8 @@ def main():
         run_ref_rollout(args)
     elif args.impl == "sweep":
         run_sweep(args)
+    elif args.impl == "classic":
+        run_classic(args)
     else:
         run_cfx(args)
 

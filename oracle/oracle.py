@@ -204,6 +204,8 @@ class RefClassic:
         L.refcl_expand.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
         L.refcl_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
                                     C.c_ulonglong, C.c_ulonglong] + [C.c_void_p] * 4
+        L.refcl_time_forward.restype = C.c_float
+        L.refcl_time_forward.argtypes = [C.c_void_p] * 4 + [C.c_int] * 4
         self.L = L
         self.H, self.layers, self.A = L.refcl_hidden(), L.refcl_layers(), L.refcl_actions()
         assert L.refcl_obs() == CLASSIC_OBS and L.refcl_record_bytes() == CLASSIC_REC
@@ -211,6 +213,10 @@ class RefClassic:
 
     def expand(self, d_rec_ptr, d_out_ptr, n):
         self.L.refcl_expand(d_rec_ptr, d_out_ptr, n)
+
+    def time_forward(self, d_params_ptr, d_rec_ptr, d_prev_done_ptr, d_state_ptr, n, warm=3, iters=10, tf32=1):
+        return float(self.L.refcl_time_forward(d_params_ptr, d_rec_ptr, d_prev_done_ptr, d_state_ptr, n,
+                                               warm, iters, tf32))
 
     def forward(self, d_params_ptr, d_rec_ptr, d_prev_done_ptr, d_state_ptr, n, seed, step):
         o = {"logits_av": np.empty((n, self.A + 1), np.float32), "h_enc": np.empty((n, self.H), np.float32),

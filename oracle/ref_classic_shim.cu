@@ -109,4 +109,68 @@ void refcl_forward(const float* d_params, const uint8_t* d_rec, const int8_t* d_
     cudaFree(d_act); cudaFree(d_ctr);
 }
 
+/* Times the record-driven forward (encode_obs_kernel, three Sgemm + mingru_epi_fwd_kernel,
+ * logits Sgemm, value_sample_kernel, bump) on device-resident inputs: `warm` untimed and `iters`
+ * timed repetitions, CUDA events on the default stream.  tf32 != 0 selects the math mode the
+ * reference's rollout uses (CUBLAS_TF32_TENSOR_OP_MATH, main_classic.cu:283).  Returns ms per
+ * forward. */
+float refcl_time_forward(const float* d_params, const uint8_t* d_rec, const int8_t* d_prev_done,
+                         float* d_state, int n, int warm, int iters, int tf32) {
+    cublasHandle_t blas;
+    RC_BLAS(cublasCreate(&blas));
+    RC_BLAS(cublasSetMathMode(blas, tf32 ? CUBLAS_TF32_TENSOR_OP_MATH : CUBLAS_DEFAULT_MATH));
+    const float* W_enc = d_params + PARAM_W_ENC;
+    const float* b_enc = d_params + PARAM_B_ENC;
+    const float* W_gru = d_params + PARAM_W_GRU;
+    const float* W_a = d_params + PARAM_W_A;
+    const float* b_a = d_params + PARAM_B_A;
+    const float* W_v = d_params + PARAM_W_V;
+    const float* b_v = d_params + PARAM_B_V;
+    const size_t hn = (size_t)HIDDEN * n;
+    float *h0, *h1, *pre, *logits, *d_lp, *d_val;
+    int32_t* d_act;
+    uint64_t* d_ctr;
+    RC_CHECK(cudaMalloc(&h0, hn * sizeof(float)));
+    RC_CHECK(cudaMalloc(&h1, hn * sizeof(float)));
+    RC_CHECK(cudaMalloc(&pre, (size_t)GRU_OUT * n * sizeof(float)));
+    RC_CHECK(cudaMalloc(&logits, (size_t)NUM_ACTIONS * n * sizeof(float)));
+    RC_CHECK(cudaMalloc(&d_lp, (size_t)n * sizeof(float)));
+    RC_CHECK(cudaMalloc(&d_val, (size_t)n * sizeof(float)));
+    RC_CHECK(cudaMalloc(&d_act, (size_t)n * sizeof(int32_t)));
+    RC_CHECK(cudaMalloc(&d_ctr, sizeof(uint64_t)));
+    RC_CHECK(cudaMemset(d_ctr, 0, sizeof(uint64_t)));
+    RC_BLAS(cublasSetStream(blas, 0));
+    const float one = 1.0f, zero = 0.0f;
+    cudaEvent_t ea, eb;
+    RC_CHECK(cudaEventCreate(&ea));
+    RC_CHECK(cudaEventCreate(&eb));
+    for (int it = 0; it < warm + iters; it++) {
+        if (it == warm) RC_CHECK(cudaEventRecord(ea, 0));
+        encode_obs_kernel<<<(int)((hn + 255) / 256), 256>>>(d_rec, W_enc, b_enc, h0, 0, n, n, n, 0);
+        float* x = h0;
+        float* y = h1;
+        for (int l = 0; l < GRU_LAYERS; l++) {
+            RC_BLAS(cublasSgemm(blas, CUBLAS_OP_T, CUBLAS_OP_N, GRU_OUT, n, HIDDEN, &one,
+                                W_gru + (size_t)l * GRU_OUT * HIDDEN, HIDDEN, x, HIDDEN, &zero, pre, GRU_OUT));
+            mingru_epi_fwd_kernel<<<(int)((hn + 255) / 256), 256>>>(pre, x, d_state + (size_t)l * hn, y, NULL,
+                                                                    d_prev_done, n);
+            float* t = x; x = y; y = t;
+        }
+        RC_BLAS(cublasSgemm(blas, CUBLAS_OP_T, CUBLAS_OP_N, NUM_ACTIONS, n, HIDDEN, &one, W_a, HIDDEN, x, HIDDEN,
+                            &zero, logits, NUM_ACTIONS));
+        value_sample_kernel<<<(n + 255) / 256, 256>>>(x, logits, b_a, W_v, b_v, d_act, d_lp, d_val, n, 1, d_ctr);
+        bump_ctr_kernel<<<1, 1>>>(d_ctr);
+    }
+    RC_CHECK(cudaEventRecord(eb, 0));
+    RC_CHECK(cudaGetLastError());
+    RC_CHECK(cudaDeviceSynchronize());
+    float ms = 0.f;
+    RC_CHECK(cudaEventElapsedTime(&ms, ea, eb));
+    cudaEventDestroy(ea); cudaEventDestroy(eb);
+    cudaFree(h0); cudaFree(h1); cudaFree(pre); cudaFree(logits); cudaFree(d_lp); cudaFree(d_val);
+    cudaFree(d_act); cudaFree(d_ctr);
+    cublasDestroy(blas);
+    return ms / (float)iters;
+}
+
 } /* extern "C" */
