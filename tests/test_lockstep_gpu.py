@@ -76,6 +76,20 @@ def test_lockstep_1024_envs_64_steps(cfx, gpu, oracle):
     assert (hist > 0).sum() >= 40            # the sampler explores the action set
 
 
+def test_lockstep_65536_envs_128_steps(cfx, gpu, oracle):
+    """Full game at 65,536 envs for 128 rollout steps with auto-reset (seed 1): every step's
+    logits and value against the reference's fp32 cuBLAS pipeline on the same records, both sides
+    free-running."""
+    if not oracle.RefEnv.available() or not oracle.RefCuda.available(2):
+        pytest.skip("oracle/_ref libraries not built (reference sources absent)")
+    worst, agree, resets, hist, kind = _lockstep(cfx, oracle, 65536, 128, 2, env_seed=1, weight_seed=43)
+    print(f"[lock-step 65536x128 L=2 vs {kind}] max|dlogit|={worst:.3e} greedy={agree:.5f} "
+          f"episode resets seen={resets}")
+    assert worst <= 2e-2
+    assert agree >= 0.995
+    assert resets > 0
+
+
 def test_lockstep_three_layers(cfx, gpu, oracle):
     if not oracle.RefEnv.available():
         pytest.skip("oracle/_ref/libcfref_env.so not built (reference sources absent)")
