@@ -9,21 +9,23 @@
 // the encoder GEMM + k_add_bias (:11954-11962), cu_gru_chain (:11978-12014: gate GEMM +
 // k_mingru_epi_fwd :9350), the head GEMM (:12040-12045) and k_value_sample (:9714).
 //
-// Tile-level dataflow (M = 128 envs = the 128 TMEM lanes; thread r of a quarter-warp set
-// owns env row r):
+// Tile-level dataflow (M = 128 envs = the 128 TMEM lanes; the worker thread that owns TMEM lane
+// r owns env row r of the tile in every phase):
 //   TMEM columns   gate phase: A0 [0,128) A1 [128,256) (layer inputs, 16-bit packed, ping-pong)
 //                              G [256,448) (gate accumulators of one 64-unit slice: zh|zg|zp;
 //                              the workers move it to registers at once, which frees it for
-//                              the next slice's MMAs while the cell runs)  HEAD [448,496)
+//                              the next slice's MMAs while the cell runs)  HEAD [448,512)
 //                  encoder phase: operand-chunk ring [0,256) (8 x 32 columns), accumulator
 //                              [256,512)
-//   shared memory  weight ring 3 x 32 KB | state ring 4 x 16 KB | record ring 4 x 10 KB
-//   warps          0 weight loads (3 lanes), 1 MMA issue + TMEM alloc, 2 record loads
-//                  (4 lanes, one per slot), 3 state ring (4 lanes, one per slot: load, store, and the
-//                  L2 prefetch of the next tile), 4..11 workers (expand, cell, sampler)
+//   shared memory  weight ring | state ring (the record ring lives inside its slots) | tail /
+//                  classic record buffer | biases, barriers: see Cfg
+//   warps          0 weight loads (one lane per slot), 1 MMA issue (one thread) + TMEM alloc,
+//                  2 record loads (one lane per slot + the tail lane), 3 state ring (one lane per
+//                  slot: load, store, and the L2 prefetch), 4..11 workers (expand, cell, sampler)
+//   launch modes   clusters of two CTAs sharing 256-row MMAs (PAIR, the default) or one CTA per
+//                  tile; full game or classic game (GAME): see Cfg and Gm
 // One round of (mbarrier wait, arrive.expect_tx, bulk copy) costs its issuing thread about
-// 500 cycles on B200, so every copy role spreads its sequence over several lanes of its
-// warp (item k belongs to lane k mod lanes) and weight stages are 24-32 KB.
+// 500 cycles on B200, so every copy role gives each ring slot a lane of its own.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -66,17 +68,19 @@ template <> struct Gm<CFX_GAME_CLASSIC> {
 constexpr int kMaxEncChunks = 22;
 
 constexpr int kNBMax = 8;        // weight ring slots (one stage each): see Cfg
+// Ring shapes of the CTA-pair mode (compile-time tuning knobs; measured at 262,144 envs: 6 or 8
+// weight slots 0.413-0.414 ms, 5 slots with a record ring of its own 0.420 ms, 4 slots 0.434 ms)
 #ifndef CFX_PAIR_NB
-#define CFX_PAIR_NB 6
+#define CFX_PAIR_NB 6   // weight slots of 16 KB
 #endif
 #ifndef CFX_PAIR_NS
-#define CFX_PAIR_NS 6
+#define CFX_PAIR_NS 6   // state slots of 16 KB
 #endif
 #ifndef CFX_PAIR_ALIAS
-#define CFX_PAIR_ALIAS 1
+#define CFX_PAIR_ALIAS 1   // record ring inside the state slots
 #endif
 #ifndef CFX_PAIR_NR
-#define CFX_PAIR_NR 6
+#define CFX_PAIR_NR 6   // record slots (= state slots when the ring lives inside them)
 #endif
 constexpr int kSSlot = 16384, kNSMax = 6;
 constexpr int kRBoxBytes = 32 * 80, kRSlot = 4 * kRBoxBytes, kNRMax = 6;
