@@ -441,10 +441,11 @@ int cfx_policy_forward(cfx_policy* p, const cfx_forward_io* io, void* stream) {
         a.seed = io->seed;
         a.env_offset = io->env_offset;
         a.step_ctr = p->step_ctr;
+        a.bump_step = io->bump_step ? 1 : 0;   // folded into the kernel: no extra launch
         rc = fused_forward(p->fused, a, st, &launches);
     }
     if (rc) return rc;
-    if (io->bump_step) {
+    if (io->bump_step && p->precision == CFX_PREC_FP32) {
         rc = launch_bump(p->step_ctr, st);
         if (rc) return rc;
         launches++;

@@ -182,8 +182,10 @@ struct Params {
     float* values;
     float* logits_av;
     float* r_state;                      // optional [L][n][256] record of the post-zero input state
-    const unsigned long long* step_ctr;
+    unsigned long long* step_ctr;        // device step counter (Philox offset); see bump_step
     uint32_t* status;
+    uint32_t* done_ctr;                  // blocks that have finished this launch (bump_step)
+    int bump_step;
     uint64_t seed, env_offset;
     int n, L, num_tiles;
     int rec_bytes;        // bytes of one record (996 full game, 148 classic)
@@ -1217,6 +1219,16 @@ k_policy_fused(const __grid_constant__ Params P) {
         if (PAIR) tmem_dealloc_pair(tmem, 512);
         else tmem_dealloc(tmem, 512);
     }
+    // The reference bumps the sampler offset with a one-thread kernel after the step
+    // (k_bump_ctr, craftax_full.cu:12085).  Here the last block to finish does it: every block
+    // read the counter (in its sampler threads) before it got here.
+    if (tid == 0 && P.bump_step) {
+        __threadfence();
+        if (atomicAdd(P.done_ctr, 1u) == gridDim.x - 1) {
+            *P.step_ctr += 1ULL;
+            *P.done_ctr = 0u;
+        }
+    }
 }
 
 // Self-test of the bounded wait: one block waits on a barrier on which nothing ever arrives,
@@ -1261,7 +1273,7 @@ struct FusedPlan {
     int device, n, H, L, A, precision;
     int game = CFX_GAME_FULL;
     uint8_t* image = nullptr;
-    uint32_t* status = nullptr;
+    uint32_t* status = nullptr;    // [0] status word, [1] finished-block counter
     float* state = nullptr;
     const float* params = nullptr;
     CUtensorMap state_map[fused::kMaxLayers];
@@ -1314,8 +1326,8 @@ int fused_create(FusedPlan** out, int device, int n, int H, int L, int A, int pr
     p->sm_count = prop.multiProcessorCount;
     cudaError_t e = cudaMalloc((void**)&p->image, game == CFX_GAME_CLASSIC ? fused::image_bytes<CFX_GAME_CLASSIC>(L)
                                                                            : fused::image_bytes<CFX_GAME_FULL>(L));
-    if (e == cudaSuccess) e = cudaMalloc((void**)&p->status, sizeof(uint32_t));
-    if (e == cudaSuccess) e = cudaMemset(p->status, 0, sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&p->status, 2 * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(p->status, 0, 2 * sizeof(uint32_t));
     if (e != cudaSuccess) {
         fused_destroy(p);
         return cuda_fail(e, "fused_create alloc", __FILE__, __LINE__);
@@ -1418,6 +1430,8 @@ int fused_forward(FusedPlan* p, const FusedArgs& a, cudaStream_t st, int* launch
     P.r_state = a.r_state;
     P.step_ctr = a.step_ctr;
     P.status = p->status;
+    P.done_ctr = p->status + 1;
+    P.bump_step = a.bump_step;
     P.seed = a.seed;
     P.env_offset = a.env_offset;
     P.n = p->n;

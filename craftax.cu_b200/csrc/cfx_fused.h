@@ -19,7 +19,8 @@ struct FusedArgs {
     float* logits_av;
     float* r_state;
     uint64_t seed, env_offset;
-    const unsigned long long* step_ctr;
+    unsigned long long* step_ctr;
+    int bump_step;   // 1: the kernel's last block adds one to *step_ctr when every block is done
 };
 
 // Shapes the fused kernel is instantiated for.

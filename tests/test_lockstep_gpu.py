@@ -60,7 +60,8 @@ def _lockstep(cfx, oracle, n, steps, layers, env_seed, weight_seed):
         resets += int(prev_t.sum())
         hist += np.bincount(d["actions"], minlength=A)
         env.step(d["actions"].astype(np.float32))
-    assert pol.step == steps
+    assert pol.step == steps             # the step counter is bumped inside the fused kernel
+    assert pol.last_launches == 1
     pol.close(); side.close(); env.close()
     return worst, agree / (steps * n), resets, hist, side.kind
 
