@@ -348,9 +348,9 @@ def run_ref_cublas(args):
 
 
 def run_sweep(args):
-    """Synthetic fused-forward sweep on one GPU: batch x MinGRU depth x operand type at hidden
-    256 (the instantiations built), one JSON line per point with the fused-roofline fraction.
-    Points of the published sweep that are not built (hidden 128 / 512, tf32 operands) are
+    """Synthetic fused-forward sweep on one GPU: batch x hidden {128, 256} x MinGRU depth x
+    operand type (the instantiations built), one JSON line per point with the fused-roofline
+    fraction.  Points of the published sweep that are not built (hidden 512, tf32 operands) are
     listed once as unavailable."""
     import cfx
     from cfx.synth import synthetic_records, init_weights
@@ -365,31 +365,30 @@ def run_sweep(args):
         del rec
         d_act = cfx.DeviceBuffer((n,), np.int32, local)
         d_lav = cfx.DeviceBuffer((n, A + 1), np.float32, local)
-        for L in (2, 3):
-            for prec in ("f16", "bf16"):
-                pol = cfx.Policy(n, 256, L, A, prec, device=local)
-                pol.set_weights(init_weights(256, L, A, seed=0))
-                for _ in range(3):
-                    pol.forward_device(d_rec, None, None, actions=d_act, logits_av=d_lav, seed=1, bump_step=True)
-                pol.check()
-                steps = 20 if n <= 262144 else 8
-                t = cfx.Timer(local)
-                t.start(pol.stream)
-                for _ in range(steps):
-                    pol.forward_device(d_rec, None, None, actions=d_act, logits_av=d_lav, seed=1, bump_step=True)
-                t.stop(pol.stream)
-                pol.check()
-                ms = t.elapsed_ms() / steps
-                flops, byts = algorithmic_work(256, L)
-                t_roof = max(n * byts / (peaks["hbm_gbs"] * 1e9), n * flops / (peaks["bf16_tflops"] * 1e12))
-                print(json.dumps({"sweep": "fused forward", "envs": n, "hidden": 256, "layers": L,
-                                  "operands": prec, "ms_per_step": ms, "env_steps_per_s": n / (ms * 1e-3),
-                                  "fused_roofline_ms": t_roof * 1e3, "fused_roofline_frac": t_roof * 1e3 / ms,
-                                  "peak_source": peaks["source"]}), flush=True)
-                pol.close()
+        for H, L, prec in [(h, l, p) for h in (256, 128) for l in (2, 3) for p in ("f16", "bf16")]:
+            pol = cfx.Policy(n, H, L, A, prec, device=local)
+            pol.set_weights(init_weights(H, L, A, seed=0))
+            for _ in range(3):
+                pol.forward_device(d_rec, None, None, actions=d_act, logits_av=d_lav, seed=1, bump_step=True)
+            pol.check()
+            steps = 20 if n <= 262144 else 8
+            t = cfx.Timer(local)
+            t.start(pol.stream)
+            for _ in range(steps):
+                pol.forward_device(d_rec, None, None, actions=d_act, logits_av=d_lav, seed=1, bump_step=True)
+            t.stop(pol.stream)
+            pol.check()
+            ms = t.elapsed_ms() / steps
+            flops, byts = algorithmic_work(H, L)
+            t_roof = max(n * byts / (peaks["hbm_gbs"] * 1e9), n * flops / (peaks["bf16_tflops"] * 1e12))
+            print(json.dumps({"sweep": "fused forward", "envs": n, "hidden": H, "layers": L,
+                              "operands": prec, "ms_per_step": ms, "env_steps_per_s": n / (ms * 1e-3),
+                              "fused_roofline_ms": t_roof * 1e3, "fused_roofline_frac": t_roof * 1e3 / ms,
+                              "peak_source": peaks["source"]}), flush=True)
+            pol.close()
         d_rec.free(); d_act.free(); d_lav.free()
     print(json.dumps({"sweep": "fused forward", "unavailable":
-                      "hidden 128 and 512 and tf32 operands are not instantiated in this library"}), flush=True)
+                      "hidden 512 and tf32 operands are not instantiated in this library"}), flush=True)
 
 
 def run_classic(args):

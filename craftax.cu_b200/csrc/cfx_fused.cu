@@ -24,6 +24,8 @@
 //                  slot: load, store, and the L2 prefetch), 4..11 workers (expand, cell, sampler)
 //   launch modes   clusters of two CTAs sharing 256-row MMAs (PAIR, the default) or one CTA per
 //                  tile; full game or classic game (GAME): see Cfg and Gm
+//   hidden size    256 (the figures in this comment) or 128 (HID): two gate slices of two K
+//                  blocks per layer, A0 / A1 of 64 columns, encoder accumulator N = 128: see Hd
 // One round of (mbarrier wait, arrive.expect_tx, bulk copy) costs its issuing thread about
 // 500 cycles on B200, so every copy role gives each ring slot a lane of its own.
 #include <cuda_bf16.h>
@@ -40,15 +42,25 @@ using namespace umma;
 
 namespace fused {
 
-constexpr int kH = 256;          // hidden units
 constexpr int kTile = 128;       // envs per tile
 constexpr int kMaxLayers = 4;
 constexpr int kSliceUnits = 64;  // hidden units per gate slice (N = 192: zh|zg|zp)
-constexpr int kSlices = kH / kSliceUnits;  // 4
 constexpr int kHalfUnits = 32;   // units of a slice handled by one worker warpgroup
-constexpr int kStateItems = kH / kHalfUnits;  // 8 state boxes (128 rows x 32 units) per layer
-constexpr int kKBlocks = kH / 64;          // 4 K blocks of 64 per 256-wide operand
 constexpr int kHeadMax = 64;     // head accumulator columns reserved in tensor memory
+// Shapes that follow from the hidden size the kernel is instantiated for (256 or 128).
+template <int HID> struct Hd {
+    static_assert(HID == 256 || HID == 128, "hidden sizes the kernel is built for");
+    static constexpr int kH = HID;                        // hidden units
+    static constexpr int kSlices = HID / kSliceUnits;     // gate slices per layer (4 / 2)
+    static constexpr int kStateItems = HID / kHalfUnits;  // state boxes (128 rows x 32 units) per layer (8 / 4)
+    static constexpr int kKBlocks = HID / 64;             // K blocks of 64 per HID-wide operand (4 / 2)
+    static constexpr int kEncCopyBytes = HID * 128;       // encoder stage: one chunk, [HID units][64 K] 16-bit
+};
+// brings the shapes of Hd<HID> into a function body
+#define CFX_DIMS(HID)                                                                        \
+    constexpr int kH = Hd<HID>::kH, kSlices = Hd<HID>::kSlices, kStateItems = Hd<HID>::kStateItems, \
+                  kKBlocks = Hd<HID>::kKBlocks, kEncCopyBytes = Hd<HID>::kEncCopyBytes;      \
+    (void)kH; (void)kSlices; (void)kStateItems; (void)kKBlocks; (void)kEncCopyBytes
 
 // What differs between the two games the kernel is instantiated for.
 //  full game (craftax_full.cu): 996-byte record = 792 map bytes + 51 raw floats, 843 features
@@ -85,19 +97,19 @@ constexpr int kNBMax = 8;        // weight ring slots (one stage each): see Cfg
 constexpr int kSSlot = 16384, kNSMax = 6;
 constexpr int kRBoxBytes = 32 * 80, kRSlot = 4 * kRBoxBytes, kNRMax = 6;
 constexpr int kAexpSlots = 8;
+constexpr int kKBlocksMax = 4;
 
 // Image blocks (one K block of 64 columns each) and the ring stages that carry them:
 // encoder stage = one chunk, 256 units (two 128-unit blocks, 32 KB); gate stage = one K block
 // of one 64-unit slice (192 rows, 24 KB); head stage = all four K blocks (24 KB).
-constexpr int kEncStageBytes = 128 * 128;            // block: [128 units][64 K] 16-bit
-constexpr int kGateStageBytes = 3 * kSliceUnits * 128;  // block: [96 rows][64 K]
-constexpr int kEncCopyBytes = 2 * kEncStageBytes, kGateCopyBytes = kGateStageBytes;
+constexpr int kGateStageBytes = 3 * kSliceUnits * 128;  // block: [192 rows][64 K]
+constexpr int kGateCopyBytes = kGateStageBytes;
 // head stage: one CTA per tile [K block][rows][64 K]; pairs [half][K block][rows / 2][64 K]
-template <int GAME> __host__ __device__ constexpr int head_bytes(bool pair) {
-    return kKBlocks * (pair ? Gm<GAME>::kHeadPair : Gm<GAME>::kHeadSingle) * 128;
+template <int GAME, int HID> __host__ __device__ constexpr int head_bytes(bool pair) {
+    return Hd<HID>::kKBlocks * (pair ? Gm<GAME>::kHeadPair : Gm<GAME>::kHeadSingle) * 128;
 }
-template <int GAME> __host__ __device__ constexpr size_t enc_bytes() {
-    return (size_t)Gm<GAME>::kEncChunks * kEncCopyBytes;
+template <int GAME, int HID> __host__ __device__ constexpr size_t enc_bytes() {
+    return (size_t)Gm<GAME>::kEncChunks * Hd<HID>::kEncCopyBytes;
 }
 
 // A lane that handles every G-th item of an N-slot ring waits on its slot's "empty" barrier
@@ -109,8 +121,9 @@ template <int GAME> __host__ __device__ constexpr size_t enc_bytes() {
 // state ring (4 slots, slices alternate) satisfy this; each weight ring has one consumer.
 
 
-template <int GAME> __host__ __device__ constexpr size_t image_bytes(int L) {   // room for either head layout
-    return enc_bytes<GAME>() + (size_t)L * kSlices * kKBlocks * kGateStageBytes + (size_t)kKBlocks * kHeadMax * 128;
+template <int GAME, int HID> __host__ __device__ constexpr size_t image_bytes(int L) {   // room for either head layout
+    return enc_bytes<GAME, HID>() + (size_t)L * Hd<HID>::kSlices * Hd<HID>::kKBlocks * kGateStageBytes +
+           (size_t)Hd<HID>::kKBlocks * kHeadMax * 128;
 }
 
 // TMEM columns
@@ -122,7 +135,7 @@ enum Bar {
     B_FULL = 0, B_EMPTY = B_FULL + kNBMax, S_FULL = B_EMPTY + kNBMax, S_DONE = S_FULL + kNSMax,
     ST_READY = S_DONE + kNSMax, R_FULL = ST_READY + kNSMax, R_EMPTY = R_FULL + kNRMax,
     AEXP_FULL = R_EMPTY + kNRMax, AEXP_EMPTY = AEXP_FULL + kAexpSlots,
-    ACC_FULL = AEXP_EMPTY + kAexpSlots, A_KB = ACC_FULL + 1, G_FULL = A_KB + kKBlocks,
+    ACC_FULL = AEXP_EMPTY + kAexpSlots, A_KB = ACC_FULL + 1, G_FULL = A_KB + kKBlocksMax,
     G_EMPTY = G_FULL + 1, H_FULL = G_EMPTY + 1, H_EMPTY = H_FULL + 1, REC_DONE = H_EMPTY + 1,
     T_FULL = REC_DONE + 1, T_EMPTY = T_FULL + 1, NUM_BARS = T_EMPTY + 1
 };
@@ -134,17 +147,19 @@ enum Bar {
 //    while the gate layers run; REC_DONE and S_DONE order the two uses per tile);
 //  CTA pair (cta_group::2): every CTA stages half of each weight stage, 4 x 16 KB; the 64 KB
 //    this frees hold a record ring of its own, 6 x 10 KB, that runs ahead into the next tile.
-template <bool PAIR, int GAME = CFX_GAME_FULL> struct Cfg {
+template <bool PAIR, int GAME, int HID> struct Cfg {
+    static constexpr int kH = HID, kStateItems = Hd<HID>::kStateItems;
     static constexpr int kNB = PAIR ? CFX_PAIR_NB : 4;
     static constexpr int kBSlot = PAIR ? 16384 : 32768;
     static constexpr int kWLanes = kNB;                  // one lane per slot
     static constexpr int kHeadRows = PAIR ? Gm<GAME>::kHeadPair : Gm<GAME>::kHeadSingle;   // N of the head MMA
     static constexpr int kHeadKbBytes = (PAIR ? kHeadRows / 2 : kHeadRows) * 128;   // one K block of the head rows a CTA stages
     static constexpr int kM = PAIR ? 256 : 128;
-    static constexpr int kNS = PAIR ? CFX_PAIR_NS : 4;     // state ring slots: even, so that slot parity = warpgroup
+    // state ring slots: even, so that slot parity = warpgroup; at most one layer's boxes
+    static constexpr int kNS = PAIR && CFX_PAIR_NS <= kStateItems ? CFX_PAIR_NS : 4;
     // record ring inside the state slots (full game only: the classic records need no ring)
     static constexpr bool kAlias = GAME == CFX_GAME_FULL && (PAIR ? (CFX_PAIR_ALIAS != 0) : true);
-    static constexpr int kNR = GAME != CFX_GAME_FULL ? 0 : (PAIR ? CFX_PAIR_NR : 4);
+    static constexpr int kNR = GAME != CFX_GAME_FULL ? 0 : (kAlias ? kNS : (PAIR ? CFX_PAIR_NR : 4));
     static constexpr int kRStride = kAlias ? kSSlot : kRSlot;
     static constexpr int kOffB = 0;
     static constexpr int kOffS = kOffB + kNB * kBSlot;
@@ -223,15 +238,18 @@ __device__ inline __nv_bfloat16 to16<__nv_bfloat16>(float v) {
 
 // One thread per 16-bit element of the image.  Stage order = consumption order of the
 // kernel: encoder (chunk-major, unit halves), gate layers (layer, slice, K block), head.
-template <typename T16, int GAME>
+template <typename T16, int GAME, int HID>
 __global__ void k_pack_image(const float* __restrict__ params, uint8_t* __restrict__ image, int L,
                              size_t off_w_gru, size_t off_w_a, size_t off_w_v, int pair) {
+    CFX_DIMS(HID);
     constexpr int kA = Gm<GAME>::kA;
-    const size_t total = image_bytes<GAME>(L) / 2;
+    constexpr int kEncStageBytes = 128 * 128;   // image block: [128 units][64 K] 16-bit
+    constexpr int kEncBlocks = kH / 128;        // blocks per encoder chunk
+    const size_t total = image_bytes<GAME, HID>(L) / 2;
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     size_t byte = idx * 2;
-    const size_t enc_b = enc_bytes<GAME>();
+    const size_t enc_b = enc_bytes<GAME, HID>();
     const size_t gate_bytes = (size_t)L * kSlices * kKBlocks * kGateStageBytes;
     float v = 0.0f;
     uint32_t row, c;
@@ -240,7 +258,7 @@ __global__ void k_pack_image(const float* __restrict__ params, uint8_t* __restri
         const int s = (int)(byte / kEncStageBytes), e = (int)((byte % kEncStageBytes) / 2);
         row = e / 64; c = e % 64;
         stage = image + (size_t)s * kEncStageBytes;
-        const int chunk = s / 2, half = s % 2;
+        const int chunk = s / kEncBlocks, half = s % kEncBlocks;
         const int f = enc_feature<GAME>(chunk, c);
         if (f >= 0) v = params[(size_t)f * kH + half * 128 + row];
     } else if (byte < enc_b + gate_bytes) {
@@ -255,7 +273,7 @@ __global__ void k_pack_image(const float* __restrict__ params, uint8_t* __restri
         // head.  One CTA per tile: [K block][rows][64 K].  CTA pairs: CTA r stages head rows
         // [r rows/2, (r + 1) rows/2): [r][K block][rows / 2][64 K].
         const size_t b = byte - enc_b - gate_bytes;
-        if (b >= (size_t)head_bytes<GAME>(pair != 0)) return;
+        if (b >= (size_t)head_bytes<GAME, HID>(pair != 0)) return;
         const int rows = pair ? Gm<GAME>::kHeadPair / 2 : Gm<GAME>::kHeadSingle;   // rows of one block
         const int blk_bytes = rows * 128;
         const int blk = (int)(b / blk_bytes), e = (int)((b % blk_bytes) / 2);
@@ -341,8 +359,8 @@ __device__ __forceinline__ void mingru_cell(float zh, float zg, float zp, float 
 struct Smem {
     uint8_t* base;
     int off_s, off_r, r_stride, off_t, off_bias, off_bars, off_misc, b_slot_bytes;
-    template <bool PAIR, int GAME> __device__ __forceinline__ void layout() {
-        using C = Cfg<PAIR, GAME>;
+    template <bool PAIR, int GAME, int HID> __device__ __forceinline__ void layout() {
+        using C = Cfg<PAIR, GAME, HID>;
         off_s = C::kOffS; off_r = C::kOffR; r_stride = C::kRStride; off_t = C::kOffT;
         off_bias = C::kOffBias; off_bars = C::kOffBars; off_misc = C::kOffMisc; b_slot_bytes = C::kBSlot;
     }
@@ -463,7 +481,9 @@ __device__ __forceinline__ void l2_prefetch_rows(const uint8_t* base, uint32_t b
     const uint32_t o = (uint32_t)piece * kL2Piece;
     if (o < bytes) bulk_prefetch_l2(base + o, min(kL2Piece, bytes - o));
 }
+template <int HID>
 __device__ __forceinline__ void l2_prefetch_for_box(const Params& P, int tile, int l, int j) {
+    CFX_DIMS(HID);
     if (tile >= P.num_tiles) return;   // the filler tile of an odd pair
     if (l < P.L - 1) {
         const int rows = min(kTile, P.n - tile * kTile);
@@ -474,7 +494,12 @@ __device__ __forceinline__ void l2_prefetch_for_box(const Params& P, int tile, i
         const int t = tile + gridDim.x;
         if (t >= P.num_tiles) return;
         const int rows = min(kTile, P.n - t * kTile);
-        l2_prefetch_rows(P.records + (size_t)t * kTile * P.rec_bytes, (uint32_t)rows * P.rec_bytes, j);
+        // a tile's records are up to eight pieces: spread over the boxes of the layer
+        constexpr int kRecPieces = 8 / kStateItems;
+#pragma unroll
+        for (int q = 0; q < kRecPieces; q++)
+            l2_prefetch_rows(P.records + (size_t)t * kTile * P.rec_bytes, (uint32_t)rows * P.rec_bytes,
+                             j * kRecPieces + q);
         l2_prefetch_rows(reinterpret_cast<const uint8_t*>(P.state + (size_t)t * kTile * kH),
                          (uint32_t)rows * kH * 4, j);
     }
@@ -486,13 +511,14 @@ __device__ __forceinline__ void l2_prefetch_for_box(const Params& P, int tile, i
 // One lane per ring slot.  In a CTA pair every CTA stages its own half of the rows of each
 // stage (the halves are contiguous in the image); the odd CTA waits for its copy to land and
 // then arrives on the even CTA's "full" barrier, where the MMA thread waits.
-template <bool PAIR, int GAME>
+template <bool PAIR, int GAME, int HID>
 __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& P, int lane,
                                                   uint32_t rank, uint32_t bar0_cta0) {
-    using C = Cfg<PAIR, GAME>;
+    using C = Cfg<PAIR, GAME, HID>;
+    CFX_DIMS(HID);
     constexpr int kEncChunks = Gm<GAME>::kEncChunks;
     const int stages_gate = P.L * kSlices * kKBlocks;
-    const size_t enc_bytes = fused::enc_bytes<GAME>();
+    const size_t enc_bytes = fused::enc_bytes<GAME, HID>();
     uint32_t cnt = 0;
     TL_INIT(3);
     for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x) {
@@ -505,7 +531,7 @@ __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& 
             } else if (s < kEncChunks + stages_gate) {
                 bytes = kGateCopyBytes; off = enc_bytes + (size_t)(s - kEncChunks) * kGateCopyBytes;
             } else {
-                bytes = head_bytes<GAME>(PAIR);
+                bytes = head_bytes<GAME, HID>(PAIR);
                 off = enc_bytes + (size_t)stages_gate * kGateCopyBytes;
             }
             if (PAIR) {
@@ -534,9 +560,9 @@ __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& 
 // aligned row); env 4g+i of a tile sits in row g at byte 996 i.  A 64-byte feature chunk of
 // all 128 envs is fetched as four boxes (one per i) of 32 rows x 80 bytes starting at the
 // 16-byte boundary below 996 i + 64 c; the 204 tail bytes take three more such box sets.
-template <bool PAIR, int GAME>
+template <bool PAIR, int GAME, int HID>
 __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& P, int lane) {
-    using C = Cfg<PAIR, GAME>;
+    using C = Cfg<PAIR, GAME, HID>;
     constexpr int kNR = C::kNR;
     constexpr int kRecFills = Gm<GAME>::kRecFills;
     uint32_t it = 0;
@@ -596,9 +622,10 @@ __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& 
 // replaced the contents with the new state, write it back (rows beyond n are clipped by the
 // tensor map), and only then load the next box into the slot.  One lane per slot needs no
 // "slot empty" barrier and saves a hand-off.
-template <bool PAIR, int GAME>
+template <bool PAIR, int GAME, int HID>
 __device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P, int lane) {
-    using C = Cfg<PAIR, GAME>;
+    using C = Cfg<PAIR, GAME, HID>;
+    CFX_DIMS(HID);
     constexpr int kNS = C::kNS;
     uint32_t cnt = 0, uses = 0, it = 0;
     const uint32_t slot_addr = smem_u32(sm.s_slot(lane));
@@ -619,7 +646,7 @@ __device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P,
                 tensor_g2s_2d(slot_addr, &P.state_map[l], j * kHalfUnits, tile * kTile,
                               sm.bar(S_FULL + lane));
 #ifndef CFX_ABL_NOPREFETCH
-                l2_prefetch_for_box(P, tile, l, j);
+                l2_prefetch_for_box<HID>(P, tile, l, j);
 #endif
                 CFX_WAIT(ST_READY + lane, uses & 1, W_ST_READY);
                 uses++;
@@ -656,9 +683,10 @@ __device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P,
         if (PAIR) mma_commit_pair(bar);  \
         else mma_commit(bar);            \
     } while (0)
-template <typename T16, bool PAIR, int GAME>
+template <typename T16, bool PAIR, int GAME, int HID>
 __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32_t tmem) {
-    using C = Cfg<PAIR, GAME>;
+    using C = Cfg<PAIR, GAME, HID>;
+    CFX_DIMS(HID);
     constexpr int kEncChunks = Gm<GAME>::kEncChunks;
     constexpr int kNB = C::kNB, kBSlot = C::kBSlot;
     constexpr uint32_t fmt = Op16<T16>::kFmt;
@@ -789,10 +817,12 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
 // ------------------------------------------------------------------ worker role
 // Eight warps, two per TMEM lane quarter (wg 0 / wg 1); thread (quarter, lane) owns env row
 // quarter*32 + lane of the tile in every phase.
-template <typename T16, bool PAIR, int GAME>
+template <typename T16, bool PAIR, int GAME, int HID>
 __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uint32_t tmem,
                                             int warp, int lane, uint32_t bar0_cta0) {
     using Op = Op16<T16>;
+    using C = Cfg<PAIR, GAME, HID>;
+    CFX_DIMS(HID);
     constexpr int kA = Gm<GAME>::kA, kEncChunks = Gm<GAME>::kEncChunks, kRecFills = Gm<GAME>::kRecFills;
     constexpr int kHeadCols = (kA + 1 + 15) / 16 * 16;   // head accumulator columns that are read
     // barriers the MMA thread waits on live in the even CTA of a pair
@@ -872,7 +902,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 __syncwarp();
                 if (kc >= kEncChunks - 2 && lane == 0) mbar_arrive(sm.bar(T_EMPTY));   // last chunk of this warp
             } else if (kc < 13) {
-                constexpr int kNRw = Cfg<PAIR, GAME>::kNR;
+                constexpr int kNRw = C::kNR;
                 const int slot = rec_slot<kNRw>(kc);
                 CFX_WAITW(R_FULL + slot, rec_phase<kNRw>(it, kc) & 1, W_R_FULL);
                 if (tl_on) TLB(3, 0x80000 | kc);
@@ -912,7 +942,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sm.bar(T_EMPTY));
             }
-            if (Cfg<PAIR, GAME>::kAlias && (kc == kLastWg1 || kc == kEncChunks - 1) && lane == 0)
+            if (C::kAlias && (kc == kLastWg1 || kc == kEncChunks - 1) && lane == 0)
                 mbar_arrive(sm.bar(REC_DONE));
             {
                 uint32_t lo[16], hi[16];
@@ -933,25 +963,28 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
         if (tl_on) TLB(5, 0xA0000);
         tc_fence_after_sync();
 #pragma unroll 2
-        for (int b = 0; b < 8; b++) {
+        for (int b = 0; b < kH / 32; b++) {   // this warpgroup's kH / 2 units, 16 at a time
             uint32_t acc[16], pk[8];
-            tmem_ld16(tmem + lane_base + kColAcc + 128 * wg + 16 * b, acc);
+            tmem_ld16(tmem + lane_base + kColAcc + (kH / 2) * wg + 16 * b, acc);
             tmem_wait_ld();
-            const float* bb = bias + 128 * wg + 16 * b;
+            const float* bb = bias + (kH / 2) * wg + 16 * b;
 #pragma unroll
             for (int q = 0; q < 8; q++)
                 pk[q] = Op::pack(__uint_as_float(acc[2 * q]) + bb[2 * q],
                                  __uint_as_float(acc[2 * q + 1]) + bb[2 * q + 1]);
-            tmem_st8(tmem + lane_base + kColA0 + 64 * wg + 8 * b, pk);
+            tmem_st8(tmem + lane_base + kColA0 + (kH / 4) * wg + 8 * b, pk);
         }
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
-            arrive_mma(A_KB + 2 * wg);
-            arrive_mma(A_KB + 2 * wg);
-            arrive_mma(A_KB + 2 * wg + 1);
-            arrive_mma(A_KB + 2 * wg + 1);
+            // the K blocks this warpgroup wrote; two arrivals each stand for the two
+            // warpgroups that arrive per K block in the gate layers
+#pragma unroll
+            for (int kb = 0; kb < kKBlocks / 2; kb++) {
+                arrive_mma(A_KB + (kKBlocks / 2) * wg + kb);
+                arrive_mma(A_KB + (kKBlocks / 2) * wg + kb);
+            }
         }
         if (tl_on) TLB(1, 0xA8000);
 
@@ -966,7 +999,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 tc_fence_after_sync();
                 const int box = 2 * j + wg;
                 const uint32_t scnt = (it * P.L + l) * kStateItems + box;
-                constexpr int kNS = Cfg<PAIR, GAME>::kNS;
+                constexpr int kNS = C::kNS;
                 const int slot = scnt % kNS;
                 const uint32_t gcol = tmem + lane_base + kColG + kHalfUnits * wg;
                 uint8_t* rbase = sm.s_slot(slot) + (row >> 3) * 1024 + (row & 7) * 128;
@@ -1111,15 +1144,16 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
 // of a pair owns tile 2 c + r in every respect (records, state, expand, cell, sampler) except
 // that the MMA thread of the even CTA issues one 256-row MMA for both tiles and every CTA
 // stages only its half of the weight rows.
-template <typename T16, bool PAIR, int GAME>
+template <typename T16, bool PAIR, int GAME, int HID>
 __global__ void __launch_bounds__(kThreads, 1)
 k_policy_fused(const __grid_constant__ Params P) {
-    using C = Cfg<PAIR, GAME>;
+    using C = Cfg<PAIR, GAME, HID>;
+    CFX_DIMS(HID);
     constexpr int kA = Gm<GAME>::kA;
     extern __shared__ uint8_t smem_raw[];
     Smem sm;
     sm.base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    sm.template layout<PAIR, GAME>();
+    sm.template layout<PAIR, GAME, HID>();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #ifdef CFX_PROFILE
     const uint64_t pf_entry = global_timer_ns();
@@ -1185,15 +1219,15 @@ k_policy_fused(const __grid_constant__ Params P) {
 #endif
 
     if (warp == 0) {
-        if (lane < C::kWLanes) role_weight_loads<PAIR, GAME>(sm, P, lane, rank, bar0_cta0);
+        if (lane < C::kWLanes) role_weight_loads<PAIR, GAME, HID>(sm, P, lane, rank, bar0_cta0);
     } else if (warp == 1) {
-        if (lane == 0 && rank == 0) role_mma<T16, PAIR, GAME>(sm, P, tmem);
+        if (lane == 0 && rank == 0) role_mma<T16, PAIR, GAME, HID>(sm, P, tmem);
     } else if (warp == 2) {
-        if (lane < C::kNR + 1) role_record_loads<PAIR, GAME>(sm, P, lane);
+        if (lane < C::kNR + 1) role_record_loads<PAIR, GAME, HID>(sm, P, lane);
     } else if (warp == 3) {
-        if (lane < C::kNS) role_state_ring<PAIR, GAME>(sm, P, lane);
+        if (lane < C::kNS) role_state_ring<PAIR, GAME, HID>(sm, P, lane);
     } else {
-        role_worker<T16, PAIR, GAME>(sm, P, tmem, warp, lane, bar0_cta0);
+        role_worker<T16, PAIR, GAME, HID>(sm, P, tmem, warp, lane, bar0_cta0);
     }
 
     // common exit: every role ends here, also after a timed-out wait.  In a pair neither CTA
@@ -1285,26 +1319,42 @@ struct FusedPlan {
 
 bool fused_supported(int H, int L, int A, int precision, int game) {
     const int want_a = game == CFX_GAME_CLASSIC ? fused::Gm<CFX_GAME_CLASSIC>::kA : fused::Gm<CFX_GAME_FULL>::kA;
-    return H == fused::kH && A == want_a && L >= 1 && L <= fused::kMaxLayers &&
+    // hidden 256 for both games, hidden 128 for the full game
+    const bool shape = H == 256 || (H == 128 && game == CFX_GAME_FULL);
+    return shape && A == want_a && L >= 1 && L <= fused::kMaxLayers &&
            (precision == CFX_PREC_F16 || precision == CFX_PREC_BF16);
 }
 
-// kernel instantiation and its shared-memory size for (operand type, launch mode, game)
-static const void* fused_kernel(int precision, int pair, int game, int* smem) {
+// kernel instantiation and its shared-memory size for (operand type, launch mode, game, hidden)
+static const void* fused_kernel(int precision, int pair, int game, int H, int* smem) {
     const bool h = precision == CFX_PREC_F16;
-#define CFX_K(T, P, G)                                         \
-    do {                                                       \
-        *smem = fused::Cfg<P, G>::kSmemBytes;                  \
-        return (const void*)fused::k_policy_fused<T, P, G>;    \
+#define CFX_K(T, P, G, HID)                                         \
+    do {                                                            \
+        *smem = fused::Cfg<P, G, HID>::kSmemBytes;                  \
+        return (const void*)fused::k_policy_fused<T, P, G, HID>;    \
+    } while (0)
+#define CFX_K2(P, G, HID)                          \
+    do {                                           \
+        if (h) CFX_K(__half, P, G, HID);           \
+        else CFX_K(__nv_bfloat16, P, G, HID);      \
     } while (0)
     if (game == CFX_GAME_CLASSIC) {
-        if (pair) { if (h) CFX_K(__half, true, CFX_GAME_CLASSIC); else CFX_K(__nv_bfloat16, true, CFX_GAME_CLASSIC); }
-        else { if (h) CFX_K(__half, false, CFX_GAME_CLASSIC); else CFX_K(__nv_bfloat16, false, CFX_GAME_CLASSIC); }
+        if (pair) CFX_K2(true, CFX_GAME_CLASSIC, 256);
+        CFX_K2(false, CFX_GAME_CLASSIC, 256);
     }
-    if (pair) { if (h) CFX_K(__half, true, CFX_GAME_FULL); else CFX_K(__nv_bfloat16, true, CFX_GAME_FULL); }
-    if (h) CFX_K(__half, false, CFX_GAME_FULL);
-    CFX_K(__nv_bfloat16, false, CFX_GAME_FULL);
+    if (H == 128) {
+        if (pair) CFX_K2(true, CFX_GAME_FULL, 128);
+        CFX_K2(false, CFX_GAME_FULL, 128);
+    }
+    if (pair) CFX_K2(true, CFX_GAME_FULL, 256);
+    CFX_K2(false, CFX_GAME_FULL, 256);
+#undef CFX_K2
 #undef CFX_K
+}
+
+static size_t fused_image_bytes(int game, int H, int L) {
+    if (game == CFX_GAME_CLASSIC) return fused::image_bytes<CFX_GAME_CLASSIC, 256>(L);
+    return H == 128 ? fused::image_bytes<CFX_GAME_FULL, 128>(L) : fused::image_bytes<CFX_GAME_FULL, 256>(L);
 }
 
 int fused_create(FusedPlan** out, int device, int n, int H, int L, int A, int precision,
@@ -1324,8 +1374,7 @@ int fused_create(FusedPlan** out, int device, int n, int H, int L, int A, int pr
     p->game = game;
     p->state = state;
     p->sm_count = prop.multiProcessorCount;
-    cudaError_t e = cudaMalloc((void**)&p->image, game == CFX_GAME_CLASSIC ? fused::image_bytes<CFX_GAME_CLASSIC>(L)
-                                                                           : fused::image_bytes<CFX_GAME_FULL>(L));
+    cudaError_t e = cudaMalloc((void**)&p->image, fused_image_bytes(game, H, L));
     if (e == cudaSuccess) e = cudaMalloc((void**)&p->status, 2 * sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(p->status, 0, 2 * sizeof(uint32_t));
     if (e != cudaSuccess) {
@@ -1343,7 +1392,7 @@ int fused_create(FusedPlan** out, int device, int n, int H, int L, int A, int pr
     }
     for (int pr = 0; pr < 2 && e == cudaSuccess; pr++) {
         int smem = 0;
-        const void* k = fused_kernel(precision, pr, game, &smem);
+        const void* k = fused_kernel(precision, pr, game, H, &smem);
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     }
     if (e != cudaSuccess) {
@@ -1358,7 +1407,7 @@ int fused_create(FusedPlan** out, int device, int n, int H, int L, int A, int pr
         cfg.gridDim = dim3(2 * (unsigned)(p->sm_count / 2));
         cfg.blockDim = dim3(fused::kThreads);
         int smem = 0;
-        const void* kpair = fused_kernel(precision, 1, game, &smem);
+        const void* kpair = fused_kernel(precision, 1, game, H, &smem);
         cfg.dynamicSmemBytes = smem;
         cudaLaunchAttribute at;
         at.id = cudaLaunchAttributeClusterDimension;
@@ -1380,12 +1429,13 @@ int fused_refresh(FusedPlan* p, const float* params, cudaStream_t st) {
     p->params = params;
     const bool classic = p->game == CFX_GAME_CLASSIC;
     const ArenaLayout o = ArenaLayout::make(p->H, p->L, p->A, classic ? kClassicObs : kObs);
-    const size_t total = (classic ? fused::image_bytes<CFX_GAME_CLASSIC>(p->L) : fused::image_bytes<CFX_GAME_FULL>(p->L)) / 2;
+    const size_t total = fused_image_bytes(p->game, p->H, p->L) / 2;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     const bool h = p->precision == CFX_PREC_F16;
-#define CFX_PACK(T, G) fused::k_pack_image<T, G><<<blocks, 256, 0, st>>>(params, p->image, p->L, o.w_gru, o.w_a, o.w_v, p->pair)
-    if (classic) { if (h) CFX_PACK(__half, CFX_GAME_CLASSIC); else CFX_PACK(__nv_bfloat16, CFX_GAME_CLASSIC); }
-    else { if (h) CFX_PACK(__half, CFX_GAME_FULL); else CFX_PACK(__nv_bfloat16, CFX_GAME_FULL); }
+#define CFX_PACK(T, G, HID) fused::k_pack_image<T, G, HID><<<blocks, 256, 0, st>>>(params, p->image, p->L, o.w_gru, o.w_a, o.w_v, p->pair)
+    if (classic) { if (h) CFX_PACK(__half, CFX_GAME_CLASSIC, 256); else CFX_PACK(__nv_bfloat16, CFX_GAME_CLASSIC, 256); }
+    else if (p->H == 128) { if (h) CFX_PACK(__half, CFX_GAME_FULL, 128); else CFX_PACK(__nv_bfloat16, CFX_GAME_FULL, 128); }
+    else { if (h) CFX_PACK(__half, CFX_GAME_FULL, 256); else CFX_PACK(__nv_bfloat16, CFX_GAME_FULL, 256); }
 #undef CFX_PACK
     CFX_CUDA(cudaGetLastError());
     return CFX_OK;
@@ -1442,7 +1492,7 @@ int fused_forward(FusedPlan* p, const FusedArgs& a, cudaStream_t st, int* launch
     P.off_b_v = o.b_v;
     P.timeline = p->timeline;
     int smem = 0;
-    const void* kern = fused_kernel(p->precision, p->pair, p->game, &smem);
+    const void* kern = fused_kernel(p->precision, p->pair, p->game, p->H, &smem);
     void* kargs[1] = {(void*)&P};
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(fused::kThreads);

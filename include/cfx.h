@@ -68,6 +68,10 @@ size_t cfx_param_count(int hidden, int layers, int num_actions);
  * parameter arena, operand mirrors, the zeroed recurrent state [L][n][H], the
  * device step counter (= 0) and a non-blocking stream on `device`.
  * num_envs must be a positive multiple of 32 (craftax_full.cu:11820).
+ * Shapes: CFX_PREC_FP32 takes any hidden size that is a multiple of 32 up to
+ * 512; the fused kernel (CFX_PREC_F16 / CFX_PREC_BF16) is built for hidden 256
+ * and 128, 1..4 layers and 43 actions, anything else returns
+ * CFX_ERR_UNSUPPORTED.
  * Weights start as zeros; call one of the three setters below. */
 int cfx_policy_create(cfx_policy** out, int device, int num_envs, int hidden,
                       int layers, int num_actions, int precision);

@@ -126,7 +126,7 @@ def test_fused_expand_is_exact_for_every_map_feature(cfx, gpu, oracle):
 
 def test_fused_rejects_what_it_cannot_do(cfx, gpu, oracle):
     with pytest.raises(cfx.CfxError):
-        cfx.Policy(64, 128, 2, A, "f16")        # hidden 128 is not instantiated
+        cfx.Policy(64, 64, 2, A, "f16")         # hidden 64 is not instantiated
     with pytest.raises(cfx.CfxError):
         cfx.Policy(64, H, L, A, "tf32")         # tf32 operands are not built
 
