@@ -33,7 +33,7 @@ class ForwardIO(C.Structure):
                 ("uniforms", C.c_void_p), ("env_actions", C.c_void_p),
                 ("actions", C.c_void_p), ("logprobs", C.c_void_p), ("values", C.c_void_p),
                 ("logits_av", C.c_void_p), ("r_state", C.c_void_p), ("seed", C.c_uint64),
-                ("env_offset", C.c_uint64), ("bump_step", C.c_int)]
+                ("env_offset", C.c_uint64), ("bump_step", C.c_int), ("r_state_bf16", C.c_int)]
 
 
 _SIGS = {
@@ -313,19 +313,22 @@ class Policy:
     # -- forward ---------------------------------------------------------
     def forward_device(self, records, prev_terminals=None, uniforms=None, *, env_actions=None,
                        actions, logprobs=None, values=None, logits_av=None, r_state=None,
-                       seed=0, env_offset=0, bump_step=False, stream=None):
-        """Device-pointer forward (arguments are DeviceBuffer or None); asynchronous."""
+                       seed=0, env_offset=0, bump_step=False, stream=None, r_state_bf16=False):
+        """Device-pointer forward (arguments are DeviceBuffer or None); asynchronous.
+        `r_state` holds fp32 [L][n][H], or bf16 of the same shape with r_state_bf16."""
         def p(b):
             return None if b is None else b.ptr
         io = ForwardIO(p(records), p(prev_terminals), p(uniforms), p(env_actions), p(actions),
                        p(logprobs), p(values), p(logits_av), p(r_state), seed, env_offset,
-                       1 if bump_step else 0)
+                       1 if bump_step else 0, 1 if r_state_bf16 else 0)
         check(lib().cfx_policy_forward(self.h, C.byref(io), stream))
 
     def forward_host(self, records, prev_terminals=None, uniforms=None, *, seed=0, env_offset=0,
                      bump_step=False, want_logits=True, want_r_state=False, out=None):
         """Host-buffer forward through cfx_policy_forward_host; returns a dict of numpy
-        arrays.  `out` may hold preallocated (pinned) arrays to reuse."""
+        arrays.  `out` may hold preallocated (pinned) arrays to reuse.  want_r_state: True for
+        the fp32 record of the post-zero input state, "bf16" for the bf16 record (returned as
+        the uint16 bit patterns)."""
         n, A = self.n, self.A
         rec = np.ascontiguousarray(records, np.uint8)
         assert rec.size == n * self.rec_bytes
@@ -337,7 +340,8 @@ class Policy:
         if want_logits:
             o.setdefault("logits_av", np.empty((n, A + 1), np.float32))
         if want_r_state:
-            o.setdefault("r_state", np.empty((self.L, n, self.H), np.float32))
+            o.setdefault("r_state", np.empty((self.L, n, self.H),
+                                             np.uint16 if want_r_state == "bf16" else np.float32))
         pt = None if prev_terminals is None else np.ascontiguousarray(prev_terminals, np.float32)
         u = None if uniforms is None else np.ascontiguousarray(uniforms, np.float32)
 
@@ -345,7 +349,8 @@ class Policy:
             return None if a is None else a.ctypes.data
         io = ForwardIO(hp(rec), hp(pt), hp(u), hp(o["env_actions"]), hp(o["actions"]),
                        hp(o["logprobs"]), hp(o["values"]), hp(o.get("logits_av")),
-                       hp(o.get("r_state")), seed, env_offset, 1 if bump_step else 0)
+                       hp(o.get("r_state")), seed, env_offset, 1 if bump_step else 0,
+                       1 if want_r_state == "bf16" else 0)
         check(lib().cfx_policy_forward_host(self.h, C.byref(io)))
         return o
 

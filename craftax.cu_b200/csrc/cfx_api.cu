@@ -417,6 +417,7 @@ int cfx_policy_forward(cfx_policy* p, const cfx_forward_io* io, void* stream) {
         a.scratch_h[1] = p->scratch_h[1];
         a.logits_av = io->logits_av ? io->logits_av : p->logits_scratch;
         a.r_state = io->r_state;
+        a.r_state_bf16 = io->r_state_bf16 ? 1 : 0;
         a.env_actions = io->env_actions;
         a.actions = io->actions;
         a.logprobs = io->logprobs;
@@ -438,6 +439,7 @@ int cfx_policy_forward(cfx_policy* p, const cfx_forward_io* io, void* stream) {
         a.values = io->values;
         a.logits_av = io->logits_av;
         a.r_state = io->r_state;
+        a.r_state_bf16 = io->r_state_bf16 ? 1 : 0;
         a.seed = io->seed;
         a.env_offset = io->env_offset;
         a.step_ctr = p->step_ctr;
@@ -503,7 +505,8 @@ int cfx_policy_forward_host(cfx_policy* p, const cfx_forward_io* h) {
     DeviceGuard g(p->device);
     cudaStream_t st = p->stream;
     const size_t n = (size_t)p->n;
-    const size_t lav = n * (size_t)(p->A + 1), rs = (size_t)p->L * n * p->H;
+    // r_state staging in floats: bf16 records take half
+    const size_t lav = n * (size_t)(p->A + 1), rs = (size_t)p->L * n * p->H / (h->r_state_bf16 ? 2 : 1);
     int rc;
     if ((rc = ensure_staging(&p->st_records, n * (size_t)p->rec_bytes))) return rc;
     if ((rc = ensure_staging(&p->st_actions, n))) return rc;
@@ -513,7 +516,7 @@ int cfx_policy_forward_host(cfx_policy* p, const cfx_forward_io* h) {
     if (h->logprobs && (rc = ensure_staging(&p->st_logprobs, n))) return rc;
     if (h->values && (rc = ensure_staging(&p->st_values, n))) return rc;
     if (h->logits_av && (rc = ensure_staging(&p->st_logits, lav))) return rc;
-    if (h->r_state && (rc = ensure_staging(&p->st_r_state, rs))) return rc;
+    if (h->r_state && (rc = ensure_staging(&p->st_r_state, (size_t)p->L * n * p->H))) return rc;
 
     CFX_CUDA(cudaMemcpyAsync(p->st_records, h->records, n * (size_t)p->rec_bytes, cudaMemcpyHostToDevice, st));
     if (h->prev_terminals)

@@ -196,7 +196,8 @@ struct Params {
     float* logprobs;
     float* values;
     float* logits_av;
-    float* r_state;                      // optional [L][n][256] record of the post-zero input state
+    float* r_state;                      // optional [L][n][H] record of the post-zero input state
+    int r_state_bf16;                    // the record holds bf16 instead of fp32
     unsigned long long* step_ctr;        // device step counter (Philox offset); see bump_step
     uint32_t* status;
     uint32_t* done_ctr;                  // blocks that have finished this launch (bump_step)
@@ -1047,9 +1048,19 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                         if (zero_state) st = make_float4(0.f, 0.f, 0.f, 0.f);
                         // optional BPTT record of the post-zero input state (what the reference's
                         // k_mingru_epi_fwd stores, craftax_full.cu:9370-9375): [L][n][256] fp32
-                        if (P.r_state != nullptr && valid)
-                            *reinterpret_cast<float4*>(P.r_state + ((size_t)l * P.n + env) * kH +
-                                                       kSliceUnits * j + kHalfUnits * wg + u) = st;
+                        if (P.r_state != nullptr && valid) {
+                            const size_t o = ((size_t)l * P.n + env) * kH + kSliceUnits * j + kHalfUnits * wg + u;
+                            if (P.r_state_bf16) {
+                                __nv_bfloat162 lo2 = __floats2bfloat162_rn(st.x, st.y);
+                                __nv_bfloat162 hi2 = __floats2bfloat162_rn(st.z, st.w);
+                                uint2 v2;
+                                v2.x = *reinterpret_cast<uint32_t*>(&lo2);
+                                v2.y = *reinterpret_cast<uint32_t*>(&hi2);
+                                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(P.r_state) + o) = v2;
+                            } else {
+                                *reinterpret_cast<float4*>(P.r_state + o) = st;
+                            }
+                        }
                         const float2 x01 = Op::unpack(xin[u / 2]), x23 = Op::unpack(xin[u / 2 + 1]);
                         float4 out;
                         float h0, h1, h2, h3;
@@ -1478,6 +1489,7 @@ int fused_forward(FusedPlan* p, const FusedArgs& a, cudaStream_t st, int* launch
     P.values = a.values;
     P.logits_av = a.logits_av;
     P.r_state = a.r_state;
+    P.r_state_bf16 = a.r_state_bf16;
     P.step_ctr = a.step_ctr;
     P.status = p->status;
     P.done_ctr = p->status + 1;

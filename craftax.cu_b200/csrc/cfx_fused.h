@@ -18,6 +18,7 @@ struct FusedArgs {
     float* values;
     float* logits_av;
     float* r_state;
+    int r_state_bf16;   // r_state holds bf16 instead of fp32
     uint64_t seed, env_offset;
     unsigned long long* step_ctr;
     int bump_step;   // 1: the kernel's last block adds one to *step_ctr when every block is done

@@ -7,6 +7,8 @@
 // reference's full-game build (Makefile:27), so the cell arithmetic rounds at
 // the same places.  It is the high-accuracy mode of the library and the
 // on-device yardstick for the tensor-core kernel at sizes a CPU cannot check.
+#include <cuda_bf16.h>
+
 #include "cfx_common.cuh"
 #include "cfx_sampler.cuh"
 #include "cfx_strict.h"
@@ -158,7 +160,8 @@ __device__ __forceinline__ float mingru_g_ref(float x) { return x >= 0.0f ? x + 
 
 __global__ void k_mingru_fp32(const float* __restrict__ x_in, const float* __restrict__ Wt,
                               float* __restrict__ state, const float* __restrict__ prev_terminals,
-                              float* __restrict__ h_out, float* __restrict__ r_state, int n, int H) {
+                              float* __restrict__ h_out, float* __restrict__ r_state, int r_bf16,
+                              int n, int H) {
     extern __shared__ float xs[];  // [GRU_ENVS][H]
     const int e0 = blockIdx.x * GRU_ENVS;
     const int k = threadIdx.x;
@@ -187,7 +190,10 @@ __global__ void k_mingru_fp32(const float* __restrict__ x_in, const float* __res
         const size_t o = (size_t)(e0 + e) * H + k;
         float st = state[o];
         if (prev_terminals != nullptr && prev_terminals[e0 + e] != 0.0f) st = 0.0f;
-        if (r_state != nullptr) r_state[o] = st;
+        if (r_state != nullptr) {
+            if (r_bf16) reinterpret_cast<__nv_bfloat16*>(r_state)[o] = __float2bfloat16(st);
+            else r_state[o] = st;
+        }
         const float out = st + sigmoid_ref(zg[e]) * (mingru_g_ref(zh[e]) - st);
         const float p = sigmoid_ref(zp[e]);
         h_out[o] = p * out + (1.0f - p) * xs[e * H + k];
@@ -343,7 +349,11 @@ int strict_forward(const StrictArgs& a, cudaStream_t st, int* launches) {
         float* out = a.scratch_h[(l + 1) & 1];
         k_mingru_fp32<<<(n + GRU_ENVS - 1) / GRU_ENVS, H, GRU_ENVS * H * sizeof(float), st>>>(
             x, a.gates_t + (size_t)l * 3 * H * H, a.state + (size_t)l * n * H, a.prev_terminals,
-            out, a.r_state ? a.r_state + (size_t)l * n * H : nullptr, n, H);
+            out,
+            a.r_state ? reinterpret_cast<float*>(reinterpret_cast<char*>(a.r_state) +
+                                                 (size_t)l * n * H * (a.r_state_bf16 ? 2 : 4))
+                      : nullptr,
+            a.r_state_bf16, n, H);
         cnt++;
         x = out;
     }
@@ -434,6 +444,7 @@ extern "C" int cfx_strict_forward_static(int device, const float* params, int hi
     a.scratch_h[1] = base + kStaticGates + kStaticLayerBuf;
     a.logits_av = io->logits_av ? io->logits_av : base + kStaticGates + 2 * kStaticLayerBuf;
     a.r_state = io->r_state;
+    a.r_state_bf16 = io->r_state_bf16 ? 1 : 0;
     a.env_actions = io->env_actions;
     a.actions = io->actions;
     a.logprobs = io->logprobs;

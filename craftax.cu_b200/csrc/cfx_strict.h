@@ -17,6 +17,7 @@ struct StrictArgs {
     float* scratch_h[2];    // [n][H] each
     float* logits_av;       // [n][A+1]
     float* r_state;
+    int r_state_bf16 = 0;   // r_state holds bf16 instead of fp32
     float* env_actions;
     int32_t* actions;
     float* logprobs;

@@ -137,8 +137,9 @@ int cfx_policy_last_launches(const cfx_policy* p);
  * (CuVec.d_actions, read back by the env step), actions int32 [n], logprobs
  * float [n], values float [n]; logits_av float [n][A+1] = logits and value
  * WITH biases added (the reference's scratch holds them before the bias add,
- * :9725-9730); r_state float [L][n][H] = post-zero state inputs for BPTT
- * (:9370-9375; fp32 only).
+ * :9725-9730); r_state [L][n][H] = post-zero state inputs for BPTT
+ * (:9370-9375), 16-byte aligned; fp32, or bf16 (__float2bfloat16 of the same
+ * values, the reference's r_state_bf16 mode) when r_state_bf16 != 0.
  * The recurrent state is updated in place.  The step counter is bumped on
  * the device after the forward when bump_step != 0.
  * No allocation, no host synchronisation and no host-varying kernel argument
@@ -156,6 +157,7 @@ typedef struct cfx_forward_io {
     uint64_t seed;
     uint64_t env_offset;
     int bump_step;
+    int r_state_bf16; /* 1: r_state points to bf16 [L][n][H] instead of fp32 */
 } cfx_forward_io;
 
 int cfx_policy_forward(cfx_policy* p, const cfx_forward_io* io, void* stream);

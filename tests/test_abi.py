@@ -40,7 +40,7 @@ def test_param_count_matches_reference_constants(cfx):
 
 
 def test_forward_io_struct_layout(cfx):
-    assert C.sizeof(cfx.ForwardIO) == 9 * 8 + 2 * 8 + 8  # 9 pointers, 2 u64, int + pad
+    assert C.sizeof(cfx.ForwardIO) == 9 * 8 + 2 * 8 + 8  # 9 pointers, 2 u64, 2 ints
 
 
 def test_invalid_arguments_return_status(cfx):

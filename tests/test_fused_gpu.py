@@ -148,6 +148,12 @@ def test_fused_records_r_state(cfx, gpu, oracle):
         pol.set_state(state)
         d = pol.forward_host(rec, prev_t, None, want_r_state=True)
         assert np.array_equal(d["r_state"], want), prec
+        # the bf16 record (the reference's r_state_bf16 mode): __float2bfloat16 of the same values
+        pol.set_state(state)
+        d = pol.forward_host(rec, prev_t, None, want_r_state="bf16")
+        u = want.view(np.uint32).astype(np.uint64)
+        want_bf = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+        assert d["r_state"].dtype == np.uint16 and np.array_equal(d["r_state"], want_bf), prec
         pol.close()
 
 
