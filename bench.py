@@ -218,10 +218,10 @@ def run_cfx(args):
         roof = {"bound": "tensor", "achieved": n * flops / (kernel_ms * 1e-3) / 1e12,
                 "peak": tensor_peak, "unit": "TFLOP/s"}
     roof["frac"] = roof["achieved"] / roof["peak"]
-    # DRAM bytes per launch: per-env figure of the committed ncu capture (65,536 envs, fp16,
-    # L = 2: 378.15 MB read+write), scaled by envs; only quoted for that configuration
-    roof["traffic"] = (NCU_DRAM_BYTES_PER_ENV * n if (prec in ("f16", "bf16") and H == 256 and L == 2)
-                       else None)
+    # DRAM bytes per launch: per-env figure of the committed ncu captures (fp16, L = 2: hidden
+    # 256 at 65,536 envs, hidden 128 at 131,072 envs), scaled by envs; only quoted for those
+    per_env = NCU_DRAM_BYTES_PER_ENV.get((H, L)) if prec in ("f16", "bf16") else None
+    roof["traffic"] = per_env * n if per_env is not None else None
     roof["peak_source"] = peaks["source"]
     roof["fused_roofline_ms"] = max(t_hbm, t_tensor) * 1e3
     roof["fused_roofline_frac"] = max(t_hbm, t_tensor) * 1e3 / kernel_ms
@@ -526,7 +526,8 @@ def main():
 
 
 DEFAULT_PRECISION = "f16"
-NCU_DRAM_BYTES_PER_ENV = (208.01e6 + 92.44e6) / 65536   # ncu capture at 65,536 envs, see profiles/
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, per env (ncu captures in profiles/)
+NCU_DRAM_BYTES_PER_ENV = {(256, 2): (208.01e6 + 92.44e6) / 65536, (128, 2): (265.93e6 + 109.67e6) / 131072}
 
 if __name__ == "__main__":
     main()
