@@ -839,6 +839,8 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
     const float* bias = sm.bias();
     const uint32_t rec_row_off = ii * kRBoxBytes + gi * 80;
     uint32_t tcnt = 0, gcnt = 0, it = 0;
+    // the sampler offset is constant for the launch (the bump happens after every block is done)
+    const unsigned long long step0 = P.uniforms == nullptr ? *P.step_ctr : 0ull;
     TL_INIT(1 + wg);
     const bool tl_on = (quarter == 0 && lane == 0);
     for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++, tcnt++) {
@@ -1092,6 +1094,11 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
 
         // ---- heads + sampler (wg 0: one thread per env; wg 1 only passes the barrier so
         // that its next-tile operand writes cannot overtake the last MMA)
+        // the uniform of this env is drawn while the head MMAs run
+        float u = 0.0f;
+        if (wg == 0 && valid)
+            u = P.uniforms != nullptr ? P.uniforms[env]
+                                      : philox_uniform(P.seed, P.env_offset + (uint64_t)env, step0);
         CFX_WAITW(H_FULL, tcnt & 1, W_H_FULL);
         if (tl_on) TLB(10, 0xE0000);
         tc_fence_after_sync();
@@ -1134,9 +1141,6 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                         dst[q] = v4;
                     }
                 }
-                const float u = P.uniforms != nullptr
-                                    ? P.uniforms[env]
-                                    : philox_uniform(P.seed, P.env_offset + (uint64_t)env, *P.step_ctr);
                 float lp;
                 const int act = sample_action<kA>(logits, u, &lp);
                 if (P.env_actions) P.env_actions[env] = (float)act;

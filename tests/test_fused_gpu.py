@@ -193,3 +193,49 @@ def test_bounded_wait_reports_a_timeout_and_leaves_the_context_usable(cfx, gpu, 
     assert np.isfinite(d["logits_av"]).all()
     pol.check()
     pol.close()
+
+
+@pytest.mark.parametrize("prec", ["f16", "fp32"])
+def test_forward_replays_from_a_cuda_graph(cfx, gpu, oracle, prec):
+    """cfx_policy_forward allocates nothing, never synchronises and reads the sampler offset from
+    device memory, so one captured forward (with the step bump) replays as a CUDA graph: replay k
+    gives what the k-th eager forward gives (same state evolution, same Philox offsets)."""
+    import torch
+    n, steps = 128 * 5 + 32, 3
+    rng = np.random.default_rng(8)
+    rec = oracle.synthetic_records(n, seed=3)
+    prev_t = (rng.random(n) < 0.1).astype(np.float32)
+    pol = cfx.Policy(n, H, L, A, prec)
+    pol.set_weights(oracle.init_weights(H, L, A, seed=2))
+    d_rec, d_pt = cfx.DeviceBuffer.from_host(rec), cfx.DeviceBuffer.from_host(prev_t)
+    d_act = cfx.DeviceBuffer((n,), np.int32)
+    d_lp = cfx.DeviceBuffer((n,), np.float32)
+    d_lav = cfx.DeviceBuffer((n, A + 1), np.float32)
+    stream = torch.cuda.Stream()
+    sp = stream.cuda_stream
+
+    def forward():
+        pol.forward_device(d_rec, d_pt, None, actions=d_act, logprobs=d_lp, logits_av=d_lav,
+                           seed=9, bump_step=True, stream=sp)
+
+    eager = []
+    for _ in range(steps):
+        forward()
+        pol.check(sp)
+        eager.append((d_act.download().copy(), d_lp.download().copy(), d_lav.download().copy()))
+    assert pol.step == steps
+    pol.reset_state()
+    pol.step = 0
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+        forward()
+    assert pol.step == 0                      # capturing runs nothing
+    for k in range(steps):
+        graph.replay()
+        torch.cuda.synchronize()
+        pol.check()
+        assert np.array_equal(d_act.download(), eager[k][0]), k
+        assert np.array_equal(d_lp.download().view(np.uint32), eager[k][1].view(np.uint32)), k
+        assert np.array_equal(d_lav.download().view(np.uint32), eager[k][2].view(np.uint32)), k
+    assert pol.step == steps
+    pol.close()
