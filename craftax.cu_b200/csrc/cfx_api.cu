@@ -28,6 +28,9 @@ int cuda_fail(cudaError_t e, const char* what, const char* file, int line) {
 
 using namespace cfx;
 
+constexpr int kHostSlicesMax = 8;
+constexpr size_t kHostSliceEnvs = 32768;   // smallest slice of the pipelined host-buffer forward
+
 // The handle: role of CuPolicy (craftax_full.cu:11758-11796).
 struct cfx_policy {
     int device = 0;
@@ -54,6 +57,10 @@ struct cfx_policy {
     float* st_values = nullptr;
     float* st_logits = nullptr;
     float* st_r_state = nullptr;
+    // cfx_policy_forward_host: copy stream and per-slice events of the pipelined upload
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t slice_ready[kHostSlicesMax] = {};
+    cudaEvent_t host_fence = nullptr;
 };
 
 static void free_dev(void* p) {
@@ -210,6 +217,10 @@ int cfx_policy_destroy(cfx_policy* p) {
     free_dev(p->st_values);
     free_dev(p->st_logits);
     free_dev(p->st_r_state);
+    for (int i = 0; i < kHostSlicesMax; i++)
+        if (p->slice_ready[i]) cudaEventDestroy(p->slice_ready[i]);
+    if (p->host_fence) cudaEventDestroy(p->host_fence);
+    if (p->copy_stream) cudaStreamDestroy(p->copy_stream);
     if (p->stream) cudaStreamDestroy(p->stream);
     delete p;
     return CFX_OK;
@@ -395,7 +406,9 @@ void* cfx_policy_stream(cfx_policy* p) { return p ? (void*)p->stream : nullptr; 
 int cfx_policy_last_launches(const cfx_policy* p) { return p ? p->last_launches : 0; }
 
 // ------------------------------------------------------------------ forward
-int cfx_policy_forward(cfx_policy* p, const cfx_forward_io* io, void* stream) {
+// One forward over the 128-env tiles [tile_begin, tile_end) of the batch (tile_end = 0: all;
+// slices are a fused-kernel feature, used by the pipelined host-buffer forward).
+static int forward_range(cfx_policy* p, const cfx_forward_io* io, void* stream, int tile_begin, int tile_end) {
     CFX_REQUIRE(p && io, "cfx_policy_forward: NULL argument");
     CFX_REQUIRE(io->records != nullptr, "cfx_policy_forward: records is NULL");
     CFX_REQUIRE(((uintptr_t)io->records & 15) == 0, "cfx_policy_forward: records not 16-byte aligned");
@@ -444,6 +457,8 @@ int cfx_policy_forward(cfx_policy* p, const cfx_forward_io* io, void* stream) {
         a.env_offset = io->env_offset;
         a.step_ctr = p->step_ctr;
         a.bump_step = io->bump_step ? 1 : 0;   // folded into the kernel: no extra launch
+        a.tile_begin = tile_begin;
+        a.tile_end = tile_end;
         rc = fused_forward(p->fused, a, st, &launches);
     }
     if (rc) return rc;
@@ -454,6 +469,10 @@ int cfx_policy_forward(cfx_policy* p, const cfx_forward_io* io, void* stream) {
     }
     p->last_launches = launches;
     return CFX_OK;
+}
+
+int cfx_policy_forward(cfx_policy* p, const cfx_forward_io* io, void* stream) {
+    return forward_range(p, io, stream, 0, 0);
 }
 
 }  // extern "C"
@@ -518,13 +537,6 @@ int cfx_policy_forward_host(cfx_policy* p, const cfx_forward_io* h) {
     if (h->logits_av && (rc = ensure_staging(&p->st_logits, lav))) return rc;
     if (h->r_state && (rc = ensure_staging(&p->st_r_state, (size_t)p->L * n * p->H))) return rc;
 
-    CFX_CUDA(cudaMemcpyAsync(p->st_records, h->records, n * (size_t)p->rec_bytes, cudaMemcpyHostToDevice, st));
-    if (h->prev_terminals)
-        CFX_CUDA(cudaMemcpyAsync(p->st_terminals, h->prev_terminals, n * sizeof(float),
-                                 cudaMemcpyHostToDevice, st));
-    if (h->uniforms)
-        CFX_CUDA(cudaMemcpyAsync(p->st_uniforms, h->uniforms, n * sizeof(float),
-                                 cudaMemcpyHostToDevice, st));
     cfx_forward_io d = *h;
     d.records = p->st_records;
     d.prev_terminals = h->prev_terminals ? p->st_terminals : nullptr;
@@ -535,8 +547,62 @@ int cfx_policy_forward_host(cfx_policy* p, const cfx_forward_io* h) {
     d.values = h->values ? p->st_values : nullptr;
     d.logits_av = h->logits_av ? p->st_logits : nullptr;
     d.r_state = h->r_state ? p->st_r_state : nullptr;
-    rc = cfx_policy_forward(p, &d, st);
-    if (rc) return rc;
+
+    // The record upload dominates a host-buffer step (996 bytes per env over PCIe against
+    // ~1.6 ns of kernel time).  With the fused kernel and a large batch the records go up in
+    // slices on a copy stream and the kernel runs slice by slice behind them (a launch takes a
+    // tile range), so that only the last slice's kernel is not hidden under the upload.
+    const int tiles = (int)((n + 127) / 128);
+    int slices = 1;
+    if (p->precision != CFX_PREC_FP32) {
+        slices = (int)(n / kHostSliceEnvs);
+        slices = slices < 1 ? 1 : (slices > kHostSlicesMax ? kHostSlicesMax : slices);
+    }
+    if (slices == 1) {
+        CFX_CUDA(cudaMemcpyAsync(p->st_records, h->records, n * (size_t)p->rec_bytes, cudaMemcpyHostToDevice, st));
+        if (h->prev_terminals)
+            CFX_CUDA(cudaMemcpyAsync(p->st_terminals, h->prev_terminals, n * sizeof(float),
+                                     cudaMemcpyHostToDevice, st));
+        if (h->uniforms)
+            CFX_CUDA(cudaMemcpyAsync(p->st_uniforms, h->uniforms, n * sizeof(float),
+                                     cudaMemcpyHostToDevice, st));
+        rc = cfx_policy_forward(p, &d, st);
+        if (rc) return rc;
+    } else {
+        if (!p->copy_stream) {
+            CFX_CUDA(cudaStreamCreateWithFlags(&p->copy_stream, cudaStreamNonBlocking));
+            CFX_CUDA(cudaEventCreateWithFlags(&p->host_fence, cudaEventDisableTiming));
+            for (int i = 0; i < kHostSlicesMax; i++)
+                CFX_CUDA(cudaEventCreateWithFlags(&p->slice_ready[i], cudaEventDisableTiming));
+        }
+        cudaStream_t cs = p->copy_stream;
+        // the staging buffers may still be read by work queued earlier on the handle's stream
+        CFX_CUDA(cudaEventRecord(p->host_fence, st));
+        CFX_CUDA(cudaStreamWaitEvent(cs, p->host_fence, 0));
+        if (h->prev_terminals)
+            CFX_CUDA(cudaMemcpyAsync(p->st_terminals, h->prev_terminals, n * sizeof(float),
+                                     cudaMemcpyHostToDevice, cs));
+        if (h->uniforms)
+            CFX_CUDA(cudaMemcpyAsync(p->st_uniforms, h->uniforms, n * sizeof(float),
+                                     cudaMemcpyHostToDevice, cs));
+        int per = (tiles + slices - 1) / slices;
+        per += per & 1;   // slices start at even tiles (CTA pairs)
+        int launches = 0;
+        for (int k = 0, t0 = 0; t0 < tiles; k++, t0 += per) {
+            const int t1 = t0 + per < tiles ? t0 + per : tiles;
+            const size_t e0 = (size_t)t0 * 128, e1 = (size_t)t1 * 128 < n ? (size_t)t1 * 128 : n;
+            CFX_CUDA(cudaMemcpyAsync(p->st_records + e0 * p->rec_bytes, h->records + e0 * p->rec_bytes,
+                                     (e1 - e0) * (size_t)p->rec_bytes, cudaMemcpyHostToDevice, cs));
+            CFX_CUDA(cudaEventRecord(p->slice_ready[k], cs));
+            CFX_CUDA(cudaStreamWaitEvent(st, p->slice_ready[k], 0));
+            cfx_forward_io dk = d;
+            dk.bump_step = (t1 == tiles) ? h->bump_step : 0;   // the last slice bumps the counter
+            rc = forward_range(p, &dk, st, t0, t1);
+            if (rc) return rc;
+            launches += p->last_launches;
+        }
+        p->last_launches = launches;
+    }
     CFX_CUDA(cudaMemcpyAsync(h->actions, p->st_actions, n * sizeof(int32_t), cudaMemcpyDeviceToHost, st));
     if (h->env_actions)
         CFX_CUDA(cudaMemcpyAsync(h->env_actions, p->st_env_actions, n * sizeof(float), cudaMemcpyDeviceToHost, st));

@@ -203,7 +203,8 @@ struct Params {
     uint32_t* done_ctr;                  // blocks that have finished this launch (bump_step)
     int bump_step;
     uint64_t seed, env_offset;
-    int n, L, num_tiles;
+    int n, L, num_tiles;  // num_tiles: end of the tile range of this launch (exclusive)
+    int tile_begin;       // first tile of this launch (a launch may cover a slice of the envs)
     int rec_bytes;        // bytes of one record (996 full game, 148 classic)
     int num_tiles_loop;   // trip bound of the tile loops: num_tiles, rounded up to even for CTA pairs
     size_t off_b_enc, off_b_a, off_b_v;
@@ -522,7 +523,7 @@ __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& 
     const size_t enc_bytes = fused::enc_bytes<GAME, HID>();
     uint32_t cnt = 0;
     TL_INIT(3);
-    for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x) {
+    for (int tile = P.tile_begin + blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x) {
         for (int s = 0; s < kEncChunks + stages_gate + 1; s++, cnt++) {
             if ((int)(cnt % C::kWLanes) != lane) continue;
             uint32_t bytes;
@@ -571,7 +572,7 @@ __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& 
         // classic: the records of the whole tile are one box, 32 rows of four 148-byte records
         // (a [n/4][148] array of 32-bit words), into the buffer the full game uses for its tail
         const uint32_t dst = smem_u32(sm.t_buf());
-        for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
+        for (int tile = P.tile_begin + blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
             CFX_WAIT(T_EMPTY, (it & 1) ^ 1, W_T_EMPTY);
             mbar_arrive_expect_tx(sm.bar(T_FULL), 128 * kClassicRec);
             tensor_g2s_2d(dst, &P.rec_map, 0, tile * 32, sm.bar(T_FULL));
@@ -579,7 +580,7 @@ __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& 
     } else if (lane < kNR) {
         // lane `lane` owns ring slot `lane` and issues all four boxes of the fills that land on it
         const uint32_t slot_addr = smem_u32(sm.r_slot(lane));
-        for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
+        for (int tile = P.tile_begin + blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
             // ring inside the state slots: before the first fill of the tile the previous
             // tile's last state box must have left this slot
             if (C::kAlias) CFX_WAIT(S_DONE + lane, (it & 1) ^ 1, W_S_DONE);
@@ -600,7 +601,7 @@ __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& 
         // the tail lane: three box sets cover the 51 raw floats (204 bytes from byte 792) of
         // every record; they go to a buffer of their own, read by warpgroup 0 only
         const uint32_t dst = smem_u32(sm.t_buf());
-        for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
+        for (int tile = P.tile_begin + blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
             CFX_WAIT(T_EMPTY, (it & 1) ^ 1, W_T_EMPTY);
 #ifdef CFX_ABL_NOREC
             mbar_arrive(sm.bar(T_FULL));
@@ -630,7 +631,7 @@ __device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P,
     constexpr int kNS = C::kNS;
     uint32_t cnt = 0, uses = 0, it = 0;
     const uint32_t slot_addr = smem_u32(sm.s_slot(lane));
-    for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
+    for (int tile = P.tile_begin + blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
         for (int l = 0; l < P.L; l++) {
             for (int j = 0; j < kStateItems; j++, cnt++) {
                 if ((int)(cnt % kNS) != lane) continue;
@@ -713,7 +714,7 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
 #ifdef CFX_PROFILE
     if (blockIdx.x == 0 && P.timeline != nullptr) P.timeline[4 * 4096 + 3] = (long long)global_timer_ns();
 #endif
-    for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, tcnt++) {
+    for (int tile = P.tile_begin + blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, tcnt++) {
         TLB(0, 0x1000000);
         // the encoder accumulator overlaps the head accumulator of the previous tile:
         // wait until the sampler threads have read it
@@ -843,7 +844,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
     const unsigned long long step0 = P.uniforms == nullptr ? *P.step_ctr : 0ull;
     TL_INIT(1 + wg);
     const bool tl_on = (quarter == 0 && lane == 0);
-    for (int tile = blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++, tcnt++) {
+    for (int tile = P.tile_begin + blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++, tcnt++) {
         if (tl_on) TLB(0, 0x1000000);
         const int env = tile * kTile + row;
         const bool valid = env < P.n;
@@ -1502,7 +1503,17 @@ int fused_forward(FusedPlan* p, const FusedArgs& a, cudaStream_t st, int* launch
     P.env_offset = a.env_offset;
     P.n = p->n;
     P.L = p->L;
-    P.num_tiles = (p->n + fused::kTile - 1) / fused::kTile;
+    const int all_tiles = (p->n + fused::kTile - 1) / fused::kTile;
+    P.tile_begin = a.tile_end > 0 ? a.tile_begin : 0;
+    P.num_tiles = a.tile_end > 0 ? a.tile_end : all_tiles;
+    // a CTA pair works on tiles 2c, 2c + 1: a slice must start at an even tile, and only the
+    // slice that ends the batch may hold an odd number of tiles (its filler tile lies beyond n)
+    if (P.tile_begin < 0 || P.num_tiles > all_tiles || P.tile_begin >= P.num_tiles || (P.tile_begin & 1) ||
+        ((P.num_tiles & 1) && P.num_tiles != all_tiles)) {
+        set_error("fused forward: bad tile range [%d, %d) of %d", P.tile_begin, P.num_tiles, all_tiles);
+        return CFX_ERR_INVALID;
+    }
+    const int range_tiles = P.num_tiles - P.tile_begin;
     P.off_b_enc = o.b_enc;
     P.off_b_a = o.b_a;
     P.off_b_v = o.b_v;
@@ -1516,15 +1527,15 @@ int fused_forward(FusedPlan* p, const FusedArgs& a, cudaStream_t st, int* launch
     cfg.stream = st;
     cudaLaunchAttribute at;
     if (p->pair) {
-        const int pairs = (P.num_tiles + 1) / 2;
-        P.num_tiles_loop = 2 * pairs;
+        const int pairs = (range_tiles + 1) / 2;
+        P.num_tiles_loop = P.tile_begin + 2 * pairs;
         cfg.gridDim = dim3(2u * (unsigned)(pairs < p->max_pairs ? pairs : p->max_pairs));
         at.id = cudaLaunchAttributeClusterDimension;
         at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
         cfg.attrs = &at; cfg.numAttrs = 1;
     } else {
         P.num_tiles_loop = P.num_tiles;
-        cfg.gridDim = dim3((unsigned)(P.num_tiles < p->sm_count ? P.num_tiles : p->sm_count));
+        cfg.gridDim = dim3((unsigned)(range_tiles < p->sm_count ? range_tiles : p->sm_count));
     }
     CFX_CUDA(cudaLaunchKernelExC(&cfg, kern, kargs));
     CFX_CUDA(cudaGetLastError());

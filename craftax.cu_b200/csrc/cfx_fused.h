@@ -22,6 +22,9 @@ struct FusedArgs {
     uint64_t seed, env_offset;
     unsigned long long* step_ctr;
     int bump_step;   // 1: the kernel's last block adds one to *step_ctr when every block is done
+    // 128-env tiles [tile_begin, tile_end) of the batch; tile_end = 0: all.  tile_begin must be
+    // even, and tile_end even unless it is the end of the batch.
+    int tile_begin = 0, tile_end = 0;
 };
 
 // Shapes the fused kernel is instantiated for.

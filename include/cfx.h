@@ -178,7 +178,10 @@ int cfx_selftest_wait_timeout(int device, unsigned limit_ms);
 
 /* Same forward with HOST buffers (pinned for full copy speed): copies
  * records/prev_terminals/uniforms to handle-owned device staging, runs
- * cfx_policy_forward, copies every non-NULL output back and synchronises. */
+ * cfx_policy_forward, copies every non-NULL output back and synchronises.
+ * With the fused kernel and at least 65,536 envs the records go up in slices
+ * of >= 32,768 envs on a second stream and the kernel is launched once per
+ * slice behind them (same results; cfx_policy_last_launches counts them). */
 int cfx_policy_forward_host(cfx_policy* p, const cfx_forward_io* host_io);
 
 /* Strict-fp32 forward for callers that cannot allocate device memory while they run -- a

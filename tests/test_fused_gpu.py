@@ -239,3 +239,40 @@ def test_forward_replays_from_a_cuda_graph(cfx, gpu, oracle, prec):
         assert np.array_equal(d_lav.download().view(np.uint32), eager[k][2].view(np.uint32)), k
     assert pol.step == steps
     pol.close()
+
+
+@pytest.mark.parametrize("n", [65536 + 128 * 3 + 32, 32768 * 5])
+def test_host_forward_in_slices_equals_one_launch(cfx, gpu, oracle, n):
+    """From 65,536 envs cfx_policy_forward_host uploads the records in slices on a copy stream and
+    launches the kernel per slice (a tile range) behind them.  The result must be what one launch
+    over device-resident inputs gives, bit for bit, including the step bump and the r_state record."""
+    rng = np.random.default_rng(n)
+    base = oracle.synthetic_records(4096, seed=6)
+    rec = base[rng.integers(0, 4096, n)]
+    params = oracle.init_weights(H, L, A, seed=12)
+    state = rng.normal(0, 1, (L, n, H)).astype(np.float32)
+    prev_t = (rng.random(n) < 0.1).astype(np.float32)
+    pol = cfx.Policy(n, H, L, A, "f16")
+    pol.set_weights(params)
+    pol.set_state(state)
+    pol.step = 4
+    d_rec, d_pt = cfx.DeviceBuffer.from_host(rec), cfx.DeviceBuffer.from_host(prev_t)
+    d_act = cfx.DeviceBuffer((n,), np.int32)
+    d_lp = cfx.DeviceBuffer((n,), np.float32)
+    d_lav = cfx.DeviceBuffer((n, A + 1), np.float32)
+    d_rs = cfx.DeviceBuffer((L, n, H), np.float32)
+    pol.forward_device(d_rec, d_pt, None, actions=d_act, logprobs=d_lp, logits_av=d_lav, r_state=d_rs,
+                       seed=3, bump_step=True)
+    pol.check()
+    assert pol.last_launches == 1 and pol.step == 5
+    want = (d_act.download(), d_lp.download(), d_lav.download(), d_rs.download(), pol.get_state())
+    pol.set_state(state)
+    pol.step = 4
+    d = pol.forward_host(rec, prev_t, None, seed=3, bump_step=True, want_r_state=True)
+    assert pol.last_launches == max(1, min(8, n // 32768)) and pol.step == 5
+    assert np.array_equal(d["actions"], want[0])
+    assert np.array_equal(d["logprobs"].view(np.uint32), want[1].view(np.uint32))
+    assert np.array_equal(d["logits_av"].view(np.uint32), want[2].view(np.uint32))
+    assert np.array_equal(d["r_state"], want[3])
+    assert np.array_equal(pol.get_state(), want[4])
+    pol.close()

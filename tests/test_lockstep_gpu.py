@@ -61,7 +61,9 @@ def _lockstep(cfx, oracle, n, steps, layers, env_seed, weight_seed):
         hist += np.bincount(d["actions"], minlength=A)
         env.step(d["actions"].astype(np.float32))
     assert pol.step == steps             # the step counter is bumped inside the fused kernel
-    assert pol.last_launches == 1
+    # one launch per forward; from 65,536 envs the host-buffer entry point uploads the records in
+    # slices of >= 32,768 envs and launches the kernel once per slice behind the copies
+    assert pol.last_launches == max(1, min(8, n // 32768))
     pol.close(); side.close(); env.close()
     return worst, agree / (steps * n), resets, hist, side.kind
 
