@@ -358,6 +358,60 @@ __device__ __forceinline__ void mingru_cell(float zh, float zg, float zp, float 
     h = fmaf(p, out - x, x);
 }
 
+// The same cell for two units at once with the packed fp32 instructions of sm_100
+// (`fma.rn.f32x2` and friends: two results per issue slot, the same roundings as the scalar
+// forms, so the results are bit-identical to mingru_cell).  The cell phase is bound by
+// instruction issue (two worker warps per scheduler), not by the FMA or SFU pipes.
+__device__ __forceinline__ uint64_t f2pack(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void f2unpack(uint64_t v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2mul(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2add(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2sub(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ void mingru_cell_pair(float zh0, float zh1, float zg0, float zg1, float zp0,
+                                                 float zp1, float st0, float st1, float x0, float x1,
+                                                 float& out0, float& out1, float& h0, float& h1) {
+    const uint64_t half2 = f2pack(0.5f, 0.5f);
+    const uint64_t zh = f2pack(zh0, zh1), st = f2pack(st0, st1), x = f2pack(x0, x1);
+    float a0, a1, b0, b1, c0, c1;
+    f2unpack(f2mul(zh, half2), a0, a1);
+    f2unpack(f2mul(f2pack(zg0, zg1), half2), b0, b1);
+    f2unpack(f2mul(f2pack(zp0, zp1), half2), c0, c1);
+    const uint64_t th = f2pack(tanh_fast(a0), tanh_fast(a1));
+    const uint64_t tg = f2pack(tanh_fast(b0), tanh_fast(b1));
+    const uint64_t tp = f2pack(tanh_fast(c0), tanh_fast(c1));
+    const uint64_t sg = f2fma(tg, half2, half2), p = f2fma(tp, half2, half2);
+    float m0, m1;
+    f2unpack(f2mul(th, half2), m0, m1);
+    const uint64_t gh = f2add(half2, f2pack(fmaxf(zh0, m0), fmaxf(zh1, m1)));
+    const uint64_t out = f2fma(sg, f2sub(gh, st), st);
+    const uint64_t h = f2fma(p, f2sub(out, x), x);
+    f2unpack(out, out0, out1);
+    f2unpack(h, h0, h1);
+}
+
 struct Smem {
     uint8_t* base;
     int off_s, off_r, r_stride, off_t, off_bias, off_bars, off_misc, b_slot_bytes;
@@ -1067,6 +1121,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                         const float2 x01 = Op::unpack(xin[u / 2]), x23 = Op::unpack(xin[u / 2 + 1]);
                         float4 out;
                         float h0, h1, h2, h3;
+#ifdef CFX_CELL_SCALAR
                         mingru_cell(__uint_as_float(zh[u]), __uint_as_float(zg[u]),
                                     __uint_as_float(zp[u]), st.x, x01.x, out.x, h0);
                         mingru_cell(__uint_as_float(zh[u + 1]), __uint_as_float(zg[u + 1]),
@@ -1075,6 +1130,16 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                                     __uint_as_float(zp[u + 2]), st.z, x23.x, out.z, h2);
                         mingru_cell(__uint_as_float(zh[u + 3]), __uint_as_float(zg[u + 3]),
                                     __uint_as_float(zp[u + 3]), st.w, x23.y, out.w, h3);
+#else
+                        mingru_cell_pair(__uint_as_float(zh[u]), __uint_as_float(zh[u + 1]),
+                                         __uint_as_float(zg[u]), __uint_as_float(zg[u + 1]),
+                                         __uint_as_float(zp[u]), __uint_as_float(zp[u + 1]),
+                                         st.x, st.y, x01.x, x01.y, out.x, out.y, h0, h1);
+                        mingru_cell_pair(__uint_as_float(zh[u + 2]), __uint_as_float(zh[u + 3]),
+                                         __uint_as_float(zg[u + 2]), __uint_as_float(zg[u + 3]),
+                                         __uint_as_float(zp[u + 2]), __uint_as_float(zp[u + 3]),
+                                         st.z, st.w, x23.x, x23.y, out.z, out.w, h2, h3);
+#endif
                         *sp = out;
                         hn[2 * q] = Op::pack(h0, h1);
                         hn[2 * q + 1] = Op::pack(h2, h3);
