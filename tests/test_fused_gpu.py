@@ -241,7 +241,7 @@ def test_forward_replays_from_a_cuda_graph(cfx, gpu, oracle, prec):
     pol.close()
 
 
-@pytest.mark.parametrize("n", [65536 + 128 * 3 + 32, 32768 * 5])
+@pytest.mark.parametrize("n", [65536 + 32, 65536 + 128 * 3 + 32, 32768 * 5])
 def test_host_forward_in_slices_equals_one_launch(cfx, gpu, oracle, n):
     """From 65,536 envs cfx_policy_forward_host uploads the records in slices on a copy stream and
     launches the kernel per slice (a tile range) behind them.  The result must be what one launch
