@@ -69,3 +69,39 @@ def test_full_size_fused_forward_properties(cfx, gpu, oracle):
         got = np.concatenate([p[0][key] for p in parts])
         assert np.array_equal(got.view(np.uint32), d16[key].view(np.uint32)), key
     assert np.array_equal(np.concatenate([p[1] for p in parts], axis=1), st16)
+
+
+def test_classic_large_batch_properties(cfx, gpu, oracle):
+    """Classic game (148-byte records, 3 layers, 17 actions) at 262,144 envs: fused kernel against
+    the fp32 device path, and env slices against the whole batch."""
+    n, layers, actions = 262144, 3, 17
+    rng = np.random.default_rng(7)
+    base = oracle.classic_synthetic_records(8192, seed=15)
+    rec = base[rng.integers(0, 8192, n)]
+    params = oracle.classic_init_weights(H, layers, actions, seed=16)
+    state = rng.standard_normal((layers, n, H), dtype=np.float32)
+    flags = (rng.random(n) < 0.01).astype(np.float32)
+
+    def run(prec, lo, hi):
+        pol = cfx.Policy(hi - lo, H, layers, actions, prec, game="classic")
+        pol.set_weights(params)
+        pol.set_state(state[:, lo:hi])
+        d = pol.forward_host(rec[lo:hi], flags[lo:hi], None, seed=5, env_offset=lo)
+        d = {k: v.copy() for k, v in d.items()}
+        st = pol.get_state()
+        pol.close()
+        return d, st
+
+    d16, st16 = run("f16", 0, n)
+    d32, st32 = run("fp32", 0, n)
+    err = float(np.abs(d16["logits_av"] - d32["logits_av"]).max())
+    agree = float((d16["logits_av"][:, :actions].argmax(1) == d32["logits_av"][:, :actions].argmax(1)).mean())
+    print(f"[classic 262144 envs] max|dlogit|={err:.3e} greedy={agree:.5f}")
+    assert err < 2e-2
+    assert agree >= 0.99
+    assert np.abs(st16 - st32).max() < 2e-2
+    parts = [run("f16", 0, n // 2), run("f16", n // 2, n)]
+    for key in ("logits_av", "actions", "logprobs", "values"):
+        got = np.concatenate([p[0][key] for p in parts])
+        assert np.array_equal(got.view(np.uint32), d16[key].view(np.uint32)), key
+    assert np.array_equal(np.concatenate([p[1] for p in parts], axis=1), st16)
