@@ -257,9 +257,20 @@ def cpu_forward_rate(H, L, budget_s=15.0, steps=1, warmup=0, threads=0):
     """Times the CPU arm: the reference's C env (when its prebuilt producer is present)
     stepping a bounded sample of envs plus the oracle's fp32 host forward on all host
     threads.  Returns the cpu_baseline object."""
+    # all host threads this process may use: torchrun exports OMP_NUM_THREADS=1 to its workers,
+    # which would make the CPU arm single-threaded whenever it is launched for N > 1
+    host = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    if not threads:
+        os.environ["OMP_NUM_THREADS"] = str(host)
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import oracle as O
-    cores = threads or O.max_threads()
+    if not threads:
+        try:   # the OpenMP runtime may already be up: set its default team size as well
+            import ctypes
+            ctypes.CDLL("libgomp.so.1").omp_set_num_threads(host)
+        except OSError:
+            pass
+    cores = threads or max(host, O.max_threads())
     params = O.init_weights(H, L, A, seed=0)
     probe = 64 * cores
     rec = O.synthetic_records(probe, seed=4)
