@@ -77,7 +77,6 @@ template <> struct Gm<CFX_GAME_CLASSIC> {
     static constexpr int kA = 17, kEncChunks = 22, kRecFills = 0, kRecBytes = kClassicRec;
     static constexpr int kHeadSingle = 32, kHeadPair = 32;
 };
-constexpr int kMaxEncChunks = 22;
 
 constexpr int kNBMax = 8;        // weight ring slots (one stage each): see Cfg
 // Ring shapes of the CTA-pair mode (compile-time tuning knobs; measured at 262,144 envs: 6 or 8
