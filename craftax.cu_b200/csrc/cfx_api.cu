@@ -122,13 +122,13 @@ size_t cfx_classic_param_count(int hidden, int layers, int num_actions) {
 
 int cfx_classic_expand_obs(int device, const uint8_t* records, float* out, int num_envs, void* stream) {
     CFX_REQUIRE(records && out && num_envs > 0, "cfx_classic_expand_obs: bad arguments");
-    DeviceGuard g(device);
+    CFX_GUARD(device);
     return launch_classic_expand(records, out, num_envs, (cudaStream_t)stream);
 }
 
 int cfx_classic_done_to_terminals(int device, const int8_t* done, float* out, int num_envs, void* stream) {
     CFX_REQUIRE(done && out && num_envs > 0, "cfx_classic_done_to_terminals: bad arguments");
-    DeviceGuard g(device);
+    CFX_GUARD(device);
     return launch_done_to_terminals(done, out, num_envs, (cudaStream_t)stream);
 }
 
@@ -148,7 +148,7 @@ static int policy_create(cfx_policy** out, int device, int num_envs, int hidden,
     int ndev = 0;
     CFX_CUDA(cudaGetDeviceCount(&ndev));
     CFX_REQUIRE(device >= 0 && device < ndev, "cfx_policy_create: device %d of %d", device, ndev);
-    DeviceGuard g(device);
+    CFX_GUARD(device);
     cfx_policy* p = new (std::nothrow) cfx_policy();
     CFX_REQUIRE(p != nullptr, "cfx_policy_create: out of host memory");
     p->device = device;
@@ -198,7 +198,7 @@ static int policy_create(cfx_policy** out, int device, int num_envs, int hidden,
 
 int cfx_policy_destroy(cfx_policy* p) {
     if (!p) return CFX_OK;
-    DeviceGuard g(p->device);
+    DeviceGuard g(p->device);   // best effort: the handle is released whatever happens
     if (p->stream) cudaStreamSynchronize(p->stream);
     if (p->fused) fused_destroy(p->fused);
     free_dev(p->params);
@@ -230,7 +230,7 @@ int cfx_policy_set_weights(cfx_policy* p, const float* arena, size_t count, int 
     CFX_REQUIRE(p && arena, "cfx_policy_set_weights: NULL argument");
     CFX_REQUIRE(count == p->param_count, "cfx_policy_set_weights: count %zu != %zu", count,
                 p->param_count);
-    DeviceGuard g(p->device);
+    CFX_GUARD(p->device);
     CFX_CUDA(cudaMemcpyAsync(p->params, arena, count * sizeof(float),
                              on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice,
                              p->stream));
@@ -244,7 +244,7 @@ int cfx_policy_get_weights(cfx_policy* p, float* host_arena, size_t count) {
     CFX_REQUIRE(p && host_arena, "cfx_policy_get_weights: NULL argument");
     CFX_REQUIRE(count == p->param_count, "cfx_policy_get_weights: count %zu != %zu", count,
                 p->param_count);
-    DeviceGuard g(p->device);
+    CFX_GUARD(p->device);
     CFX_CUDA(cudaMemcpyAsync(host_arena, p->params, count * sizeof(float), cudaMemcpyDeviceToHost,
                              p->stream));
     CFX_CUDA(cudaStreamSynchronize(p->stream));
@@ -253,7 +253,7 @@ int cfx_policy_get_weights(cfx_policy* p, float* host_arena, size_t count) {
 
 int cfx_policy_init_weights(cfx_policy* p, uint64_t seed) {
     CFX_REQUIRE(p, "cfx_policy_init_weights: NULL handle");
-    DeviceGuard g(p->device);
+    CFX_GUARD(p->device);
     const ArenaLayout o = ArenaLayout::make(p->H, p->L, p->A, p->obs);
     const float be = 1.0f / sqrtf((float)p->obs), bh = 1.0f / sqrtf((float)p->H);
     const struct { size_t off; size_t count; float bound; } segs[7] = {
@@ -340,7 +340,7 @@ int cfx_policy_set_precision(cfx_policy* p, int precision) {
     CFX_REQUIRE(precision >= CFX_PREC_FP32 && precision <= CFX_PREC_TF32,
                 "cfx_policy_set_precision: unknown precision %d", precision);
     if (precision == p->precision) return CFX_OK;
-    DeviceGuard g(p->device);
+    CFX_GUARD(p->device);
     CFX_CUDA(cudaStreamSynchronize(p->stream));
     const int old = p->precision;
     p->precision = precision;
@@ -370,7 +370,7 @@ float* cfx_policy_state(cfx_policy* p) { return p ? p->state : nullptr; }
 
 int cfx_policy_reset_state(cfx_policy* p, void* stream) {
     CFX_REQUIRE(p, "cfx_policy_reset_state: NULL handle");
-    DeviceGuard g(p->device);
+    CFX_GUARD(p->device);
     cudaStream_t st = stream ? (cudaStream_t)stream : p->stream;
     CFX_CUDA(cudaMemsetAsync(p->state, 0, (size_t)p->L * p->n * p->H * sizeof(float), st));
     return CFX_OK;
@@ -378,7 +378,7 @@ int cfx_policy_reset_state(cfx_policy* p, void* stream) {
 
 int cfx_policy_set_step(cfx_policy* p, uint64_t step, void* stream) {
     CFX_REQUIRE(p, "cfx_policy_set_step: NULL handle");
-    DeviceGuard g(p->device);
+    CFX_GUARD(p->device);
     cudaStream_t st = stream ? (cudaStream_t)stream : p->stream;
     unsigned long long v = step;
     CFX_CUDA(cudaMemcpyAsync(p->step_ctr, &v, sizeof(v), cudaMemcpyHostToDevice, st));
@@ -388,7 +388,7 @@ int cfx_policy_set_step(cfx_policy* p, uint64_t step, void* stream) {
 
 int cfx_policy_get_step(cfx_policy* p, uint64_t* step) {
     CFX_REQUIRE(p && step, "cfx_policy_get_step: NULL argument");
-    DeviceGuard g(p->device);
+    CFX_GUARD(p->device);
     unsigned long long v = 0;
     CFX_CUDA(cudaMemcpyAsync(&v, p->step_ctr, sizeof(v), cudaMemcpyDeviceToHost, p->stream));
     CFX_CUDA(cudaStreamSynchronize(p->stream));
@@ -398,7 +398,7 @@ int cfx_policy_get_step(cfx_policy* p, uint64_t* step) {
 
 int cfx_policy_bump_step(cfx_policy* p, void* stream) {
     CFX_REQUIRE(p, "cfx_policy_bump_step: NULL handle");
-    DeviceGuard g(p->device);
+    CFX_GUARD(p->device);
     return launch_bump(p->step_ctr, stream ? (cudaStream_t)stream : p->stream);
 }
 
@@ -413,7 +413,7 @@ static int forward_range(cfx_policy* p, const cfx_forward_io* io, void* stream, 
     CFX_REQUIRE(io->records != nullptr, "cfx_policy_forward: records is NULL");
     CFX_REQUIRE(((uintptr_t)io->records & 15) == 0, "cfx_policy_forward: records not 16-byte aligned");
     CFX_REQUIRE(io->actions != nullptr, "cfx_policy_forward: actions is NULL");
-    DeviceGuard g(p->device);
+    CFX_GUARD(p->device);
     cudaStream_t st = stream ? (cudaStream_t)stream : p->stream;
     int launches = 0, rc;
     if (p->precision == CFX_PREC_FP32) {
@@ -479,7 +479,7 @@ int cfx_policy_forward(cfx_policy* p, const cfx_forward_io* io, void* stream) {
 
 extern "C" int cfx_policy_check(cfx_policy* p, void* stream) {
     CFX_REQUIRE(p, "cfx_policy_check: NULL handle");
-    DeviceGuard g(p->device);
+    CFX_GUARD(p->device);
     cudaStream_t st = stream ? (cudaStream_t)stream : p->stream;
     CFX_CUDA(cudaStreamSynchronize(st));
     if (p->fused) {
@@ -496,7 +496,7 @@ extern "C" int cfx_policy_check(cfx_policy* p, void* stream) {
 
 extern "C" int cfx_selftest_wait_timeout(int device, unsigned limit_ms) {
     CFX_REQUIRE(limit_ms >= 1 && limit_ms <= 1000, "cfx_selftest_wait_timeout: limit_ms=%u out of [1,1000]", limit_ms);
-    DeviceGuard g(device);
+    CFX_GUARD(device);
     unsigned status = 0;
     int rc = fused_selftest_wait_timeout(limit_ms, &status);
     if (rc) return rc;
@@ -521,7 +521,7 @@ extern "C" {
 int cfx_policy_forward_host(cfx_policy* p, const cfx_forward_io* h) {
     CFX_REQUIRE(p && h, "cfx_policy_forward_host: NULL argument");
     CFX_REQUIRE(h->records && h->actions, "cfx_policy_forward_host: records/actions is NULL");
-    DeviceGuard g(p->device);
+    CFX_GUARD(p->device);
     cudaStream_t st = p->stream;
     const size_t n = (size_t)p->n;
     // r_state staging in floats: bf16 records take half
@@ -620,7 +620,9 @@ int cfx_policy_forward_host(cfx_policy* p, const cfx_forward_io* h) {
 // ------------------------------------------------------------------ stand-alone stages
 int cfx_expand_obs(int device, const uint8_t* records, float* features, int n, void* stream) {
     CFX_REQUIRE(records && features && n > 0, "cfx_expand_obs: bad argument");
-    DeviceGuard g(device);
+    // the 51 tail floats of a record are read as 32-bit words
+    CFX_REQUIRE(((uintptr_t)records & 3) == 0, "cfx_expand_obs: records not 4-byte aligned");
+    CFX_GUARD(device);
     return launch_expand(records, features, n, (cudaStream_t)stream);
 }
 
@@ -630,7 +632,7 @@ int cfx_sample_actions(int device, const float* logits, int ld, int num_actions,
     CFX_REQUIRE(logits && uniforms && actions && logprobs && n > 0, "cfx_sample_actions: bad argument");
     CFX_REQUIRE(num_actions >= 2 && num_actions <= kMaxActions && ld >= num_actions,
                 "cfx_sample_actions: num_actions=%d ld=%d", num_actions, ld);
-    DeviceGuard g(device);
+    CFX_GUARD(device);
     return launch_sample(logits, ld, num_actions, uniforms, 0, 0, nullptr, n, nullptr, actions,
                          logprobs, nullptr, (cudaStream_t)stream);
 }
@@ -638,7 +640,7 @@ int cfx_sample_actions(int device, const float* logits, int ld, int num_actions,
 int cfx_philox_uniforms(int device, uint64_t seed, uint64_t env_offset, uint64_t step, int n,
                         float* uniforms, void* stream) {
     CFX_REQUIRE(uniforms && n > 0, "cfx_philox_uniforms: bad argument");
-    DeviceGuard g(device);
+    CFX_GUARD(device);
     return launch_uniforms(seed, env_offset, step, n, uniforms, (cudaStream_t)stream);
 }
 
@@ -665,13 +667,13 @@ int cfx_device_name(int device, char* buf, size_t len, int* sm_count, int* cc_ma
 
 int cfx_device_alloc(int device, void** ptr, size_t bytes) {
     CFX_REQUIRE(ptr, "cfx_device_alloc: NULL");
-    DeviceGuard g(device);
+    CFX_GUARD(device);
     CFX_CUDA(cudaMalloc(ptr, bytes ? bytes : 1));
     return CFX_OK;
 }
 
 int cfx_device_free(int device, void* ptr) {
-    DeviceGuard g(device);
+    CFX_GUARD(device);
     CFX_CUDA(cudaFree(ptr));
     return CFX_OK;
 }
@@ -688,25 +690,25 @@ int cfx_host_free_pinned(void* ptr) {
 }
 
 int cfx_memcpy_h2d(int device, void* dst, const void* src, size_t bytes, void* stream) {
-    DeviceGuard g(device);
+    CFX_GUARD(device);
     CFX_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
     return CFX_OK;
 }
 
 int cfx_memcpy_d2h(int device, void* dst, const void* src, size_t bytes, void* stream) {
-    DeviceGuard g(device);
+    CFX_GUARD(device);
     CFX_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     return CFX_OK;
 }
 
 int cfx_memset(int device, void* dst, int value, size_t bytes, void* stream) {
-    DeviceGuard g(device);
+    CFX_GUARD(device);
     CFX_CUDA(cudaMemsetAsync(dst, value, bytes, (cudaStream_t)stream));
     return CFX_OK;
 }
 
 int cfx_stream_sync(int device, void* stream) {
-    DeviceGuard g(device);
+    CFX_GUARD(device);
     CFX_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     return CFX_OK;
 }
@@ -718,7 +720,7 @@ struct cfx_timer {
 
 int cfx_timer_create(int device, void** timer) {
     CFX_REQUIRE(timer, "cfx_timer_create: NULL");
-    DeviceGuard g(device);
+    CFX_GUARD(device);
     cfx_timer* t = new (std::nothrow) cfx_timer();
     CFX_REQUIRE(t, "cfx_timer_create: out of host memory");
     t->device = device;
@@ -741,7 +743,7 @@ int cfx_timer_destroy(void* timer) {
 int cfx_timer_start(void* timer, void* stream) {
     cfx_timer* t = (cfx_timer*)timer;
     CFX_REQUIRE(t, "cfx_timer_start: NULL");
-    DeviceGuard g(t->device);
+    CFX_GUARD(t->device);
     CFX_CUDA(cudaEventRecord(t->a, (cudaStream_t)stream));
     return CFX_OK;
 }
@@ -749,7 +751,7 @@ int cfx_timer_start(void* timer, void* stream) {
 int cfx_timer_stop(void* timer, void* stream) {
     cfx_timer* t = (cfx_timer*)timer;
     CFX_REQUIRE(t, "cfx_timer_stop: NULL");
-    DeviceGuard g(t->device);
+    CFX_GUARD(t->device);
     CFX_CUDA(cudaEventRecord(t->b, (cudaStream_t)stream));
     return CFX_OK;
 }
@@ -757,7 +759,7 @@ int cfx_timer_stop(void* timer, void* stream) {
 int cfx_timer_elapsed_ms(void* timer, float* ms) {
     cfx_timer* t = (cfx_timer*)timer;
     CFX_REQUIRE(t && ms, "cfx_timer_elapsed_ms: NULL");
-    DeviceGuard g(t->device);
+    CFX_GUARD(t->device);
     CFX_CUDA(cudaEventSynchronize(t->b));
     CFX_CUDA(cudaEventElapsedTime(ms, t->a, t->b));
     return CFX_OK;
@@ -770,7 +772,7 @@ int cfx_timer_elapsed_ms(void* timer, float* ms) {
 extern "C" int cfx_debug_timeline(cfx::FusedPlan* p, long long* host_out, int arm);
 extern "C" int cfx_policy_debug_timeline(cfx_policy* p, long long* host_out, int arm) {
     if (!p || !p->fused) return CFX_ERR_INVALID;
-    DeviceGuard g(p->device);
+    CFX_GUARD(p->device);
     cudaStreamSynchronize(p->stream);
     return cfx_debug_timeline(p->fused, host_out, arm);
 }

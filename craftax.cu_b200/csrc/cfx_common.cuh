@@ -53,7 +53,8 @@ int cuda_fail(cudaError_t e, const char* what, const char* file, int line);
         }                                      \
     } while (0)
 
-// Scoped cudaSetDevice.
+// Scoped cudaSetDevice.  Entry points use CFX_GUARD, which returns an error when the device
+// cannot be selected instead of carrying on with whatever device is current.
 struct DeviceGuard {
     int prev = -1;
     bool ok = true;
@@ -65,5 +66,15 @@ struct DeviceGuard {
         if (prev >= 0) cudaSetDevice(prev);
     }
 };
+
+#define CFX_GUARD(dev)                                                                   \
+    ::cfx::DeviceGuard _cfx_guard(dev);                                                  \
+    do {                                                                                 \
+        if (!_cfx_guard.ok) {                                                            \
+            cudaGetLastError();                                                          \
+            ::cfx::set_error("%s: cannot select CUDA device %d", __func__, (int)(dev));  \
+            return CFX_ERR_CUDA;                                                         \
+        }                                                                                \
+    } while (0)
 
 }  // namespace cfx

@@ -9,6 +9,8 @@
 // on-device yardstick for the tensor-core kernel at sizes a CPU cannot check.
 #include <cuda_bf16.h>
 
+#include <atomic>
+
 #include "cfx_common.cuh"
 #include "cfx_sampler.cuh"
 #include "cfx_strict.h"
@@ -396,8 +398,12 @@ constexpr size_t kStaticFloats = kStaticGates + 2 * kStaticLayerBuf + kStaticLog
 static __device__ __align__(256) float g_static_scratch[kStaticFloats];
 
 // Device address of the array per device ordinal; in host code the symbol's name is only a
-// handle for cudaGetSymbolAddress, never a pointer a kernel could use.
-static float* g_static_scratch_addr[64] = {nullptr};
+// handle for cudaGetSymbolAddress, never a pointer a kernel could use.  The cache is filled
+// once per device (atomic: two host threads may make their first calls together and resolve
+// the same address).  It is not invalidated: after cudaDeviceReset the library must be
+// reloaded before this entry point is used again.
+constexpr int kStaticMaxDevices = 64;
+static std::atomic<float*> g_static_scratch_addr[kStaticMaxDevices];
 }  // namespace cfx
 
 extern "C" int cfx_strict_forward_static(int device, const float* params, int hidden, int layers,
@@ -407,7 +413,13 @@ extern "C" int cfx_strict_forward_static(int device, const float* params, int hi
     using namespace cfx;
     CFX_REQUIRE(params && state && io, "cfx_strict_forward_static: NULL argument");
     CFX_REQUIRE(io->records && io->actions, "cfx_strict_forward_static: records/actions is NULL");
-    CFX_REQUIRE(device >= 0 && device < 64, "cfx_strict_forward_static: device %d out of [0,64)", device);
+    // same rule as cfx_policy_forward; the encoder reads the tail floats of a record as words
+    CFX_REQUIRE(((uintptr_t)io->records & 15) == 0,
+                "cfx_strict_forward_static: records not 16-byte aligned");
+    int ndev = 0;
+    CFX_CUDA(cudaGetDeviceCount(&ndev));
+    CFX_REQUIRE(device >= 0 && device < ndev && device < kStaticMaxDevices,
+                "cfx_strict_forward_static: device %d of %d", device, ndev);
     CFX_REQUIRE(hidden == kStaticHidden,
                 "cfx_strict_forward_static: hidden=%d, the fixed scratch is sized for %d", hidden,
                 kStaticHidden);
@@ -419,16 +431,22 @@ extern "C" int cfx_strict_forward_static(int device, const float* params, int hi
     CFX_REQUIRE(num_envs > 0 && num_envs % 32 == 0 && num_envs <= kStaticMaxEnvs,
                 "cfx_strict_forward_static: num_envs=%d must be a multiple of 32 and at most %d "
                 "(size of the fixed scratch)", num_envs, kStaticMaxEnvs);
-    DeviceGuard g(device);
-    if (g_static_scratch_addr[device] == nullptr) {
-        // one-time set-up for this device, with it current: resolve the array's device address
+    CFX_GUARD(device);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (g_static_scratch_addr[device].load(std::memory_order_acquire) == nullptr) {
+        // one-time set-up for this device, with it current: resolve the array's device address.
+        // It must not happen while the stream is being captured.
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) cudaGetLastError();
+        CFX_REQUIRE(cap == cudaStreamCaptureStatusNone,
+                    "cfx_strict_forward_static: the first call on a device does its set-up and "
+                    "must come before any stream capture");
         float* addr = nullptr;
         CFX_CUDA(cudaGetSymbolAddress((void**)&addr, g_static_scratch));
         CFX_REQUIRE(addr != nullptr, "cfx_strict_forward_static: no device address for the scratch");
-        g_static_scratch_addr[device] = addr;
+        g_static_scratch_addr[device].store(addr, std::memory_order_release);
     }
-    float* base = g_static_scratch_addr[device];
-    cudaStream_t st = (cudaStream_t)stream;
+    float* base = g_static_scratch_addr[device].load(std::memory_order_acquire);
     const ArenaLayout o = ArenaLayout::make(hidden, layers, num_actions);
     int rc = launch_transpose_gates(params + o.w_gru, base, hidden, layers, st);
     if (rc) return rc;

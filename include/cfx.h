@@ -52,9 +52,14 @@ typedef enum cfx_precision {
     CFX_PREC_F16 = 1,  /* fused tcgen05 kernel, fp16 operands (11-bit significand,
                           the same as tf32, at the bf16 rate)                    */
     CFX_PREC_BF16 = 2, /* fused tcgen05 kernel, bf16 operands (the reference's
-                          CF_GEMM_BF16 mode, craftax_full.cu:11309)              */
-    CFX_PREC_TF32 = 3  /* fused tcgen05 kernel, tf32 operands (the reference's
-                          cublasSgemm TF32 mode, craftax_full.cu:11297)          */
+                          CF_GEMM_BF16 mode, craftax_full.cu:11309).  A throughput
+                          point only: its 8-bit significand misses the accuracy
+                          gates the fp16 mode meets (greedy-action agreement with
+                          the fp32 path about 99.2 % against 99.5 % required)    */
+    CFX_PREC_TF32 = 3  /* reserved (the reference's cublasSgemm TF32 mode,
+                          craftax_full.cu:11297): not built, create and
+                          set_precision return CFX_ERR_UNSUPPORTED; fp16 operands
+                          carry the same 11-bit significand                      */
 } cfx_precision;
 
 typedef struct cfx_policy cfx_policy;
@@ -195,10 +200,13 @@ int cfx_policy_forward_host(cfx_policy* p, const cfx_forward_io* host_io);
  * two layer buffers, logits) lives in one fixed 5.5 MB device array inside the library,
  * resident on every GPU that loads it: hidden must be 256, layers <= 4, num_actions <= 63,
  * num_envs <= 1024 and a multiple of 32; larger sizes are rejected with CFX_ERR_INVALID.
- * The first call on a device looks the array's address up (cudaGetSymbolAddress) and should
- * therefore come before any stream capture.  No call allocates or frees.  All calls share the
- * array: calls that overlap on the GPU race on it.  Results equal cfx_policy_forward with
- * CFX_PREC_FP32 bit for bit. */
+ * io->records must be 16-byte aligned, as for cfx_policy_forward.
+ * The first call on a device looks the array's address up (cudaGetSymbolAddress) and must
+ * therefore come before any stream capture (a first call on a capturing stream is rejected).
+ * The address is kept for the life of the process: after cudaDeviceReset the library has to be
+ * reloaded.  No call allocates or frees.  All calls share the array: calls that overlap on
+ * the GPU race on it.  Results equal cfx_policy_forward with CFX_PREC_FP32 bit for bit (the
+ * same kernels in the same order). */
 int cfx_strict_forward_static(int device, const float* params, int hidden, int layers,
                               int num_actions, int num_envs, float* state,
                               const cfx_forward_io* io, const uint64_t* step_ctr, void* stream);

@@ -248,6 +248,9 @@ class RefCuda:
         L.refcu_destroy.argtypes = [C.c_void_p]
         L.refcu_set_weights.argtypes = [C.c_void_p, C.c_void_p]
         L.refcu_get_weights.argtypes = [C.c_void_p, C.c_void_p]
+        if hasattr(L, "refcu_save_cfw1"):
+            L.refcu_save_cfw1.argtypes = [C.c_void_p, C.c_char_p]
+            L.refcu_load_cfw1.argtypes = [C.c_void_p, C.c_char_p]
         L.refcu_set_state.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
         L.refcu_get_state.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
         L.refcu_set_step.argtypes = [C.c_void_p, C.c_ulonglong]
@@ -273,6 +276,14 @@ class RefCuda:
         p = np.empty(self.L.refcu_param_count(), np.float32)
         self.L.refcu_get_weights(self.h, _p(p))
         return p
+
+    def save_cfw1(self, path):
+        """The reference's cu_save_weights on its current arena."""
+        self.L.refcu_save_cfw1(self.h, os.fsencode(path))
+
+    def load_cfw1(self, path):
+        """The reference's cu_load_weights; returns its status (0 = loaded)."""
+        return int(self.L.refcu_load_cfw1(self.h, os.fsencode(path)))
 
     def set_state(self, mode, state):
         s = np.ascontiguousarray(state, np.float32)

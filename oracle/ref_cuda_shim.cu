@@ -101,6 +101,21 @@ void refcu_get_weights(void* h, float* host_arena) {
                         cudaMemcpyDeviceToHost));
 }
 
+/* The reference's own checkpoint writer and reader (cu_save_weights / cu_load_weights,
+ * :12248-12293) on the fp32-only policy; the loaded arena is mirrored into the bf16 policy. */
+void refcu_save_cfw1(void* h, const char* path) {
+    refcu* r = (refcu*)h;
+    cu_save_weights(&r->pol[1], path);
+}
+
+int refcu_load_cfw1(void* h, const char* path) {
+    refcu* r = (refcu*)h;
+    g_gemm_bf16 = 0;
+    if (cu_load_weights(&r->pol[1], path) != 0) return 1;
+    g_gemm_bf16 = 1;
+    return cu_load_weights(&r->pol[0], path);
+}
+
 /* Live state of the batched path, [L][n][H] (same layout as ours). */
 void refcu_set_state(void* h, int mode, const float* host_state) {
     refcu* r = (refcu*)h;

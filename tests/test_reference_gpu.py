@@ -132,3 +132,59 @@ def test_reference_run_loop_with_the_forward_swapped_in(cfx, oracle, refcu):
         assert np.isfinite(sps) and sps > 0
         print(f"rollout 4096 envs: reference {ref_sps / 1e6:.1f} M SPS, swapped (precision {prec}) {sps / 1e6:.1f} M SPS")
     assert ref_sps > 0
+
+
+@pytest.mark.parametrize("L", [2, 3])
+def test_init_weights_equals_the_reference_initialiser(cfx, oracle, refcu, L):
+    """cfx_policy_init_weights(1234) against the arena cu_policy_init writes
+    (craftax_full.cu:11830-11845: Philox U(+-1/sqrt(fan_in)), seed 1234, one subsequence per
+    segment), bit for bit."""
+    if not refcu.available(L):
+        pytest.skip(f"oracle/_ref/libcfref_cuda_l{L}.so not built")
+    ref = refcu(32, L)
+    want = ref.get_weights()          # untouched since cu_policy_init
+    ref.close()
+    pol = cfx.Policy(32, H, L, A, "fp32")
+    pol.init_weights(1234)
+    got = pol.get_weights()
+    pol.close()
+    assert got.size == want.size == cfx.lib().cfx_param_count(H, L, A)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert np.abs(want).max() > 0
+
+
+@pytest.mark.parametrize("L", [2, 3])
+def test_cfw1_files_cross_load_with_the_reference(cfx, oracle, refcu, L, tmp_path):
+    """CFW1 checkpoints in both directions: a file written by the reference's cu_save_weights
+    (craftax_full.cu:12248-12263) loads with cfx_policy_load_cfw1, and a file written by
+    cfx_policy_save_cfw1 loads with cu_load_weights (:12264-12293); arenas and file bytes equal."""
+    if not refcu.available(L):
+        pytest.skip(f"oracle/_ref/libcfref_cuda_l{L}.so not built")
+    ref = refcu(32, L)
+    if not hasattr(ref.L, "refcu_save_cfw1"):
+        pytest.skip("reference shim built without the checkpoint wrappers")
+    params = oracle.init_weights(H, L, A, seed=31, scheme="uniform")
+    # reference -> library
+    ref.set_weights(params)
+    f_ref = str(tmp_path / "from_reference.cfw1")
+    ref.save_cfw1(f_ref)
+    pol = cfx.Policy(32, H, L, A, "fp32")
+    pol.load(f_ref)
+    assert np.array_equal(pol.get_weights().view(np.uint32), params.view(np.uint32))
+    # library -> reference
+    params2 = oracle.init_weights(H, L, A, seed=32)
+    pol.set_weights(params2)
+    f_cfx = str(tmp_path / "from_library.cfw1")
+    pol.save(f_cfx)
+    assert ref.load_cfw1(f_cfx) == 0
+    assert np.array_equal(ref.get_weights().view(np.uint32), params2.view(np.uint32))
+    # same bytes for the same arena, whoever writes
+    ref.save_cfw1(f_ref)
+    assert open(f_ref, "rb").read() == open(f_cfx, "rb").read()
+    # a file of another depth is refused by both sides
+    other = cfx.Policy(32, H, 5 - L, A, "fp32")
+    with pytest.raises(cfx.CfxError):
+        other.load(f_cfx)
+    other.close()
+    pol.close()
+    ref.close()
