@@ -11,6 +11,12 @@ on the launching stream with inputs resident in HBM; `e2e` goes through
 cfx_policy_forward_host with pinned host buffers (copies inside the timed region).
 Under torchrun each rank drives its own GPU and its own contiguous slice of envs;
 there is no data-path collective, only a barrier and a max over ranks of the timings.
+The K-step region is timed several times (`timed_repetitions`, each bracketed by a barrier
+and a synchronize, max over ranks per repetition) and the median repetition is reported, so
+that a few milliseconds of work are not judged on one sample.  At N = 1 the line also
+carries the reference's own cuBLAS forward on the same GPU and inputs (`reference_cublas`,
+from the library built out of the reference sources when it is present) and the CPU arm
+(`cpu_baseline`).
 """
 import argparse
 import json
@@ -119,7 +125,10 @@ def run_cfx(args):
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = local
-    n, H, L = args.envs, args.hidden, args.layers
+    from cfx.sharding import aggregate_throughput, env_slice, max_over_ranks
+    # weak scaling: the job is world x --envs envs, this rank owns a contiguous slice of it
+    env_begin, env_end = env_slice(rank, world, world * args.envs)
+    n, H, L = env_end - env_begin, args.hidden, args.layers
     prec = args.precision
     rng = np.random.default_rng(4 + rank)
     from cfx.synth import synthetic_records, init_weights
@@ -144,7 +153,7 @@ def run_cfx(args):
 
     def step():
         pol.forward_device(d_rec, d_pt, None, env_actions=d_env, actions=d_act, logprobs=d_lp,
-                           values=d_val, logits_av=d_lav, seed=2, env_offset=rank * n,
+                           values=d_val, logits_av=d_lav, seed=2, env_offset=env_begin,
                            bump_step=True, stream=stream)
 
     def barrier():
@@ -160,19 +169,34 @@ def run_cfx(args):
     pol.sync()
     launches_per_step = pol.last_launches
     sampler.start()
-    timers = [cfx.Timer(dev) for _ in range(args.steps)]
-    barrier()
-    t_all = cfx.Timer(dev)
-    t_all.start(stream)
-    for t in timers:
-        t.start(stream)
-        step()
-        t.stop(stream)
-    t_all.stop(stream)
-    barrier()
+    # The K-step region, repeated: one repetition of K = 20 steps is ~8 ms, too short for a
+    # max over ranks; repetitions fill about `--min-timed-ms` of device time.
+    t_probe = cfx.Timer(dev)
+    t_probe.start(stream)
+    step()
+    t_probe.stop(stream)
+    pol.sync()
+    reps = int(np.clip(np.ceil(args.min_timed_ms / max(1e-3, t_probe.elapsed_ms() * args.steps)), 1, 50))
+    if dist is not None:   # every rank must run the same number of repetitions
+        import torch
+        r = torch.tensor([reps], device="cuda")
+        dist.all_reduce(r, op=dist.ReduceOp.MAX)
+        reps = int(r.item())
+    rep_ms, per_step = [], []
+    for _ in range(reps):
+        timers = [cfx.Timer(dev) for _ in range(args.steps)]
+        barrier()
+        t_all = cfx.Timer(dev)
+        t_all.start(stream)
+        for t in timers:
+            t.start(stream)
+            step()
+            t.stop(stream)
+        t_all.stop(stream)
+        barrier()
+        rep_ms.append(t_all.elapsed_ms())
+        per_step.extend(t.elapsed_ms() for t in timers)
     pol.check()
-    total_ms = t_all.elapsed_ms()
-    per_step = [t.elapsed_ms() for t in timers]
 
     # end to end through the host-buffer entry point, pinned buffers
     pin_rec = cfx.PinnedBuffer((n, 996), np.uint8)
@@ -185,30 +209,48 @@ def run_cfx(args):
     out_arrays = {k: v.array for k, v in outs.items()}
     e2e_steps = max(2, min(args.steps, 10))
     for _ in range(2):
-        pol.forward_host(pin_rec.array, pin_pt.array, None, seed=2, env_offset=rank * n,
+        pol.forward_host(pin_rec.array, pin_pt.array, None, seed=2, env_offset=env_begin,
                          bump_step=True, want_logits=False, out=out_arrays)
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        pol.forward_host(pin_rec.array, pin_pt.array, None, seed=2, env_offset=rank * n,
+        pol.forward_host(pin_rec.array, pin_pt.array, None, seed=2, env_offset=env_begin,
                          bump_step=True, want_logits=False, out=out_arrays)
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    clocks = sampler.stop()   # sampled over both timed regions (device-resident and end to end)
+    # where an end-to-end step goes: the same copies alone (CUDA events, all ranks at once)
+    lib = cfx.lib()
     h2d = n * 996 + n * 4
     d2h = 4 * n * 4
+    tc = cfx.Timer(dev)
+    barrier()
+    tc.start(stream)
+    for _ in range(e2e_steps):
+        cfx.check(lib.cfx_memcpy_h2d(dev, d_rec.ptr, pin_rec.ptr, n * 996, stream))
+        cfx.check(lib.cfx_memcpy_h2d(dev, d_pt.ptr, pin_pt.ptr, n * 4, stream))
+    tc.stop(stream)
+    pol.sync()
+    upload_ms = tc.elapsed_ms() / e2e_steps
+    barrier()
+    tc.start(stream)
+    for _ in range(e2e_steps):
+        for k, b in (("env_actions", d_env), ("actions", d_act), ("logprobs", d_lp), ("values", d_val)):
+            cfx.check(lib.cfx_memcpy_d2h(dev, outs[k].ptr, b.ptr, n * 4, stream))
+    tc.stop(stream)
+    pol.sync()
+    readback_ms = tc.elapsed_ms() / e2e_steps
+    clocks = sampler.stop()   # sampled over both timed regions (device-resident and end to end)
 
-    if dist is not None:
-        import torch
-        v = torch.tensor([total_ms, e2e_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(v, op=dist.ReduceOp.MAX)
-        total_ms, e2e_ms = v.tolist()
+    v = max_over_ranks(list(rep_ms) + [e2e_ms, upload_ms, readback_ms], dist)
+    rep_ms, (e2e_ms, upload_ms, readback_ms) = np.array(v[:reps]), v[reps:]
+    total_ms = float(np.median(rep_ms))
+    # whole job: env-steps of all ranks over the slowest rank's time
+    value, _ = aggregate_throughput(total_ms, n * args.steps, dist)
     ms_per_step = total_ms / args.steps
-    value = world * n / (ms_per_step * 1e-3)
     flops, byts = algorithmic_work(H, L)
     peaks = load_peaks()
     kernel_ms = float(np.mean(per_step))
-    tensor_peak = peaks["bf16_tflops"] * (0.5 if prec == "tf32" else 1.0)
+    tensor_peak = peaks["bf16_tflops"]
     t_hbm = n * byts / (peaks["hbm_gbs"] * 1e9)
     t_tensor = n * flops / (tensor_peak * 1e12)
     if prec == "fp32" or t_hbm >= t_tensor:
@@ -231,8 +273,7 @@ def run_cfx(args):
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None,
         "dtype": {"fp32": "f32", "f16": "f16 operands, f32 accumulate",
-                  "bf16": "bf16 operands, f32 accumulate",
-                  "tf32": "tf32 operands, f32 accumulate"}[prec],
+                  "bf16": "bf16 operands, f32 accumulate"}[prec],
         "data": "synthetic",
         "config": {"workload": f"policy forward, {n} envs/GPU, h{H}x{L}, {A} actions, 996-B records",
                    "envs_per_gpu": n, "hidden": H, "layers": L, "precision": prec,
@@ -241,16 +282,54 @@ def run_cfx(args):
                          % ((n * 996 + L * n * H * 4) / 1e6)},
         "roofline": roof,
         "e2e": {"value": world * n / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
-        "gpu_launches": launches_per_step * args.steps,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                # the step's copies timed alone (max over ranks, all ranks copying at once) and
+                # what is left for the kernel that the sliced upload does not hide
+                "upload_ms": upload_ms, "readback_ms": readback_ms,
+                "exposed_kernel_ms": max(0.0, e2e_ms - upload_ms - readback_ms),
+                "h2d_gbs_per_gpu": h2d / (upload_ms * 1e-3) / 1e9,
+                "bound": "host-to-device link"},
+        "gpu_launches": launches_per_step * args.steps * reps,
+        "timed_repetitions": reps,
+        "ms_per_step_repetitions": [float(x) / args.steps for x in rep_ms],
         "clocks": clocks,
     }
+    if rank == 0 and world == 1 and not args.no_reference_cublas:
+        line["reference_cublas"] = reference_cublas_forward(args, d_rec, d_pt, kernel_ms)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_forward_rate(H, L, budget_s=args.cpu_budget)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+
+
+def reference_cublas_forward(args, d_rec, d_pt, kernel_ms):
+    """The reference's own forward (k_expand_obs ... k_value_sample + k_bump_ctr with its cuBLAS
+    GEMMs, CUDA-graph replay as in its `run` mode, craftax_full.cu:12142-12160) on the SAME
+    device buffers, in this process, right after the product arm: its bf16 mode (its default on
+    this GPU, :11325-11332) and its TF32 mode.  Needs the library built from the reference
+    sources (oracle/_ref/); reported as unavailable where that is absent."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    try:
+        import oracle as O
+        L = args.layers
+        if args.hidden != 256 or not O.RefCuda.available(L):
+            return {"unavailable": f"oracle/_ref/libcfref_cuda_l{L}.so not built (reference sources absent)"}
+        from cfx.synth import init_weights
+        ref = O.RefCuda(args.envs, L)
+        ref.set_weights(init_weights(256, L, A, seed=0))
+        steps = max(10, min(args.steps, 50))
+        out = {"steps": steps, "what": "reference kernels + cuBLAS, graph replay, same records and "
+                                       "prev_terminals buffers, same process"}
+        for name, mode in (("bf16", ref.BF16), ("tf32", ref.TF32)):
+            ms = ref.time_forward(mode, d_rec.ptr, d_pt.ptr, warm=3, iters=steps, graph=1)
+            out[f"{name}_ms"] = ms
+            out[f"ratio_{name}"] = ms / kernel_ms
+        ref.close()
+        return out
+    except Exception as e:   # a comparison arm must not take the product line down
+        return {"unavailable": f"{type(e).__name__}: {e}"}
 
 
 def cpu_forward_rate(H, L, budget_s=15.0, steps=1, warmup=0, threads=0):
@@ -315,8 +394,11 @@ def run_reference(args):
         "ms_per_step": b["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"policy forward, {args.envs} envs/GPU, h{H}x{L}, {A} actions, 996-B records",
-                   "envs_per_gpu": args.envs, "hidden": H, "layers": L,
-                   "note": "CPU arm: bounded sample of the workload per step on the host cores"},
+                   "envs_per_gpu": args.envs, "hidden": H, "layers": L, "precision": "fp32",
+                   "sharding": "rank 0 only, host cores",
+                   "l2": "not applicable (CPU arm)",
+                   "sample_envs": b["envs_per_step"],
+                   "note": "CPU arm: every step is a bounded sample (sample_envs) of the workload"},
         "cpu_baseline": {k: b[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": b["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -515,8 +597,11 @@ def main():
     ap.add_argument("--envs", type=int, default=262144, help="envs per GPU")
     ap.add_argument("--hidden", type=int, default=256)
     ap.add_argument("--layers", type=int, default=2)
-    ap.add_argument("--precision", default=None, choices=["fp32", "f16", "bf16", "tf32"])
+    ap.add_argument("--precision", default=None, choices=["fp32", "f16", "bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-cublas", action="store_true")
+    ap.add_argument("--min-timed-ms", type=float, default=100.0,
+                    help="device time to fill with repetitions of the K-step region")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "cfx" else args.warmup

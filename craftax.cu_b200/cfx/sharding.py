@@ -18,15 +18,30 @@ def env_slice(rank, world, n_total, align=32):
     return start_u * align, (start_u + size_u) * align
 
 
+def _single(dist):
+    return dist is None or not dist.is_initialized() or dist.get_world_size() == 1
+
+
+def max_over_ranks(values, dist=None):
+    """Element-wise maximum over ranks of a list of timings (the slowest rank sets the job
+    time).  `dist` is an initialised torch.distributed module or None for a single process."""
+    vals = [float(v) for v in values]
+    if _single(dist) or not vals:
+        return vals
+    import torch
+    dev = "cuda" if dist.get_backend() == "nccl" else "cpu"
+    t = torch.tensor(vals, dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
 def aggregate_throughput(local_ms, local_env_steps, dist=None):
-    """Whole-job env-steps/s = env-steps of all ranks / max over ranks of the elapsed time.
-    `dist` is an initialised torch.distributed module or None for a single process."""
-    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+    """Whole-job env-steps/s = env-steps of all ranks / max over ranks of the elapsed time."""
+    if _single(dist):
         return local_env_steps / (local_ms * 1e-3), local_ms
     import torch
     dev = "cuda" if dist.get_backend() == "nccl" else "cpu"
-    t = torch.tensor([local_ms], dtype=torch.float64, device=dev)
     s = torch.tensor([float(local_env_steps)], dtype=torch.float64, device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dist.all_reduce(s, op=dist.ReduceOp.SUM)
-    return s.item() / (t.item() * 1e-3), t.item()
+    t = max_over_ranks([local_ms], dist)[0]
+    return s.item() / (t * 1e-3), t

@@ -218,6 +218,25 @@ class RefClassic:
         return float(self.L.refcl_time_forward(d_params_ptr, d_rec_ptr, d_prev_done_ptr, d_state_ptr, n,
                                                warm, iters, tf32))
 
+    LOCKSTEP_KEYS = ("max_dlogit", "max_dvalue", "greedy_agreement", "sampled_agreement",
+                     "episode_ends", "max_logit", "env_steps")
+
+    def lockstep(self, n, steps, seed, params, precision, tf32=0):
+        """Classic rollout on the GPU: the reference's classic env kernels driven by libcfx's
+        classic forward (CFX_PREC_* code `precision`), the reference's classic pipeline on the
+        same records beside it; returns the device-side comparison figures."""
+        if not hasattr(self.L, "refcl_lockstep"):
+            raise RuntimeError("reference classic shim built without the lock-step loop")
+        self.L.refcl_lockstep.argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_void_p, C.c_int, C.c_int,
+                                          C.c_void_p]
+        p = np.ascontiguousarray(params, np.float32)
+        assert p.size == self.param_count
+        out = np.zeros(8, np.float64)
+        rc = self.L.refcl_lockstep(n, steps, seed, _p(p), precision, tf32, _p(out))
+        if rc != 0:
+            raise RuntimeError("refcl_lockstep: a cfx call failed (see stderr)")
+        return dict(zip(self.LOCKSTEP_KEYS, out.tolist()))
+
     def forward(self, d_params_ptr, d_rec_ptr, d_prev_done_ptr, d_state_ptr, n, seed, step):
         o = {"logits_av": np.empty((n, self.A + 1), np.float32), "h_enc": np.empty((n, self.H), np.float32),
              "actions": np.empty(n, np.int32), "logprobs": np.empty(n, np.float32)}
@@ -266,6 +285,27 @@ class RefCuda:
         assert L.refcu_layers() == layers and L.refcu_hidden() == 256
         self.L, self.n, self.layers, self.H = L, n, layers, 256
         self.h = L.refcu_create(n)
+
+    LOCKSTEP_KEYS = ("max_dlogit", "max_dvalue", "greedy_agreement", "sampled_agreement",
+                     "episode_ends", "max_logit", "env_steps")
+
+    @classmethod
+    def lockstep(cls, layers, n, steps, seed, params, precision, sync_state=0):
+        """Full-game rollout on the GPU: the reference's CUDA env (records written on the device
+        by its k_record_obs) driven by libcfx's forward (CFX_PREC_* code `precision`), the
+        reference's strict-fp32 cuBLAS pipeline on the same records beside it; returns the
+        device-side comparison figures.  libcfx.so must be loaded first (the shim links it)."""
+        L = C.CDLL(cls.path(layers))
+        if not hasattr(L, "refcu_lockstep"):
+            raise RuntimeError("reference shim built without the lock-step loop")
+        L.refcu_lockstep.argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        p = np.ascontiguousarray(params, np.float32)
+        assert p.size == L.refcu_param_count() and L.refcu_layers() == layers
+        out = np.zeros(8, np.float64)
+        rc = L.refcu_lockstep(n, steps, seed, _p(p), precision, sync_state, _p(out))
+        if rc != 0:
+            raise RuntimeError("refcu_lockstep: a cfx call failed (see stderr)")
+        return dict(zip(cls.LOCKSTEP_KEYS, out.tolist()))
 
     def set_weights(self, params):
         p = np.ascontiguousarray(params, np.float32)

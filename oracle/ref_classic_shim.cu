@@ -12,6 +12,7 @@
  */
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <cublas_v2.h>
 #include CFX_REF_CLASSIC_CU
 
@@ -172,5 +173,189 @@ float refcl_time_forward(const float* d_params, const uint8_t* d_rec, const int8
     cublasDestroy(blas);
     return ms / (float)iters;
 }
+
+#ifdef CFX_REF_WITH_CFX
+#include "cfx.h"
+/* ---- lock-step classic rollout: the reference's classic env kernels (reset_all_warp_kernel
+ * :1443, record_obs_kernel :1884, step_mark_kernel :1401, reset_warp_ctr_kernel :1908,
+ * bump_ctr_kernel :1929, in the order of Rollout::step, main_classic.cu:439-474), driven by
+ * this library's classic forward, with the reference's record-driven classic pipeline
+ * (encode_obs_kernel, cublasSgemm + mingru_epi_fwd_kernel per layer, logits Sgemm,
+ * value_sample_kernel) consuming the same 148-byte records beside it.  Both keep their own
+ * recurrent state, zeroed from the previous step's dones and never at t = 0
+ * (main_classic.cu:436-443).  tf32 != 0 runs the reference products in the math mode its
+ * rollout uses (main_classic.cu:283) instead of strict fp32.  The comparison runs on the device
+ * every step.  out[0] max |dlogit|, out[1] max |dvalue|, out[2] fraction of env-steps with the
+ * same greedy action, out[3] with the same sampled action (same Philox draw), out[4] episode
+ * ends seen, out[5] max |logit|, out[6] env-steps compared.  Returns 0, or 1 when a cfx call
+ * failed (message on stderr). */
+__global__ void refcl_k_compare(const float* __restrict__ ref_logits, const float* __restrict__ b_a,
+                                const float* __restrict__ ref_val, const float* __restrict__ cfx_lav,
+                                const int32_t* __restrict__ ref_act, const int32_t* __restrict__ cfx_act,
+                                int n, unsigned* fmax, unsigned long long* counts) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n) return;
+    const float* r = ref_logits + (size_t)e * NUM_ACTIONS;
+    const float* c = cfx_lav + (size_t)e * (NUM_ACTIONS + 1);
+    float dmax = 0.f, lmax = 0.f, rbest = 0.f, cbest = 0.f;
+    int ra = 0, ca = 0;
+    for (int a = 0; a < NUM_ACTIONS; a++) {
+        const float rl = r[a] + b_a[a], cl = c[a];
+        dmax = fmaxf(dmax, fabsf(rl - cl));
+        lmax = fmaxf(lmax, fabsf(rl));
+        if (a == 0 || rl > rbest) { rbest = rl; ra = a; }
+        if (a == 0 || cl > cbest) { cbest = cl; ca = a; }
+    }
+    atomicMax(&fmax[0], __float_as_uint(dmax));   /* non-negative floats order like their bits */
+    atomicMax(&fmax[1], __float_as_uint(fabsf(ref_val[e] - c[NUM_ACTIONS])));
+    atomicMax(&fmax[2], __float_as_uint(lmax));
+    if (ra == ca) atomicAdd(&counts[0], 1ULL);
+    if (ref_act[e] == cfx_act[e]) atomicAdd(&counts[1], 1ULL);
+}
+
+__global__ void refcl_k_count_done(const int8_t* __restrict__ done, int n, unsigned long long* counts) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e < n && done[e]) atomicAdd(&counts[2], 1ULL);
+}
+
+int refcl_lockstep(int n, int steps, unsigned long long seed, const float* host_params, int precision,
+                   int tf32, double* out) {
+    cublasHandle_t blas;
+    RC_BLAS(cublasCreate(&blas));
+    RC_BLAS(cublasSetMathMode(blas, tf32 ? CUBLAS_TF32_TENSOR_OP_MATH : CUBLAS_DEFAULT_MATH));
+    cudaStream_t st;
+    RC_CHECK(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    RC_BLAS(cublasSetStream(blas, st));
+    uint8_t* arena;
+    RC_CHECK(cudaMalloc(&arena, soa_bytes(n)));
+    RC_CHECK(cudaMemset(arena, 0, soa_bytes(n)));
+    EnvSoA g = carve_soa(arena, n);
+    float* d_params;
+    RC_CHECK(cudaMalloc(&d_params, (size_t)PARAM_COUNT * sizeof(float)));
+    RC_CHECK(cudaMemcpy(d_params, host_params, (size_t)PARAM_COUNT * sizeof(float), cudaMemcpyHostToDevice));
+    const float* W_enc = d_params + PARAM_W_ENC;
+    const float* b_enc = d_params + PARAM_B_ENC;
+    const float* W_gru = d_params + PARAM_W_GRU;
+    const float* W_a = d_params + PARAM_W_A;
+    const float* b_a = d_params + PARAM_B_A;
+    const float* W_v = d_params + PARAM_W_V;
+    const float* b_v = d_params + PARAM_B_V;
+    const size_t hn = (size_t)HIDDEN * n;
+    float *h0, *h1, *pre, *logits, *ref_state, *ref_lp, *ref_val, *rewards, *term, *d_lav;
+    int32_t *ref_act, *cfx_act, *reset_list, *reset_ctrl;
+    int8_t* done[2];
+    uint8_t* rec;
+    uint64_t* step_ctr;
+    unsigned* d_fmax;
+    unsigned long long* d_counts;
+    RC_CHECK(cudaMalloc(&h0, hn * sizeof(float)));
+    RC_CHECK(cudaMalloc(&h1, hn * sizeof(float)));
+    RC_CHECK(cudaMalloc(&pre, (size_t)GRU_OUT * n * sizeof(float)));
+    RC_CHECK(cudaMalloc(&logits, (size_t)NUM_ACTIONS * n * sizeof(float)));
+    RC_CHECK(cudaMalloc(&ref_state, (size_t)GRU_LAYERS * hn * sizeof(float)));
+    RC_CHECK(cudaMemset(ref_state, 0, (size_t)GRU_LAYERS * hn * sizeof(float)));
+    RC_CHECK(cudaMalloc(&ref_lp, (size_t)n * sizeof(float)));
+    RC_CHECK(cudaMalloc(&ref_val, (size_t)n * sizeof(float)));
+    RC_CHECK(cudaMalloc(&rewards, (size_t)n * sizeof(float)));
+    RC_CHECK(cudaMalloc(&term, (size_t)n * sizeof(float)));
+    RC_CHECK(cudaMalloc(&d_lav, (size_t)n * (NUM_ACTIONS + 1) * sizeof(float)));
+    RC_CHECK(cudaMalloc(&ref_act, (size_t)n * sizeof(int32_t)));
+    RC_CHECK(cudaMalloc(&cfx_act, (size_t)n * sizeof(int32_t)));
+    RC_CHECK(cudaMalloc(&reset_list, (size_t)n * sizeof(int32_t)));
+    RC_CHECK(cudaMalloc(&reset_ctrl, 2 * sizeof(int32_t)));
+    RC_CHECK(cudaMalloc(&done[0], (size_t)n));
+    RC_CHECK(cudaMalloc(&done[1], (size_t)n));
+    RC_CHECK(cudaMalloc(&rec, (size_t)n * OBS_DIM_COMPACT));
+    RC_CHECK(cudaMalloc(&step_ctr, sizeof(uint64_t)));
+    RC_CHECK(cudaMemset(step_ctr, 0, sizeof(uint64_t)));
+    RC_CHECK(cudaMalloc(&d_fmax, 4 * sizeof(unsigned)));
+    RC_CHECK(cudaMalloc(&d_counts, 4 * sizeof(unsigned long long)));
+    RC_CHECK(cudaMemset(d_fmax, 0, 4 * sizeof(unsigned)));
+    RC_CHECK(cudaMemset(d_counts, 0, 4 * sizeof(unsigned long long)));
+    int dev = 0, rc = 0;
+    RC_CHECK(cudaGetDevice(&dev));
+    cfx_policy* cp = NULL;
+    if (cfx_policy_create_classic(&cp, dev, n, HIDDEN, GRU_LAYERS, NUM_ACTIONS, precision) != CFX_OK ||
+        cfx_policy_set_weights(cp, d_params, PARAM_COUNT, 1) != CFX_OK) {
+        fprintf(stderr, "cfx: %s\n", cfx_last_error());
+        rc = 1;
+    }
+    const int block = 256, grid = (n + block - 1) / block;
+    {
+        int wgrid = (int)(((size_t)n * 32 + RESET_WARP_BLOCK - 1) / RESET_WARP_BLOCK);
+        reset_all_warp_kernel<<<wgrid, RESET_WARP_BLOCK, 0, st>>>(g, n, seed);
+        RC_CHECK(cudaGetLastError());
+        RC_CHECK(cudaStreamSynchronize(st));
+    }
+    const float one = 1.0f, zero = 0.0f;
+    for (int t = 0; t < steps && rc == 0; t++) {
+        const int8_t* prev = (t == 0) ? NULL : done[(t - 1) & 1];
+        RC_CHECK(cudaMemsetAsync(reset_ctrl, 0, 8, st));
+        record_obs_kernel<<<grid, block, 0, st>>>(g, rec, n);
+        /* reference pipeline on the records */
+        encode_obs_kernel<<<(int)((hn + 255) / 256), 256, 0, st>>>(rec, W_enc, b_enc, h0, 0, n, n, n, 0);
+        float* x = h0;
+        float* y = h1;
+        for (int l = 0; l < GRU_LAYERS; l++) {
+            RC_BLAS(cublasSgemm(blas, CUBLAS_OP_T, CUBLAS_OP_N, GRU_OUT, n, HIDDEN, &one,
+                                W_gru + (size_t)l * GRU_OUT * HIDDEN, HIDDEN, x, HIDDEN, &zero, pre, GRU_OUT));
+            mingru_epi_fwd_kernel<<<(int)((hn + 255) / 256), 256, 0, st>>>(pre, x, ref_state + (size_t)l * hn, y,
+                                                                           NULL, prev, n);
+            float* tmp = x; x = y; y = tmp;
+        }
+        RC_BLAS(cublasSgemm(blas, CUBLAS_OP_T, CUBLAS_OP_N, NUM_ACTIONS, n, HIDDEN, &one, W_a, HIDDEN, x, HIDDEN,
+                            &zero, logits, NUM_ACTIONS));
+        value_sample_kernel<<<grid, block, 0, st>>>(x, logits, b_a, W_v, b_v, ref_act, ref_lp, ref_val, n, seed,
+                                                    step_ctr);
+        /* path under test */
+        if (prev && cfx_classic_done_to_terminals(dev, prev, term, n, st) != CFX_OK) rc = 1;
+        cfx_forward_io io;
+        memset(&io, 0, sizeof(io));
+        io.records = rec;
+        io.prev_terminals = prev ? term : NULL;
+        io.actions = cfx_act;
+        io.logits_av = d_lav;
+        io.seed = seed;
+        io.bump_step = 1;
+        if (rc == 0 && cfx_policy_forward(cp, &io, st) != CFX_OK) rc = 1;
+        if (rc) {
+            fprintf(stderr, "cfx: %s\n", cfx_last_error());
+            break;
+        }
+        refcl_k_compare<<<grid, block, 0, st>>>(logits, b_a, ref_val, d_lav, ref_act, cfx_act, n, d_fmax, d_counts);
+        /* the env advances with the actions of the path under test */
+        step_mark_kernel<<<grid, block, 0, st>>>(g, cfx_act, rewards, done[t & 1], reset_list, reset_ctrl, n);
+        refcl_k_count_done<<<grid, block, 0, st>>>(done[t & 1], n, d_counts);
+        int rwgrid = (n + RESET_WARP_BLOCK / 32 - 1) / (RESET_WARP_BLOCK / 32);
+        if (rwgrid > 512) rwgrid = 512;
+        reset_warp_ctr_kernel<<<rwgrid, RESET_WARP_BLOCK, 0, st>>>(g, reset_list, reset_ctrl, n, seed, step_ctr);
+        bump_ctr_kernel<<<1, 1, 0, st>>>(step_ctr);
+        RC_CHECK(cudaGetLastError());
+        if ((t & 15) == 15) RC_CHECK(cudaStreamSynchronize(st));
+    }
+    RC_CHECK(cudaStreamSynchronize(st));
+    if (rc == 0 && cfx_policy_check(cp, st) != CFX_OK) {
+        fprintf(stderr, "cfx: %s\n", cfx_last_error());
+        rc = 1;
+    }
+    unsigned fm[4];
+    unsigned long long cn[4];
+    RC_CHECK(cudaMemcpy(fm, d_fmax, sizeof(fm), cudaMemcpyDeviceToHost));
+    RC_CHECK(cudaMemcpy(cn, d_counts, sizeof(cn), cudaMemcpyDeviceToHost));
+    const double total = (double)n * (double)steps;
+    float f0, f1, f2;
+    memcpy(&f0, &fm[0], 4); memcpy(&f1, &fm[1], 4); memcpy(&f2, &fm[2], 4);
+    out[0] = f0; out[1] = f1; out[2] = (double)cn[0] / total; out[3] = (double)cn[1] / total;
+    out[4] = (double)cn[2]; out[5] = f2; out[6] = total;
+    if (cp) cfx_policy_destroy(cp);
+    cudaFree(arena); cudaFree(d_params); cudaFree(h0); cudaFree(h1); cudaFree(pre); cudaFree(logits);
+    cudaFree(ref_state); cudaFree(ref_lp); cudaFree(ref_val); cudaFree(rewards); cudaFree(term); cudaFree(d_lav);
+    cudaFree(ref_act); cudaFree(cfx_act); cudaFree(reset_list); cudaFree(reset_ctrl); cudaFree(done[0]);
+    cudaFree(done[1]); cudaFree(rec); cudaFree(step_ctr); cudaFree(d_fmax); cudaFree(d_counts);
+    cudaStreamDestroy(st);
+    cublasDestroy(blas);
+    return rc;
+}
+#endif
 
 } /* extern "C" */

@@ -411,6 +411,133 @@ double refcu_rollout_swap_sps(int n, int iters, unsigned long long seed, int gra
     cu_vec_free(&v);
     return sps;
 }
+/* ---- lock-step rollout: the reference's CUDA env, driven by this library's forward, with the
+ * reference's strict-fp32 cuBLAS pipeline consuming the same records beside it ----
+ * Protocol of the reference's runverify (:12501-12507, :12545-12603): the env advances with
+ * the actions of the path under test (cfx_policy_forward at `precision`); at every step both
+ * forwards read the same record row (written on the device by k_record_obs) and the same
+ * prev_terminals.  sync_state = 0: both keep their own recurrent state for the whole rollout
+ * (free-running); 1: the reference's state is overwritten with this library's before every
+ * step, so the figures measure one forward.  The comparison runs on the device every step.
+ * out[0] max |dlogit| (reference logits with their bias added), out[1] max |dvalue|,
+ * out[2] fraction of env-steps with the same greedy action, out[3] with the same sampled action
+ * (same Philox draw on both sides), out[4] episode ends seen, out[5] max |logit|,
+ * out[6] env-steps compared.  Returns 0, or 1 when a cfx call failed (message on stderr). */
+__global__ void refcu_k_compare(const float* __restrict__ ref_logits, const float* __restrict__ b_a,
+                                const float* __restrict__ b_v, const float* __restrict__ cfx_lav,
+                                const int* __restrict__ ref_act, const int* __restrict__ cfx_act,
+                                const float* __restrict__ terminals, int n, unsigned* fmax,
+                                unsigned long long* counts) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n) return;
+    const float* r = ref_logits + (size_t)e * CF_NN_AV;
+    const float* c = cfx_lav + (size_t)e * CF_NN_AV;
+    float dmax = 0.f, lmax = 0.f, rbest = 0.f, cbest = 0.f;
+    int ra = 0, ca = 0;
+    for (int a = 0; a < CRAFTAX_NUM_ACTIONS; a++) {
+        const float rl = r[a] + b_a[a], cl = c[a];
+        dmax = fmaxf(dmax, fabsf(rl - cl));
+        lmax = fmaxf(lmax, fabsf(rl));
+        if (a == 0 || rl > rbest) { rbest = rl; ra = a; }
+        if (a == 0 || cl > cbest) { cbest = cl; ca = a; }
+    }
+    const float dv = fabsf(r[CRAFTAX_NUM_ACTIONS] + b_v[0] - c[CRAFTAX_NUM_ACTIONS]);
+    atomicMax(&fmax[0], __float_as_uint(dmax));   /* non-negative floats order like their bits */
+    atomicMax(&fmax[1], __float_as_uint(dv));
+    atomicMax(&fmax[2], __float_as_uint(lmax));
+    if (ra == ca) atomicAdd(&counts[0], 1ULL);
+    if (ref_act[e] == cfx_act[e]) atomicAdd(&counts[1], 1ULL);
+    if (terminals[e] != 0.0f) atomicAdd(&counts[2], 1ULL);
+}
+
+int refcu_lockstep(int n, int steps, unsigned long long seed, const float* host_arena, int precision,
+                   int sync_state, double* out) {
+    CuVec v; CuPolicy p;
+    cu_vec_init(&v, n, seed);
+    g_gemm_bf16 = 0;
+    cu_policy_init(&p, n);   /* record row, sampler outputs; also the reference fp32 pipeline */
+    refcu_h2d(p.params, host_arena, (size_t)CF_NN_PARAM_COUNT * sizeof(float));
+    cu_params_refresh_bf16(&p, p.stream);
+    cu_pack_wav(&p, p.stream);
+    CUBLAS_CHECK(cublasSetMathMode(g_blas, CUBLAS_DEFAULT_MATH));
+    int dev = 0;
+    CU_CHECK(cudaGetDevice(&dev));
+    cfx_policy* cp = NULL;
+    float* d_lav = NULL; int* d_cact = NULL; unsigned* d_fmax = NULL; unsigned long long* d_counts = NULL;
+    CU_CHECK(cudaMalloc(&d_lav, (size_t)n * CF_NN_AV * sizeof(float)));
+    CU_CHECK(cudaMalloc(&d_cact, (size_t)n * sizeof(int)));
+    CU_CHECK(cudaMalloc(&d_fmax, 4 * sizeof(unsigned)));
+    CU_CHECK(cudaMalloc(&d_counts, 4 * sizeof(unsigned long long)));
+    CU_CHECK(cudaMemset(d_fmax, 0, 4 * sizeof(unsigned)));
+    CU_CHECK(cudaMemset(d_counts, 0, 4 * sizeof(unsigned long long)));
+    int rc = 0;
+    if (cfx_policy_create(&cp, dev, n, CF_NN_HIDDEN, CF_NN_LAYERS, CRAFTAX_NUM_ACTIONS, precision) != CFX_OK ||
+        cfx_policy_set_weights(cp, p.params, CF_NN_PARAM_COUNT, 1) != CFX_OK) {
+        fprintf(stderr, "cfx: %s\n", cfx_last_error());
+        rc = 1;
+    }
+    CU_CHECK(cudaDeviceSynchronize());
+    refcu r;
+    memset(&r, 0, sizeof(r));
+    r.n = n;
+    cudaStream_t st = p.stream;
+    const size_t state_bytes = (size_t)CF_NN_LAYERS * CF_NN_HIDDEN * n * sizeof(float);
+    for (int t = 0; t < steps && rc == 0; t++) {
+        k_record_obs<<<(int)(((size_t)n * 32 + 255) / 256), 256, 0, st>>>(p.rec, n);
+        CU_CHECK(cudaMemsetAsync(v.d_reset_count, 0, sizeof(int), st));
+        CU_CHECK(cudaMemsetAsync(v.d_spawn_count, 0, sizeof(int), st));
+        if (sync_state)
+            CU_CHECK(cudaMemcpyAsync(p.h_state, cfx_policy_state(cp), state_bytes, cudaMemcpyDeviceToDevice, st));
+        /* reference fp32 pipeline: its sampler output goes to p.d_act, its env-action slot to a sink */
+        refcu_enqueue(&r, &p, p.rec, v.d_terminals, seed, p.xobs);
+        k_bump_ctr<<<1, 1, 0, st>>>(p.step_ctr);
+        /* path under test: fills the env's action slots */
+        cfx_forward_io io;
+        memset(&io, 0, sizeof(io));
+        io.records = p.rec;
+        io.prev_terminals = v.d_terminals;
+        io.env_actions = v.d_actions;
+        io.actions = d_cact;
+        io.logits_av = d_lav;
+        io.seed = seed;
+        io.bump_step = 1;
+        if (cfx_policy_forward(cp, &io, st) != CFX_OK) {
+            fprintf(stderr, "cfx: %s\n", cfx_last_error());
+            rc = 1;
+            break;
+        }
+        refcu_k_compare<<<(n + 255) / 256, 256, 0, st>>>(p.logits, p.w.b_a, p.w.b_v, d_lav, p.d_act, d_cact,
+                                                         v.d_terminals, n, d_fmax, d_counts);
+        cu_launch_step_run(v.d_envs, n, v.d_resets, NULL, st);
+        int tail_blocks = (n * 32 + 255) / 256;
+        if (tail_blocks > 512) tail_blocks = 512;
+        k_spawn_tail<<<tail_blocks, 256, 0, st>>>();
+        if (v.lazy) cu_launch_reset_list_warp(v.d_envs, v.d_resets, n, st);
+        else k_reset_list<<<(n + 63) / 64, 64, 0, st>>>(v.d_envs, v.d_resets);
+        CU_CHECK(cudaGetLastError());
+        if ((t & 15) == 15) CU_CHECK(cudaStreamSynchronize(st));
+    }
+    CU_CHECK(cudaStreamSynchronize(st));
+    if (rc == 0 && cfx_policy_check(cp, st) != CFX_OK) {
+        fprintf(stderr, "cfx: %s\n", cfx_last_error());
+        rc = 1;
+    }
+    unsigned fm[4]; unsigned long long cn[4];
+    CU_CHECK(cudaMemcpy(fm, d_fmax, sizeof(fm), cudaMemcpyDeviceToHost));
+    CU_CHECK(cudaMemcpy(cn, d_counts, sizeof(cn), cudaMemcpyDeviceToHost));
+    const double total = (double)n * (double)steps;
+    float f0, f1, f2;
+    memcpy(&f0, &fm[0], 4); memcpy(&f1, &fm[1], 4); memcpy(&f2, &fm[2], 4);
+    out[0] = f0; out[1] = f1; out[2] = (double)cn[0] / total; out[3] = (double)cn[1] / total;
+    out[4] = (double)cn[2]; out[5] = f2; out[6] = total;
+    CUBLAS_CHECK(cublasSetMathMode(g_blas, CUBLAS_TF32_TENSOR_OP_MATH));
+    if (cp) cfx_policy_destroy(cp);
+    cudaFree(d_lav); cudaFree(d_cact); cudaFree(d_fmax); cudaFree(d_counts);
+    cu_policy_free(&p);
+    cu_vec_free(&v);
+    return rc;
+}
 #endif
+
 
 } /* extern "C" */

@@ -7,7 +7,7 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, os.path.join(ROOT, "craftax.cu_b200"))
-from cfx.sharding import aggregate_throughput, env_slice  # noqa: E402
+from cfx.sharding import aggregate_throughput, env_slice, max_over_ranks  # noqa: E402
 
 
 @pytest.mark.parametrize("n,world", [(262144, 1), (262144 * 8, 8), (96, 2), (160, 4), (32, 4), (2080, 3)])
@@ -37,8 +37,9 @@ def _worker(rank, world, port, q):
     a, b = env_slice(rank, world, 2080)
     ms = 2.0 if rank == 0 else 5.0        # the slower rank sets the job time
     sps, t = aggregate_throughput(ms, (b - a) * 10, dist)
+    both = max_over_ranks([ms, 7.0 - ms], dist)
     dist.barrier()
-    q.put((rank, a, b, sps, t))
+    q.put((rank, a, b, sps, t, both))
     dist.destroy_process_group()
 
 
@@ -57,7 +58,8 @@ def test_two_rank_aggregation_over_gloo():
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    (r0, a0, b0, sps0, t0), (r1, a1, b1, sps1, t1) = res
+    (r0, a0, b0, sps0, t0, m0), (r1, a1, b1, sps1, t1, m1) = res
+    assert m0 == m1 == [5.0, 5.0]
     assert (a0, b1) == (0, 2080) and b0 == a1
     assert t0 == t1 == 5.0
     assert sps0 == sps1 == pytest.approx(2080 * 10 / 5e-3)
@@ -66,3 +68,4 @@ def test_two_rank_aggregation_over_gloo():
 def test_single_process_aggregate():
     sps, t = aggregate_throughput(4.0, 1000)
     assert t == 4.0 and sps == pytest.approx(250000.0)
+    assert max_over_ranks([1.5, 2.5]) == [1.5, 2.5]
