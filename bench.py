@@ -12,8 +12,10 @@ cfx_policy_forward_host with pinned host buffers (copies inside the timed region
 Under torchrun each rank drives its own GPU and its own contiguous slice of envs;
 there is no data-path collective, only a barrier and a max over ranks of the timings.
 The K-step region is timed several times (`timed_repetitions`, each bracketed by a barrier
-and a synchronize, max over ranks per repetition) and the median repetition is reported, so
-that a few milliseconds of work are not judged on one sample.  At N = 1 the line also
+and a synchronize, max over ranks per repetition, a short idle gap between repetitions) and the
+median repetition is reported, so that a few milliseconds of work are not judged on one
+sample; `sustained` is the same step run back to back for about a fifth of a second, where a
+1 kW part meets its power cap (its clock record is reported with it).  At N = 1 the line also
 carries the reference's own cuBLAS forward on the same GPU and inputs (`reference_cublas`,
 from the library built out of the reference sources when it is present) and the CPU arm
 (`cpu_baseline`).
@@ -61,6 +63,8 @@ class ClockSampler:
     def __init__(self, index):
         self.index, self.mhz, self.bits, self.max_mhz = index, [], 0, None
         self._stop = threading.Event()
+        self.active = threading.Event()   # samples are taken only while a timed region runs
+        self.active.set()
         self.thread = None
         self._nvml = None
         try:   # NVML is brought up here, before the warm-up, so that start() costs nothing
@@ -86,7 +90,8 @@ class ClockSampler:
 
         def loop():
             while not self._stop.is_set():
-                self._sample()
+                if self.active.is_set():
+                    self._sample()
                 time.sleep(0.0005)
         self.thread = threading.Thread(target=loop, daemon=True)
         self.thread.start()
@@ -185,7 +190,10 @@ def run_cfx(args):
     rep_ms, per_step = [], []
     for _ in range(reps):
         timers = [cfx.Timer(dev) for _ in range(args.steps)]
+        sampler.active.clear()
+        time.sleep(args.rep_gap_ms * 1e-3)   # repetitions are separate measurements, not one long run
         barrier()
+        sampler.active.set()
         t_all = cfx.Timer(dev)
         t_all.start(stream)
         for t in timers:
@@ -196,6 +204,20 @@ def run_cfx(args):
         barrier()
         rep_ms.append(t_all.elapsed_ms())
         per_step.extend(t.elapsed_ms() for t in timers)
+    clocks = sampler.stop()   # sampled over the repetitions of the K-step region
+    # the same step back to back for ~0.2 s: what a long rollout sees under the power cap
+    sus_sampler = ClockSampler(dev)
+    sus_steps = int(np.clip(args.sustained_ms / max(1e-3, float(np.median(per_step))), args.steps, 2000))
+    barrier()
+    sus_sampler.start()
+    t_sus = cfx.Timer(dev)
+    t_sus.start(stream)
+    for _ in range(sus_steps):
+        step()
+    t_sus.stop(stream)
+    barrier()
+    sustained_ms = t_sus.elapsed_ms() / sus_steps
+    sus_clocks = sus_sampler.stop()
     pol.check()
 
     # end to end through the host-buffer entry point, pinned buffers
@@ -239,10 +261,9 @@ def run_cfx(args):
     tc.stop(stream)
     pol.sync()
     readback_ms = tc.elapsed_ms() / e2e_steps
-    clocks = sampler.stop()   # sampled over both timed regions (device-resident and end to end)
 
-    v = max_over_ranks(list(rep_ms) + [e2e_ms, upload_ms, readback_ms], dist)
-    rep_ms, (e2e_ms, upload_ms, readback_ms) = np.array(v[:reps]), v[reps:]
+    v = max_over_ranks(list(rep_ms) + [e2e_ms, upload_ms, readback_ms, sustained_ms], dist)
+    rep_ms, (e2e_ms, upload_ms, readback_ms, sustained_ms) = np.array(v[:reps]), v[reps:]
     total_ms = float(np.median(rep_ms))
     # whole job: env-steps of all ranks over the slowest rank's time
     value, _ = aggregate_throughput(total_ms, n * args.steps, dist)
@@ -293,6 +314,8 @@ def run_cfx(args):
         "timed_repetitions": reps,
         "ms_per_step_repetitions": [float(x) / args.steps for x in rep_ms],
         "clocks": clocks,
+        "sustained": {"ms_per_step": sustained_ms, "value": world * n / (sustained_ms * 1e-3), "steps": sus_steps,
+                      "clocks": sus_clocks},
     }
     if rank == 0 and world == 1 and not args.no_reference_cublas:
         line["reference_cublas"] = reference_cublas_forward(args, d_rec, d_pt, kernel_ms)
@@ -602,6 +625,9 @@ def main():
     ap.add_argument("--no-reference-cublas", action="store_true")
     ap.add_argument("--min-timed-ms", type=float, default=100.0,
                     help="device time to fill with repetitions of the K-step region")
+    ap.add_argument("--rep-gap-ms", type=float, default=30.0, help="idle gap between repetitions")
+    ap.add_argument("--sustained-ms", type=float, default=200.0,
+                    help="length of the back-to-back run reported as `sustained`")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "cfx" else args.warmup

@@ -766,14 +766,3 @@ int cfx_timer_elapsed_ms(void* timer, float* ms) {
 }
 
 }  // extern "C"
-
-#ifdef CFX_TIMELINE
-// Debug builds only: per-role event log of block 0 of the fused kernel.
-extern "C" int cfx_debug_timeline(cfx::FusedPlan* p, long long* host_out, int arm);
-extern "C" int cfx_policy_debug_timeline(cfx_policy* p, long long* host_out, int arm) {
-    if (!p || !p->fused) return CFX_ERR_INVALID;
-    CFX_GUARD(p->device);
-    cudaStreamSynchronize(p->stream);
-    return cfx_debug_timeline(p->fused, host_out, arm);
-}
-#endif

@@ -54,7 +54,9 @@ template <int HID> struct Hd {
     static constexpr int kSlices = HID / kSliceUnits;     // gate slices per layer (4 / 2)
     static constexpr int kStateItems = HID / kHalfUnits;  // state boxes (128 rows x 32 units) per layer (8 / 4)
     static constexpr int kKBlocks = HID / 64;             // K blocks of 64 per HID-wide operand (4 / 2)
-    static constexpr int kEncCopyBytes = HID * 128;       // encoder stage: one chunk, [HID units][64 K] 16-bit
+    static constexpr int kEncBlockBytes = HID * 128;      // one encoder chunk: [HID units][64 K] 16-bit
+    static constexpr int kEncCopyBytes = 2 * HID * 128;   // encoder stage: two chunks
+    static_assert((HID / 64) % 2 == 0, "a gate stage carries two K blocks");
 };
 // brings the shapes of Hd<HID> into a function body
 #define CFX_DIMS(HID)                                                                        \
@@ -79,36 +81,29 @@ template <> struct Gm<CFX_GAME_CLASSIC> {
 };
 
 constexpr int kNBMax = 8;        // weight ring slots (one stage each): see Cfg
-// Ring shapes of the CTA-pair mode (compile-time tuning knobs; measured at 262,144 envs: 6 or 8
-// weight slots 0.413-0.414 ms, 5 slots with a record ring of its own 0.420 ms, 4 slots 0.434 ms)
-#ifndef CFX_PAIR_NB
-#define CFX_PAIR_NB 6   // weight slots of 16 KB
-#endif
-#ifndef CFX_PAIR_NS
-#define CFX_PAIR_NS 6   // state slots of 16 KB
-#endif
-#ifndef CFX_PAIR_ALIAS
-#define CFX_PAIR_ALIAS 1   // record ring inside the state slots
-#endif
-#ifndef CFX_PAIR_NR
-#define CFX_PAIR_NR 6   // record slots (= state slots when the ring lives inside them)
-#endif
+// Ring shapes of the CTA-pair mode
+constexpr int kPairNS = 6;       // state slots of 16 KB; the record ring lives inside them
 constexpr int kSSlot = 16384, kNSMax = 6;
 constexpr int kRBoxBytes = 32 * 80, kRSlot = 4 * kRBoxBytes, kNRMax = 6;
 constexpr int kAexpSlots = 8;
 constexpr int kKBlocksMax = 4;
 
-// Image blocks (one K block of 64 columns each) and the ring stages that carry them:
-// encoder stage = one chunk, 256 units (two 128-unit blocks, 32 KB); gate stage = one K block
-// of one 64-unit slice (192 rows, 24 KB); head stage = all four K blocks (24 KB).
-constexpr int kGateStageBytes = 3 * kSliceUnits * 128;  // block: [192 rows][64 K]
-constexpr int kGateCopyBytes = kGateStageBytes;
+// Image blocks (one K block of 64 columns each) and the ring stages that carry them.  A stage
+// holds TWO blocks, so that the MMA thread waits, probes and commits once per eight MMAs:
+// encoder stage = two chunks of 256 units (2 x 32 KB); gate stage = two K blocks of one 64-unit
+// slice (2 x 192 rows, 2 x 24 KB); head stage = all K blocks.  One CTA per tile stages whole
+// stages, [block][rows][64 K]; in a CTA pair every CTA stages its half of the rows of both
+// blocks, laid out [half][block][rows / 2][64 K] so that a CTA's part is one contiguous copy.
+constexpr int kStageBlocks = 2;
+constexpr int kGateBlockBytes = 3 * kSliceUnits * 128;               // block: [192 rows][64 K]
+constexpr int kGateStageBytes = kStageBlocks * kGateBlockBytes;
 // head stage: one CTA per tile [K block][rows][64 K]; pairs [half][K block][rows / 2][64 K]
 template <int GAME, int HID> __host__ __device__ constexpr int head_bytes(bool pair) {
     return Hd<HID>::kKBlocks * (pair ? Gm<GAME>::kHeadPair : Gm<GAME>::kHeadSingle) * 128;
 }
 template <int GAME, int HID> __host__ __device__ constexpr size_t enc_bytes() {
-    return (size_t)Gm<GAME>::kEncChunks * Hd<HID>::kEncCopyBytes;
+    static_assert(Gm<GAME>::kEncChunks % 2 == 0, "an encoder stage carries two chunks");
+    return (size_t)Gm<GAME>::kEncChunks * Hd<HID>::kEncBlockBytes;
 }
 
 // A lane that handles every G-th item of an N-slot ring waits on its slot's "empty" barrier
@@ -121,7 +116,7 @@ template <int GAME, int HID> __host__ __device__ constexpr size_t enc_bytes() {
 
 
 template <int GAME, int HID> __host__ __device__ constexpr size_t image_bytes(int L) {   // room for either head layout
-    return enc_bytes<GAME, HID>() + (size_t)L * Hd<HID>::kSlices * Hd<HID>::kKBlocks * kGateStageBytes +
+    return enc_bytes<GAME, HID>() + (size_t)L * Hd<HID>::kSlices * Hd<HID>::kKBlocks * kGateBlockBytes +
            (size_t)Hd<HID>::kKBlocks * kHeadMax * 128;
 }
 
@@ -141,24 +136,25 @@ enum Bar {
 
 // Shared memory map (offsets from a 1024-byte aligned base) and the shapes that depend on the
 // launch mode.
-//  one CTA per tile: weight ring 4 x 32 KB (whole stages); the record ring (4 x 10 KB) lives
-//    INSIDE the state slots (records are needed only while the encoder runs, state boxes only
-//    while the gate layers run; REC_DONE and S_DONE order the two uses per tile);
-//  CTA pair (cta_group::2): every CTA stages half of each weight stage, 4 x 16 KB; the 64 KB
-//    this frees hold a record ring of its own, 6 x 10 KB, that runs ahead into the next tile.
+//  one CTA per tile: weight ring 2 x 64 KB (whole two-block stages), state ring 4 x 16 KB;
+//  CTA pair (cta_group::2): every CTA stages half of each weight stage, 3 x 32 KB, and has a
+//    state ring of 6 x 16 KB.
+//  In both modes the record ring (one 10 KB slot per state slot) lives INSIDE the state slots:
+//  records are needed only while the encoder runs, state boxes only while the gate layers run;
+//  REC_DONE and S_DONE order the two uses per tile.
 template <bool PAIR, int GAME, int HID> struct Cfg {
     static constexpr int kH = HID, kStateItems = Hd<HID>::kStateItems;
-    static constexpr int kNB = PAIR ? CFX_PAIR_NB : 4;
-    static constexpr int kBSlot = PAIR ? 16384 : 32768;
+    static constexpr int kNB = PAIR ? 3 : 2;             // stages of two blocks (96 / 128 KB of weights in flight)
+    static constexpr int kBSlot = PAIR ? 32768 : 65536;
     static constexpr int kWLanes = kNB;                  // one lane per slot
     static constexpr int kHeadRows = PAIR ? Gm<GAME>::kHeadPair : Gm<GAME>::kHeadSingle;   // N of the head MMA
     static constexpr int kHeadKbBytes = (PAIR ? kHeadRows / 2 : kHeadRows) * 128;   // one K block of the head rows a CTA stages
     static constexpr int kM = PAIR ? 256 : 128;
     // state ring slots: even, so that slot parity = warpgroup; at most one layer's boxes
-    static constexpr int kNS = PAIR && CFX_PAIR_NS <= kStateItems ? CFX_PAIR_NS : 4;
+    static constexpr int kNS = PAIR && kPairNS <= kStateItems ? kPairNS : 4;
     // record ring inside the state slots (full game only: the classic records need no ring)
-    static constexpr bool kAlias = GAME == CFX_GAME_FULL && (PAIR ? (CFX_PAIR_ALIAS != 0) : true);
-    static constexpr int kNR = GAME != CFX_GAME_FULL ? 0 : (kAlias ? kNS : (PAIR ? CFX_PAIR_NR : 4));
+    static constexpr bool kAlias = GAME == CFX_GAME_FULL;
+    static constexpr int kNR = GAME != CFX_GAME_FULL ? 0 : kNS;
     static constexpr int kRStride = kAlias ? kSSlot : kRSlot;
     static constexpr int kOffB = 0;
     static constexpr int kOffS = kOffB + kNB * kBSlot;
@@ -207,7 +203,6 @@ struct Params {
     int rec_bytes;        // bytes of one record (996 full game, 148 classic)
     int num_tiles_loop;   // trip bound of the tile loops: num_tiles, rounded up to even for CTA pairs
     size_t off_b_enc, off_b_a, off_b_v;
-    long long* timeline;  // debug builds only (CFX_TIMELINE): per-role (tag, clock) log of block 0
 };
 
 // ------------------------------------------------------------------ weight image
@@ -237,39 +232,64 @@ __device__ inline __nv_bfloat16 to16<__nv_bfloat16>(float v) {
     return __float2bfloat16_rn(v);
 }
 
+// Position of one 16-bit element inside a two-block stage of `rows` rows per block: which
+// block, which row of the block, which K column, and the byte offset of the element in the
+// stage's shared-memory image (128-byte swizzled tiles).  `b` is the element's index-order byte
+// offset in the stage; the mapping is a bijection of the stage's bytes.
+struct StagePos { int blk, row, c; uint32_t dst; };
+__host__ __device__ inline StagePos stage_pos(uint32_t b, int rows, bool pair) {
+    StagePos p;
+    if (pair) {   // [half][block][rows / 2][64 K]
+        const uint32_t tile = (uint32_t)(rows / 2) * 128, half_bytes = kStageBlocks * tile;
+        const uint32_t half = b / half_bytes, r2 = b % half_bytes, e = (r2 % tile) / 2;
+        p.blk = (int)(r2 / tile);
+        p.c = (int)(e % 64);
+        p.row = (int)(half * (rows / 2) + e / 64);
+        p.dst = half * half_bytes + (uint32_t)p.blk * tile + sw128_off(e / 64, (e % 64) * 2);
+    } else {      // [block][rows][64 K]
+        const uint32_t tile = (uint32_t)rows * 128, e = (b % tile) / 2;
+        p.blk = (int)(b / tile);
+        p.c = (int)(e % 64);
+        p.row = (int)(e / 64);
+        p.dst = (uint32_t)p.blk * tile + sw128_off(e / 64, (e % 64) * 2);
+    }
+    return p;
+}
+
 // One thread per 16-bit element of the image.  Stage order = consumption order of the
-// kernel: encoder (chunk-major, unit halves), gate layers (layer, slice, K block), head.
+// kernel: encoder (chunk pairs), gate layers (layer, slice, K-block pair), head.
 template <typename T16, int GAME, int HID>
 __global__ void k_pack_image(const float* __restrict__ params, uint8_t* __restrict__ image, int L,
                              size_t off_w_gru, size_t off_w_a, size_t off_w_v, int pair) {
     CFX_DIMS(HID);
     constexpr int kA = Gm<GAME>::kA;
-    constexpr int kEncStageBytes = 128 * 128;   // image block: [128 units][64 K] 16-bit
-    constexpr int kEncBlocks = kH / 128;        // blocks per encoder chunk
     const size_t total = image_bytes<GAME, HID>(L) / 2;
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     size_t byte = idx * 2;
     const size_t enc_b = enc_bytes<GAME, HID>();
-    const size_t gate_bytes = (size_t)L * kSlices * kKBlocks * kGateStageBytes;
+    const size_t gate_bytes = (size_t)L * kSlices * kKBlocks * kGateBlockBytes;
     float v = 0.0f;
     uint32_t row, c;
     uint8_t* stage;
     if (byte < enc_b) {
-        const int s = (int)(byte / kEncStageBytes), e = (int)((byte % kEncStageBytes) / 2);
-        row = e / 64; c = e % 64;
-        stage = image + (size_t)s * kEncStageBytes;
-        const int chunk = s / kEncBlocks, half = s % kEncBlocks;
-        const int f = enc_feature<GAME>(chunk, c);
-        if (f >= 0) v = params[(size_t)f * kH + half * 128 + row];
+        const int s = (int)(byte / kEncCopyBytes);
+        const StagePos q = stage_pos((uint32_t)(byte % kEncCopyBytes), kH, pair != 0);
+        const int f = enc_feature<GAME>(kStageBlocks * s + q.blk, q.c);
+        if (f >= 0) v = params[(size_t)f * kH + q.row];
+        *reinterpret_cast<T16*>(image + (size_t)s * kEncCopyBytes + q.dst) = to16<T16>(v);
+        return;
     } else if (byte < enc_b + gate_bytes) {
         const size_t b = byte - enc_b;
-        const int s = (int)(b / kGateStageBytes), e = (int)((b % kGateStageBytes) / 2);
-        row = e / 64; c = e % 64;
-        stage = image + enc_b + (size_t)s * kGateStageBytes;
-        const int kb = s % kKBlocks, j = (s / kKBlocks) % kSlices, l = s / (kKBlocks * kSlices);
-        const int gate = row / kSliceUnits, unit = j * kSliceUnits + row % kSliceUnits;
-        v = params[off_w_gru + ((size_t)l * 3 * kH + gate * kH + unit) * kH + kb * 64 + c];
+        const int s = (int)(b / kGateStageBytes);
+        const StagePos q = stage_pos((uint32_t)(b % kGateStageBytes), 3 * kSliceUnits, pair != 0);
+        constexpr int kPairsPerSlice = kKBlocks / kStageBlocks;
+        const int kb = kStageBlocks * (s % kPairsPerSlice) + q.blk, j = (s / kPairsPerSlice) % kSlices,
+                  l = s / (kPairsPerSlice * kSlices);
+        const int gate = q.row / kSliceUnits, unit = j * kSliceUnits + q.row % kSliceUnits;
+        v = params[off_w_gru + ((size_t)l * 3 * kH + gate * kH + unit) * kH + kb * 64 + q.c];
+        *reinterpret_cast<T16*>(image + enc_b + (size_t)s * kGateStageBytes + q.dst) = to16<T16>(v);
+        return;
     } else {
         // head.  One CTA per tile: [K block][rows][64 K].  CTA pairs: CTA r stages head rows
         // [r rows/2, (r + 1) rows/2): [r][K block][rows / 2][64 K].
@@ -431,60 +451,12 @@ struct Smem {
     }
 };
 
-// Debug builds (-DCFX_CHECK): typed shared/global accesses verify their alignment, report a
-// violation and substitute an aligned address inside the same buffer.
-#ifdef CFX_CHECK
-template <typename T>
-__device__ __forceinline__ T* chk_ptr(T* p, const char* what) {
-    if ((reinterpret_cast<uintptr_t>(p) & (sizeof(T) - 1)) != 0) {
-        printf("CFX_CHECK %s: block %d thread %d ptr=%llx\n", what, (int)blockIdx.x, (int)threadIdx.x,
-               (unsigned long long)reinterpret_cast<uintptr_t>(p));
-        return reinterpret_cast<T*>(reinterpret_cast<uintptr_t>(p) & ~(uintptr_t)(sizeof(T) - 1));
-    }
-    return p;
-}
-#define CHKP(p, what) chk_ptr(p, what)
-#else
-#define CHKP(p, what) (p)
-#endif
-
-// Optional instrumentation of block 0 (debug builds only).
-//  -DCFX_TIMELINE: every role logs (tag, clock64) pairs.
-//  -DCFX_TIMELINE -DCFX_PROFILE: instead of a log, every role sums the cycles between
-//  consecutive marks into per-bucket registers and writes the sums once at its end (far less
-//  intrusive than the log: no stores on the timed path).
-#if defined(CFX_PROFILE)
-#define TL_INIT(role)                                  \
-    long long* tl_ptr = P.timeline + (role) * 4096;    \
-    long long pf_[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; \
-    long long pf_t = clock64()
-#define TLB(b, tag)                        \
-    do {                                   \
-        const long long n_ = clock64();    \
-        pf_[b] += n_ - pf_t;               \
-        pf_t = n_;                         \
-    } while (0)
-#define TL_FLUSH()                                                       \
-    do {                                                                 \
-        if (blockIdx.x == 0 && P.timeline != nullptr)                    \
-            for (int i_ = 0; i_ < 12; i_++) tl_ptr[i_] = pf_[i_];        \
-    } while (0)
-#elif defined(CFX_TIMELINE)
-#define TL_INIT(role) long long* tl_ptr = P.timeline + (role) * 4096; int tl_i = 0
-#define TLB(b, tag)                                                           \
-    do {                                                                      \
-        if (blockIdx.x == 0 && P.timeline != nullptr && tl_i < 2047) {        \
-            tl_ptr[2 * tl_i] = (long long)(tag);                              \
-            tl_ptr[2 * tl_i + 1] = clock64();                                 \
-            tl_i++;                                                           \
-            tl_ptr[4094] = tl_i;                                              \
-        }                                                                     \
-    } while (0)
-#define TL_FLUSH()
-#else
-#define TL_INIT(role)
-#define TLB(b, tag)
-#define TL_FLUSH()
+// Hooks of a profiling build: a header given with -include may define them to sum clock64
+// deltas per phase; in the library they expand to nothing.
+#ifndef CFX_MARK
+#define CFX_MARK_INIT(role)
+#define CFX_MARK(bucket)
+#define CFX_MARK_FLUSH()
 #endif
 
 // every role runs in its own function: a failed (timed-out) wait returns to the common exit
@@ -564,50 +536,50 @@ __device__ __forceinline__ void l2_prefetch_for_box(const Params& P, int tile, i
 // Weight stages: the image is laid out in consumption order, so stage s of a tile starts
 // where stage s-1 ended; every tile replays the same sequence (it stays L2 resident).
 // One lane per ring slot.  In a CTA pair every CTA stages its own half of the rows of each
-// stage (the halves are contiguous in the image); the odd CTA waits for its copy to land and
-// then arrives on the even CTA's "full" barrier, where the MMA thread waits.
+// stage (contiguous in the image); the odd CTA waits for its copy to land and then arrives on
+// the even CTA's "full" barrier, where the MMA thread waits.
 template <bool PAIR, int GAME, int HID>
 __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& P, int lane,
                                                   uint32_t rank, uint32_t bar0_cta0) {
     using C = Cfg<PAIR, GAME, HID>;
     CFX_DIMS(HID);
     constexpr int kEncChunks = Gm<GAME>::kEncChunks;
-    const int stages_gate = P.L * kSlices * kKBlocks;
+    constexpr int kEncStages = kEncChunks / kStageBlocks;
+    const int stages_gate = P.L * kSlices * (kKBlocks / kStageBlocks);
     const size_t enc_bytes = fused::enc_bytes<GAME, HID>();
-    uint32_t cnt = 0;
-    TL_INIT(3);
-    for (int tile = P.tile_begin + blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x) {
-        for (int s = 0; s < kEncChunks + stages_gate + 1; s++, cnt++) {
-            if ((int)(cnt % C::kWLanes) != lane) continue;
-            uint32_t bytes;
-            size_t off;
-            if (s < kEncChunks) {
-                bytes = kEncCopyBytes; off = (size_t)s * kEncCopyBytes;
-            } else if (s < kEncChunks + stages_gate) {
-                bytes = kGateCopyBytes; off = enc_bytes + (size_t)(s - kEncChunks) * kGateCopyBytes;
-            } else {
-                bytes = head_bytes<GAME, HID>(PAIR);
-                off = enc_bytes + (size_t)stages_gate * kGateCopyBytes;
-            }
-            if (PAIR) {
-                bytes >>= 1;
-                off += (size_t)rank * bytes;
-            }
-            const int slot = cnt % C::kNB;
-            CFX_WAIT(B_EMPTY + slot, ((cnt / C::kNB) & 1) ^ 1, W_B_EMPTY);
-            if (lane == 0) TLB(1, 0x10000 | s);
-#ifdef CFX_ABL_NOWEIGHTS
-            mbar_arrive(sm.bar(B_FULL + slot));
-#else
-            mbar_arrive_expect_tx(sm.bar(B_FULL + slot), bytes);
-            bulk_g2s(smem_u32(sm.b_ring() + slot * C::kBSlot), P.image + off, bytes, sm.bar(B_FULL + slot));
-#endif
-            if (PAIR && rank != 0) {
-                // local barrier (one arrival per phase here): wait for the copy, tell the even CTA
-                CFX_WAIT(B_FULL + slot, (cnt / C::kNB) & 1, W_B_FULL);
-                mbar_arrive_cluster(bar0_cta0 + 8u * (uint32_t)(B_FULL + slot));
-            }
+    static_assert(C::kWLanes == C::kNB, "one lane per slot: the lane's k-th stage is the slot's k-th fill");
+    // this lane's stages: every kNB-th of the launch-wide stage sequence, starting at `lane`
+    const int per_tile = kEncStages + stages_gate + 1;
+    int tile = P.tile_begin + blockIdx.x, s = lane;
+    auto normalise = [&]() {
+        while (s >= per_tile) { s -= per_tile; tile += gridDim.x; }
+    };
+    normalise();
+    for (uint32_t use = 0; tile < P.num_tiles_loop; use++) {
+        uint32_t bytes;
+        size_t off;
+        if (s < kEncStages) {
+            bytes = kEncCopyBytes; off = (size_t)s * kEncCopyBytes;
+        } else if (s < kEncStages + stages_gate) {
+            bytes = kGateStageBytes; off = enc_bytes + (size_t)(s - kEncStages) * kGateStageBytes;
+        } else {
+            bytes = head_bytes<GAME, HID>(PAIR);
+            off = enc_bytes + (size_t)stages_gate * kGateStageBytes;
         }
+        if (PAIR) {
+            bytes >>= 1;
+            off += (size_t)rank * bytes;
+        }
+        CFX_WAIT(B_EMPTY + lane, (use & 1) ^ 1, W_B_EMPTY);
+        mbar_arrive_expect_tx(sm.bar(B_FULL + lane), bytes);
+        bulk_g2s(smem_u32(sm.b_ring() + lane * C::kBSlot), P.image + off, bytes, sm.bar(B_FULL + lane));
+        if (PAIR && rank != 0) {
+            // local barrier (one arrival per phase here): wait for the copy, tell the even CTA
+            CFX_WAIT(B_FULL + lane, use & 1, W_B_FULL);
+            mbar_arrive_cluster(bar0_cta0 + 8u * (uint32_t)(B_FULL + lane));
+        }
+        s += C::kNB;
+        normalise();
     }
 }
 
@@ -639,10 +611,6 @@ __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& 
             if (C::kAlias) CFX_WAIT(S_DONE + lane, (it & 1) ^ 1, W_S_DONE);
             for (int kc = lane; kc < kRecFills; kc += kNR) {
                 CFX_WAIT(R_EMPTY + lane, (rec_phase<kNR>(it, kc) & 1) ^ 1, W_R_EMPTY);
-#ifdef CFX_ABL_NOREC
-                mbar_arrive(sm.bar(R_FULL + lane));
-                continue;
-#endif
                 mbar_arrive_expect_tx(sm.bar(R_FULL + lane), kRSlot);
 #pragma unroll
                 for (int i = 0; i < 4; i++)
@@ -656,10 +624,6 @@ __device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& 
         const uint32_t dst = smem_u32(sm.t_buf());
         for (int tile = P.tile_begin + blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
             CFX_WAIT(T_EMPTY, (it & 1) ^ 1, W_T_EMPTY);
-#ifdef CFX_ABL_NOREC
-            mbar_arrive(sm.bar(T_FULL));
-            continue;
-#endif
             mbar_arrive_expect_tx(sm.bar(T_FULL), kTailBytes);
 #pragma unroll
             for (int s3 = 0; s3 < 3; s3++)
@@ -692,23 +656,15 @@ __device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P,
                 // every record of the tile has been expanded
                 const int b = l * kStateItems + j;
                 if (C::kAlias && b < kNS) CFX_WAIT(REC_DONE, it & 1, W_REC_DONE);
-#ifdef CFX_ABL_NOSTATE
-                mbar_arrive(sm.bar(S_FULL + lane));
-                CFX_WAIT(ST_READY + lane, uses & 1, W_ST_READY);
-                uses++;
-#else
                 mbar_arrive_expect_tx(sm.bar(S_FULL + lane), kSSlot);
                 tensor_g2s_2d(slot_addr, &P.state_map[l], j * kHalfUnits, tile * kTile,
                               sm.bar(S_FULL + lane));
-#ifndef CFX_ABL_NOPREFETCH
                 l2_prefetch_for_box<HID>(P, tile, l, j);
-#endif
                 CFX_WAIT(ST_READY + lane, uses & 1, W_ST_READY);
                 uses++;
                 tensor_s2g_2d(&P.state_map[l], slot_addr, j * kHalfUnits, tile * kTile);
                 bulk_commit_group();
                 bulk_wait_group_read<0>();
-#endif
                 // this lane's last box of the tile has left the slot: records may come in
                 if (C::kAlias && b >= P.L * kStateItems - kNS) mbar_arrive(sm.bar(S_DONE + lane));
             }
@@ -723,15 +679,11 @@ __device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P,
 // a per-slot base and every K-step loop is fully unrolled (rebuilding descriptors per MMA
 // measured ~150 cycles per instruction on B200, against 45-50 for the bare instruction), and
 // MMAs are as wide as the tensor memory budget allows (N = 192 / 256).
-#ifdef CFX_ABL_NOMMA
-#define MMA_TS(...) ((void)0)
-#else
 #define MMA_TS(...)                                  \
     do {                                             \
         if (PAIR) mma_f16_ts_pair(__VA_ARGS__);      \
         else mma_f16_ts(__VA_ARGS__);                \
     } while (0)
-#endif
 // commits: in a pair they arrive on the barrier of BOTH CTAs
 #define MMA_COMMIT(bar)                  \
     do {                                 \
@@ -748,45 +700,58 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
     constexpr uint32_t idesc_enc = make_idesc(fmt, C::kM, kH);
     constexpr uint32_t idesc_gate = make_idesc(fmt, C::kM, 3 * kSliceUnits);
     constexpr uint32_t idesc_head = make_idesc(fmt, C::kM, C::kHeadRows);
+    // descriptor steps (16-byte units) between the two blocks of a stage: a CTA of a pair
+    // holds half of each block's rows
+    constexpr uint32_t kEncBlkStep = ((PAIR ? kH / 2 : kH) * 128) >> 4;
+    constexpr uint32_t kGateBlkStep = ((PAIR ? 3 * kSliceUnits / 2 : 3 * kSliceUnits) * 128) >> 4;
     const uint64_t bdesc0 = smem_desc_sw128(smem_u32(sm.b_ring()));
-    uint32_t bcnt = 0, acnt = 0, akb_use = 0, gcnt = 0, tcnt = 0;
+    uint32_t acnt = 0, akb_use = 0, gcnt = 0, tcnt = 0;
+    // position in the weight ring of the stage being consumed: slot and phase parity, advanced
+    // incrementally (a division per stage on this thread would sit on the critical path)
+    int bslot = 0;
+    uint32_t bpar = 0;
+    auto b_advance = [&]() {
+        if (++bslot == kNB) { bslot = 0; bpar ^= 1u; }
+    };
     // The "full" barriers of the NEXT stage are probed before the current stage's MMAs are
     // issued, so that the probe's shared-memory round trip (~150 cycles on this thread) runs
     // under the MMA issue; only a failed probe falls into the bounded wait.  Probing one stage
     // early is sound: the previous use of that slot has already been consumed by this thread,
     // so its barrier is at most one phase behind.
-    auto probe_b = [&](uint32_t cnt) -> bool {
-        return mbar_test_wait(sm.bar(B_FULL + (int)(cnt % kNB)), (cnt / kNB) & 1);
+    auto probe_b_next = [&]() -> bool {
+        const bool wrap = bslot + 1 == kNB;
+        return mbar_test_wait(sm.bar(B_FULL + (wrap ? 0 : bslot + 1)), wrap ? bpar ^ 1u : bpar);
     };
     auto probe_a = [&](uint32_t cnt) -> bool {
         return mbar_test_wait(sm.bar(AEXP_FULL + (int)(cnt % kAexpSlots)), (cnt / kAexpSlots) & 1);
     };
 #define CFX_WAIT_PROBED(ready, barid, parity, code) \
     if (!(ready) && !mbar_wait_spin(sm.bar(barid), (parity), sm.abort_flag(), (code))) return
-    TL_INIT(0);
-#ifdef CFX_PROFILE
-    if (blockIdx.x == 0 && P.timeline != nullptr) P.timeline[4 * 4096 + 3] = (long long)global_timer_ns();
-#endif
+    CFX_MARK_INIT(0);
     for (int tile = P.tile_begin + blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, tcnt++) {
-        TLB(0, 0x1000000);
+        CFX_MARK(0);
         // the encoder accumulator overlaps the head accumulator of the previous tile:
         // wait until the sampler threads have read it
         CFX_WAIT_LEADER(H_EMPTY, (tcnt & 1) ^ 1, W_H_EMPTY);
-        bool a_ready = probe_a(acnt), b_ready = probe_b(bcnt);
-        // ---- encoder: 14 operand chunks, N = 256 units
-        for (int kc = 0; kc < kEncChunks; kc++, acnt++, bcnt++) {
-            const int as = acnt % kAexpSlots;
-            const int slot = bcnt % kNB;
-            CFX_WAIT_PROBED(a_ready, AEXP_FULL + as, (acnt / kAexpSlots) & 1, W_AEXP_FULL);
-            TLB(2, 0x20000 | kc);
-            CFX_WAIT_PROBED(b_ready, B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
-            TLB(3, 0x30000 | kc);
-            tc_fence_after_sync();
-            a_ready = kc + 1 < kEncChunks ? probe_a(acnt + 1) : false;
-            b_ready = probe_b(bcnt + 1);
-            const uint32_t a_col = tmem + kColAexp + as * 32;
-            const uint64_t bd = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
-            {
+        bool a_ready = probe_a(acnt), b_ready = mbar_test_wait(sm.bar(B_FULL + bslot), bpar);
+        // ---- encoder: operand chunks of 64 features, N = 256 units; one weight stage per two chunks
+        for (int kp = 0; kp < kEncChunks / kStageBlocks; kp++) {
+            const int slot = bslot;
+            CFX_WAIT_PROBED(b_ready, B_FULL + slot, bpar, W_B_FULL);
+            CFX_MARK(3);
+            b_ready = probe_b_next();
+            b_advance();
+            const uint64_t bd0 = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
+#pragma unroll
+            for (int c2 = 0; c2 < kStageBlocks; c2++, acnt++) {
+                const int kc = kStageBlocks * kp + c2;
+                const int as = acnt % kAexpSlots;
+                CFX_WAIT_PROBED(a_ready, AEXP_FULL + as, (acnt / kAexpSlots) & 1, W_AEXP_FULL);
+                CFX_MARK(2);
+                tc_fence_after_sync();
+                a_ready = kc + 1 < kEncChunks ? probe_a(acnt + 1) : false;
+                const uint32_t a_col = tmem + kColAexp + as * 32;
+                const uint64_t bd = bd0 + (uint64_t)(c2 * kEncBlkStep);
                 if (kc == 0) MMA_TS(tmem + kColAcc, a_col, bd, idesc_enc, 0);
                 else MMA_TS(tmem + kColAcc, a_col, bd, idesc_enc, 1);
                 // short chunks: full game chunk 12 carries 24 map bytes (two K steps), the classic
@@ -797,76 +762,81 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
                     MMA_TS(tmem + kColAcc, a_col + 16, bd + 4, idesc_enc, 1);
                     MMA_TS(tmem + kColAcc, a_col + 24, bd + 6, idesc_enc, 1);
                 }
-                MMA_COMMIT(sm.bar(B_EMPTY + slot));
                 MMA_COMMIT(sm.bar(AEXP_EMPTY + as));
-                TLB(4, 0x38000 | kc);
+                CFX_MARK(4);
             }
-            
+            MMA_COMMIT(sm.bar(B_EMPTY + slot));
         }
         MMA_COMMIT(sm.bar(ACC_FULL));
-        
-        // ---- MinGRU layers: 4 slices of 64 units, one stage per K block, N = 192 (zh|zg|zp)
+
+        // ---- MinGRU layers: 4 slices of 64 units, one stage per two K blocks, N = 192 (zh|zg|zp)
         for (int l = 0; l < P.L; l++, akb_use++) {
             const uint32_t a_cur = tmem + ((l & 1) ? kColA1 : kColA0);
             for (int j = 0; j < kSlices; j++, gcnt++) {
                 CFX_WAIT_LEADER(G_EMPTY, (gcnt & 1) ^ 1, W_G_EMPTY);
-                TLB(5, 0x40000 | (l << 8) | j);
+                CFX_MARK(5);
+                // The gate accumulator overlaps the encoder accumulator, which the encoder
+                // epilogue of BOTH worker warpgroups reads until they have signalled their K
+                // blocks: the first gate MMA of a tile waits for all of them, not only for the K
+                // block it multiplies.
+                if (l == 0 && j == 0) {
 #pragma unroll
-                for (int kb = 0; kb < kKBlocks; kb++, bcnt++) {
-                    if (j == 0) {
-                        CFX_WAIT_LEADER(A_KB + kb, akb_use & 1, W_A_KB);
-                        TLB(9, 0x48000 | (l << 8) | kb);
-                    }
-                    const int slot = bcnt % kNB;
-                    CFX_WAIT_PROBED(b_ready, B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
-                    TLB(6, 0x50000 | (l << 8) | (j << 2) | kb);
-                    tc_fence_after_sync();
-                    b_ready = probe_b(bcnt + 1);
-                    const uint64_t bd = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
-                    {
+                    for (int kb = 0; kb < kKBlocks; kb++) CFX_WAIT_LEADER(A_KB + kb, akb_use & 1, W_A_KB);
+                    CFX_MARK(9);
+                }
+#pragma unroll
+                for (int kp = 0; kp < kKBlocks / kStageBlocks; kp++) {
+                    const int slot = bslot;
+                    CFX_WAIT_PROBED(b_ready, B_FULL + slot, bpar, W_B_FULL);
+                    CFX_MARK(6);
+                    b_ready = probe_b_next();
+                    b_advance();
+                    const uint64_t bd0 = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
+#pragma unroll
+                    for (int c2 = 0; c2 < kStageBlocks; c2++) {
+                        const int kb = kStageBlocks * kp + c2;
+                        // the layer's input arrives K block by K block (slice kb of the previous layer)
+                        if (j == 0 && l != 0) {
+                            CFX_WAIT_LEADER(A_KB + kb, akb_use & 1, W_A_KB);
+                            CFX_MARK(9);
+                        }
+                        tc_fence_after_sync();
 #pragma unroll
                         for (int ks = 0; ks < 4; ks++)
-                            MMA_TS(tmem + kColG, a_cur + kb * 32 + ks * 8, bd + (uint64_t)(2 * ks),
-                                       idesc_gate, (kb | ks) != 0 ? 1u : 0u);
-                        MMA_COMMIT(sm.bar(B_EMPTY + slot));
-                        TLB(7, 0x58000 | (l << 8) | (j << 2) | kb);
+                            MMA_TS(tmem + kColG, a_cur + kb * 32 + ks * 8,
+                                   bd0 + (uint64_t)(c2 * kGateBlkStep + 2 * ks), idesc_gate,
+                                   (kb | ks) != 0 ? 1u : 0u);
                     }
-                    
+                    MMA_COMMIT(sm.bar(B_EMPTY + slot));
+                    CFX_MARK(7);
                 }
                 MMA_COMMIT(sm.bar(G_FULL));
-                
             }
         }
-        // ---- heads: N = 48, one stage with all four K blocks
+        // ---- heads: N = 48 (64 in a pair), one stage with all K blocks
         {
             const uint32_t a_cur = tmem + ((P.L & 1) ? kColA1 : kColA0);
 #pragma unroll
             for (int kb = 0; kb < kKBlocks; kb++) CFX_WAIT_LEADER(A_KB + kb, akb_use & 1, W_A_KB);
             akb_use++;
-            const int slot = bcnt % kNB;
-            CFX_WAIT_PROBED(b_ready, B_FULL + slot, (bcnt / kNB) & 1, W_B_FULL);
+            const int slot = bslot;
+            CFX_WAIT_PROBED(b_ready, B_FULL + slot, bpar, W_B_FULL);
             tc_fence_after_sync();
+            b_advance();
             const uint64_t bd = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
-            {
 #pragma unroll
-                for (int kb = 0; kb < kKBlocks; kb++)
+            for (int kb = 0; kb < kKBlocks; kb++)
 #pragma unroll
-                    for (int ks = 0; ks < 4; ks++)
-                        MMA_TS(tmem + kColHead, a_cur + kb * 32 + ks * 8,
-                                   bd + (uint64_t)((kb * C::kHeadKbBytes + ks * 32) >> 4), idesc_head,
-                                   (kb | ks) != 0 ? 1u : 0u);
-                MMA_COMMIT(sm.bar(B_EMPTY + slot));
-                MMA_COMMIT(sm.bar(H_FULL));
-                TLB(8, 0x60000);
-            }
-            
-            bcnt++;
+                for (int ks = 0; ks < 4; ks++)
+                    MMA_TS(tmem + kColHead, a_cur + kb * 32 + ks * 8,
+                           bd + (uint64_t)((kb * C::kHeadKbBytes + ks * 32) >> 4), idesc_head,
+                           (kb | ks) != 0 ? 1u : 0u);
+            MMA_COMMIT(sm.bar(B_EMPTY + slot));
+            MMA_COMMIT(sm.bar(H_FULL));
+            CFX_MARK(8);
         }
     }
-    TL_FLUSH();
-#ifdef CFX_PROFILE
-    if (blockIdx.x == 0 && P.timeline != nullptr) P.timeline[4 * 4096 + 4] = (long long)global_timer_ns();
-#endif
+    CFX_MARK_FLUSH();
 }
 
 // ------------------------------------------------------------------ worker role
@@ -895,10 +865,9 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
     uint32_t tcnt = 0, gcnt = 0, it = 0;
     // the sampler offset is constant for the launch (the bump happens after every block is done)
     const unsigned long long step0 = P.uniforms == nullptr ? *P.step_ctr : 0ull;
-    TL_INIT(1 + wg);
-    const bool tl_on = (quarter == 0 && lane == 0);
+    CFX_MARK_INIT(1 + wg);
     for (int tile = P.tile_begin + blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++, tcnt++) {
-        if (tl_on) TLB(0, 0x1000000);
+        CFX_MARK(0);
         const int env = tile * kTile + row;
         const bool valid = env < P.n;
         const bool zero_state =
@@ -913,7 +882,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
             const uint32_t acnt = it * kEncChunks + kc;
             const int as = acnt % kAexpSlots;
             CFX_WAITW(AEXP_EMPTY + as, ((acnt / kAexpSlots) & 1) ^ 1, W_AEXP_EMPTY);
-            if (tl_on) TLB(2, 0x70000 | kc);
+            CFX_MARK(2);
             tc_fence_after_sync();
             uint32_t regs[32];
             if constexpr (GAME == CFX_GAME_CLASSIC) {
@@ -962,19 +931,14 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 constexpr int kNRw = C::kNR;
                 const int slot = rec_slot<kNRw>(kc);
                 CFX_WAITW(R_FULL + slot, rec_phase<kNRw>(it, kc) & 1, W_R_FULL);
-                if (tl_on) TLB(3, 0x80000 | kc);
+                CFX_MARK(3);
                 const uint8_t* src = sm.r_slot(slot) + rec_row_off + ((kRec * ii) & 15);
-#ifdef CFX_ABL_NOEXPAND
-#pragma unroll
-                for (int q = 0; q < 32; q++) regs[q] = 0x3c003c00u + (uint32_t)(src - sm.base);
-#else
 #pragma unroll
                 for (int q = 0; q < 16; q++) {
                     uint32_t w32 = *reinterpret_cast<const uint32_t*>(src + 4 * q);
                     if (kc == 12 && q >= 6) w32 = 0;  // record bytes 792.. are not map bytes
                     Op::bytes4(w32, regs[2 * q], regs[2 * q + 1]);
                 }
-#endif
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sm.bar(R_EMPTY + slot));
             } else {
@@ -1012,12 +976,12 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) arrive_mma(AEXP_FULL + as);
-            if (tl_on) TLB(4, 0x90000 | kc);
+            CFX_MARK(4);
         }
 
         // ---- encoder epilogue: accumulator + bias -> layer-0 input A0 (wg = unit half)
         CFX_WAITW(ACC_FULL, tcnt & 1, W_ACC_FULL);
-        if (tl_on) TLB(5, 0xA0000);
+        CFX_MARK(5);
         tc_fence_after_sync();
 #pragma unroll 2
         for (int b = 0; b < kH / 32; b++) {   // this warpgroup's kH / 2 units, 16 at a time
@@ -1043,7 +1007,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 arrive_mma(A_KB + (kKBlocks / 2) * wg + kb);
             }
         }
-        if (tl_on) TLB(1, 0xA8000);
+        CFX_MARK(1);
 
         // ---- MinGRU layers: both warpgroups work on every 64-unit slice; wg handles units
         // [64 j + 32 wg, 64 j + 32 wg + 32) = state box 2 j + wg of the layer
@@ -1052,7 +1016,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
             const uint32_t a_next = tmem + lane_base + ((l & 1) ? kColA0 : kColA1);
             for (int j = 0; j < kSlices; j++, gcnt++) {
                 CFX_WAITW(G_FULL, gcnt & 1, W_G_FULL);
-                if (tl_on) TLB(6, 0xB0000 | (l << 8) | j);
+                CFX_MARK(6);
                 tc_fence_after_sync();
                 const int box = 2 * j + wg;
                 const uint32_t scnt = (it * P.L + l) * kStateItems + box;
@@ -1084,9 +1048,9 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) arrive_mma(G_EMPTY);
-                if (tl_on) TLB(7, 0xB8000 | (l << 8) | j);
+                CFX_MARK(7);
                 CFX_WAITW(S_FULL + slot, (scnt / kNS) & 1, W_S_FULL);
-                if (tl_on) TLB(8, 0xC0000 | (l << 8) | j);
+                CFX_MARK(8);
 #pragma unroll
                 for (int hf = 0; hf < 2; hf++) {
                     uint32_t hn[8];
@@ -1094,12 +1058,6 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                     for (int q = 0; q < 4; q++) {
                         const int u = 16 * hf + 4 * q;  // first of four units
                         float4* sp = reinterpret_cast<float4*>(rbase + (((4 * hf + q) ^ xr) << 4));
-#ifdef CFX_ABL_NOCELL
-                        hn[2 * q] = zh[u] ^ zg[u + 1] ^ zp[u + 2] ^ xin[u / 2];
-                        hn[2 * q + 1] = zh[u + 3] ^ zg[u + 2] ^ zp[u] ^ xin[u / 2 + 1];
-                        if (zero_state && hn[2 * q] == 0x12345u) *sp = make_float4(0.f, 0.f, 0.f, 0.f);
-                        continue;
-#endif
                         float4 st = *sp;
                         if (zero_state) st = make_float4(0.f, 0.f, 0.f, 0.f);
                         // optional BPTT record of the post-zero input state (what the reference's
@@ -1120,16 +1078,6 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                         const float2 x01 = Op::unpack(xin[u / 2]), x23 = Op::unpack(xin[u / 2 + 1]);
                         float4 out;
                         float h0, h1, h2, h3;
-#ifdef CFX_CELL_SCALAR
-                        mingru_cell(__uint_as_float(zh[u]), __uint_as_float(zg[u]),
-                                    __uint_as_float(zp[u]), st.x, x01.x, out.x, h0);
-                        mingru_cell(__uint_as_float(zh[u + 1]), __uint_as_float(zg[u + 1]),
-                                    __uint_as_float(zp[u + 1]), st.y, x01.y, out.y, h1);
-                        mingru_cell(__uint_as_float(zh[u + 2]), __uint_as_float(zg[u + 2]),
-                                    __uint_as_float(zp[u + 2]), st.z, x23.x, out.z, h2);
-                        mingru_cell(__uint_as_float(zh[u + 3]), __uint_as_float(zg[u + 3]),
-                                    __uint_as_float(zp[u + 3]), st.w, x23.y, out.w, h3);
-#else
                         mingru_cell_pair(__uint_as_float(zh[u]), __uint_as_float(zh[u + 1]),
                                          __uint_as_float(zg[u]), __uint_as_float(zg[u + 1]),
                                          __uint_as_float(zp[u]), __uint_as_float(zp[u + 1]),
@@ -1138,7 +1086,6 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                                          __uint_as_float(zg[u + 2]), __uint_as_float(zg[u + 3]),
                                          __uint_as_float(zp[u + 2]), __uint_as_float(zp[u + 3]),
                                          st.z, st.w, x23.x, x23.y, out.z, out.w, h2, h3);
-#endif
                         *sp = out;
                         hn[2 * q] = Op::pack(h0, h1);
                         hn[2 * q + 1] = Op::pack(h2, h3);
@@ -1153,7 +1100,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                     arrive_mma(A_KB + j);
                     mbar_arrive(sm.bar(ST_READY + slot));
                 }
-                if (tl_on) TLB(9, 0xD0000 | (l << 8) | j);
+                CFX_MARK(9);
             }
         }
 
@@ -1165,7 +1112,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
             u = P.uniforms != nullptr ? P.uniforms[env]
                                       : philox_uniform(P.seed, P.env_offset + (uint64_t)env, step0);
         CFX_WAITW(H_FULL, tcnt & 1, W_H_FULL);
-        if (tl_on) TLB(10, 0xE0000);
+        CFX_MARK(10);
         tc_fence_after_sync();
         if (wg == 0) {
             uint32_t hv[kHeadCols];
@@ -1180,11 +1127,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) arrive_mma(H_EMPTY);
-#ifdef CFX_ABL_NOSAMPLER
-            if (valid && hv[0] == 0x7fc12345u) {
-#else
             if (valid) {
-#endif
                 float logits[kA];
 #pragma unroll
                 for (int a = 0; a < kA; a++) logits[a] = __uint_as_float(hv[a]) + bias[kH + a];
@@ -1213,10 +1156,10 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 if (P.logprobs) P.logprobs[env] = lp;
                 if (P.values) P.values[env] = value;
             }
-            if (tl_on) TLB(11, 0xF0000);
+            CFX_MARK(11);
         }
     }
-    if (tl_on) TL_FLUSH();
+    CFX_MARK_FLUSH();
 }
 
 // ------------------------------------------------------------------ kernel
@@ -1235,9 +1178,6 @@ k_policy_fused(const __grid_constant__ Params P) {
     sm.base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     sm.template layout<PAIR, GAME, HID>();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef CFX_PROFILE
-    const uint64_t pf_entry = global_timer_ns();
-#endif
     const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
     // arrivals per phase on the barriers the MMA thread waits on: both CTAs' workers in a pair
     const uint32_t both = (PAIR && rank == 0) ? 2u : 1u;
@@ -1294,9 +1234,6 @@ k_policy_fused(const __grid_constant__ Params P) {
     tc_fence_after_sync();
     const uint32_t tmem = *sm.tmem_base();
     const uint32_t bar0_cta0 = PAIR ? map_to_cta(sm.bar(0), 0u) : 0u;
-#ifdef CFX_PROFILE
-    const uint64_t pf_roles = global_timer_ns();
-#endif
 
     if (warp == 0) {
         if (lane < C::kWLanes) role_weight_loads<PAIR, GAME, HID>(sm, P, lane, rank, bar0_cta0);
@@ -1316,12 +1253,6 @@ k_policy_fused(const __grid_constant__ Params P) {
     tc_fence_before_sync();
     if (PAIR) cluster_sync_all();
     else __syncthreads();
-#ifdef CFX_PROFILE
-    if (tid == 0 && P.timeline != nullptr && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) {
-        long long* t = P.timeline + 4 * 4096 + (blockIdx.x == 0 ? 0 : 8);
-        t[0] = (long long)pf_entry; t[1] = (long long)pf_roles; t[2] = (long long)global_timer_ns();
-    }
-#endif
     const uint32_t aborted = *sm.abort_flag();
     if (aborted != 0) {
         if (tid == 0) atomicCAS(P.status, 0u, aborted | ((uint32_t)blockIdx.x << 8));
@@ -1394,7 +1325,6 @@ struct FusedPlan {
     int sm_count = 0;
     int pair = 0;        // 1: launch as clusters of two CTAs (cta_group::2 MMAs)
     int max_pairs = 0;   // co-resident clusters of two
-    long long* timeline = nullptr;
 };
 
 bool fused_supported(int H, int L, int A, int precision, int game) {
@@ -1581,7 +1511,6 @@ int fused_forward(FusedPlan* p, const FusedArgs& a, cudaStream_t st, int* launch
     P.off_b_enc = o.b_enc;
     P.off_b_a = o.b_a;
     P.off_b_v = o.b_v;
-    P.timeline = p->timeline;
     int smem = 0;
     const void* kern = fused_kernel(p->precision, p->pair, p->game, p->H, &smem);
     void* kargs[1] = {(void*)&P};
@@ -1616,24 +1545,9 @@ int fused_check_status(FusedPlan* p, cudaStream_t st, unsigned* status) {
     return CFX_OK;
 }
 
-#ifdef CFX_TIMELINE
-// Debug builds: (re)arms the timeline log and copies it out (8 roles x 4096 words).
-extern "C" int cfx_debug_timeline(FusedPlan* p, long long* host_out, int arm) {
-    const size_t bytes = 8 * 4096 * sizeof(long long);
-    if (arm) {
-        if (!p->timeline) CFX_CUDA(cudaMalloc((void**)&p->timeline, bytes));
-        CFX_CUDA(cudaMemset(p->timeline, 0, bytes));
-        return CFX_OK;
-    }
-    if (!p->timeline) return CFX_ERR_INVALID;
-    CFX_CUDA(cudaMemcpy(host_out, p->timeline, bytes, cudaMemcpyDeviceToHost));
-    return CFX_OK;
-}
-#endif
 
 void fused_destroy(FusedPlan* p) {
     if (!p) return;
-    if (p->timeline) cudaFree(p->timeline);
     if (p->image) cudaFree(p->image);
     if (p->status) cudaFree(p->status);
     delete p;

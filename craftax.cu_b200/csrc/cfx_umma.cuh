@@ -98,18 +98,6 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred P;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, P;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(ns)
-        : "memory");
-    return ok != 0;
-}
-
 // Bounded wait: spins on try_wait; after kWaitLimitNs without completion (or as soon as
 // another thread of the CTA has given up) it records `code` in *abort_flag (shared
 // memory) and returns false.  Callers then skip their work and fall through to the
@@ -124,11 +112,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
     uint64_t t0 = 0;
     uint32_t spins = 0;
     while (true) {
-#ifdef CFX_WAIT_HINT
-        if (mbar_try_wait_hint(bar, parity, CFX_WAIT_HINT)) return true;
-#else
         if (mbar_try_wait(bar, parity)) return true;
-#endif
         __nanosleep(100);   // back off between probes: 1 % faster kernel than polling flat out
         // the timer and the abort flag are looked at only every 4096 failed polls: reading
         // %globaltimer costs a few hundred ns and must stay off the normal path
