@@ -281,10 +281,12 @@ def run_cfx(args):
         roof = {"bound": "tensor", "achieved": n * flops / (kernel_ms * 1e-3) / 1e12,
                 "peak": tensor_peak, "unit": "TFLOP/s"}
     roof["frac"] = roof["achieved"] / roof["peak"]
-    # DRAM bytes per launch: per-env figure of the committed ncu captures (fp16, L = 2: hidden
-    # 256 at 65,536 envs, hidden 128 at 131,072 envs), scaled by envs; only quoted for those
+    # DRAM bytes of one launch (dram__bytes_read.sum + dram__bytes_write.sum of the committed
+    # ncu captures): hidden 256 was captured at this very size (262,144 envs); hidden 128 at
+    # 131,072 envs and is scaled by envs.  Other shapes have no capture and report null.
     per_env = NCU_DRAM_BYTES_PER_ENV.get((H, L)) if prec in ("f16", "bf16") else None
     roof["traffic"] = per_env * n if per_env is not None else None
+    roof["traffic_source"] = NCU_DRAM_SOURCE.get((H, L)) if per_env is not None else None
     roof["peak_source"] = peaks["source"]
     roof["fused_roofline_ms"] = max(t_hbm, t_tensor) * 1e3
     roof["fused_roofline_frac"] = max(t_hbm, t_tensor) * 1e3 / kernel_ms
@@ -649,7 +651,9 @@ def main():
 
 DEFAULT_PRECISION = "f16"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, per env (ncu captures in profiles/)
-NCU_DRAM_BYTES_PER_ENV = {(256, 2): (208.01e6 + 92.44e6) / 65536, (128, 2): (265.93e6 + 109.67e6) / 131072}
+NCU_DRAM_BYTES_PER_ENV = {(256, 2): (842.75e6 + 529.81e6) / 262144, (128, 2): (265.93e6 + 109.67e6) / 131072}
+NCU_DRAM_SOURCE = {(256, 2): "ncu capture of one launch at 262,144 envs",
+                   (128, 2): "ncu capture at 131,072 envs, scaled by envs (part of the writes was still in L2)"}
 
 if __name__ == "__main__":
     main()

@@ -82,7 +82,10 @@ template <> struct Gm<CFX_GAME_CLASSIC> {
 
 constexpr int kNBMax = 8;        // weight ring slots (one stage each): see Cfg
 // Ring shapes of the CTA-pair mode
-constexpr int kPairNS = 6;       // state slots of 16 KB; the record ring lives inside them
+// (measured at 262,144 envs, h256x2: four weight slots with four state slots 0.407 ms, three
+// weight slots with six state slots 0.419 ms: the weight ring's depth is what hides the L2
+// round trip of a stage and the odd CTA's forwarding hop)
+constexpr int kPairNS = 4;       // state slots of 16 KB; the record ring lives inside them
 constexpr int kSSlot = 16384, kNSMax = 6;
 constexpr int kRBoxBytes = 32 * 80, kRSlot = 4 * kRBoxBytes, kNRMax = 6;
 constexpr int kAexpSlots = 8;
@@ -137,14 +140,14 @@ enum Bar {
 // Shared memory map (offsets from a 1024-byte aligned base) and the shapes that depend on the
 // launch mode.
 //  one CTA per tile: weight ring 2 x 64 KB (whole two-block stages), state ring 4 x 16 KB;
-//  CTA pair (cta_group::2): every CTA stages half of each weight stage, 3 x 32 KB, and has a
-//    state ring of 6 x 16 KB.
+//  CTA pair (cta_group::2): every CTA stages half of each weight stage, 4 x 32 KB, state ring
+//    4 x 16 KB.
 //  In both modes the record ring (one 10 KB slot per state slot) lives INSIDE the state slots:
 //  records are needed only while the encoder runs, state boxes only while the gate layers run;
 //  REC_DONE and S_DONE order the two uses per tile.
 template <bool PAIR, int GAME, int HID> struct Cfg {
     static constexpr int kH = HID, kStateItems = Hd<HID>::kStateItems;
-    static constexpr int kNB = PAIR ? 3 : 2;             // stages of two blocks (96 / 128 KB of weights in flight)
+    static constexpr int kNB = PAIR ? 4 : 2;             // stages of two blocks (128 KB of weights in flight)
     static constexpr int kBSlot = PAIR ? 32768 : 65536;
     static constexpr int kWLanes = kNB;                  // one lane per slot
     static constexpr int kHeadRows = PAIR ? Gm<GAME>::kHeadPair : Gm<GAME>::kHeadSingle;   // N of the head MMA

@@ -454,8 +454,13 @@ int refcu_lockstep(int n, int steps, unsigned long long seed, const float* host_
                    int sync_state, double* out) {
     CuVec v; CuPolicy p;
     cu_vec_init(&v, n, seed);
+    /* The first cu_ensure_blas() call reads CF_GEMM_BF16 from the environment (bf16 when it is
+     * unset, :11309-11310) and would undo a mode chosen before it: initialise first, then
+     * select the fp32 pipeline, and again after cu_policy_init (whose auto-gate may change it). */
+    cu_ensure_blas();
     g_gemm_bf16 = 0;
     cu_policy_init(&p, n);   /* record row, sampler outputs; also the reference fp32 pipeline */
+    g_gemm_bf16 = 0;
     refcu_h2d(p.params, host_arena, (size_t)CF_NN_PARAM_COUNT * sizeof(float));
     cu_params_refresh_bf16(&p, p.stream);
     cu_pack_wav(&p, p.stream);
