@@ -182,6 +182,9 @@ enum WaitCode : uint32_t {
 
 struct Params {
     CUtensorMap rec_map;                 // uint8 [n/4][3984], box 32 x 80
+    // pair mode: the operand image as [rows][64] 16-bit tensors, one map per region (encoder,
+    // gate layers, heads); a box is the part of a stage that one CTA of the pair copies
+    CUtensorMap w_map[3];
     CUtensorMap state_map[kMaxLayers];   // fp32 [n][256] per layer, box 128 x 32, SWIZZLE_128B
     const uint8_t* records;              // [n][996], for the L2 prefetch of the next tile
     const float* state;                  // [L][n][256]
@@ -290,7 +293,9 @@ __global__ void k_pack_image(const float* __restrict__ params, uint8_t* __restri
         const int kb = kStageBlocks * (s % kPairsPerSlice) + q.blk, j = (s / kPairsPerSlice) % kSlices,
                   l = s / (kPairsPerSlice * kSlices);
         const int gate = q.row / kSliceUnits, unit = j * kSliceUnits + q.row % kSliceUnits;
-        v = params[off_w_gru + ((size_t)l * 3 * kH + gate * kH + unit) * kH + kb * 64 + q.c];
+        // gate weights are stored halved: the accumulator then holds z / 2, the argument of the
+        // cell's tanh (a power-of-two scale is exact for every weight above the subnormal range)
+        v = 0.5f * params[off_w_gru + ((size_t)l * 3 * kH + gate * kH + unit) * kH + kb * 64 + q.c];
         *reinterpret_cast<T16*>(image + enc_b + (size_t)s * kGateStageBytes + q.dst) = to16<T16>(v);
         return;
     } else {
@@ -362,28 +367,20 @@ struct Op16<__nv_bfloat16> {
     }
 };
 
+// MinGRU cell (k_mingru_epi_fwd, craftax_full.cu:9377-9381) with
+// sigmoid(z) = 0.5 + 0.5 tanh(z/2) on the SFU and g(z) - 0.5 = max(z, 0.5 tanh(z/2))
+// (equal to z for z >= 0 and to sigmoid(z) - 0.5 for z < 0).  The arguments are the HALVED
+// pre-activations zh/2, zg/2, zp/2, which is what the gate MMAs produce (the operand image
+// holds the gate weights times 0.5), so the cell starts with the tanh.
 __device__ __forceinline__ float tanh_fast(float x) {
     float y;
     asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
 
-// MinGRU cell (k_mingru_epi_fwd, craftax_full.cu:9377-9381) with
-// sigmoid(z) = 0.5 + 0.5 tanh(z/2) on the SFU and g(z) - 0.5 = max(z, 0.5 tanh(z/2))
-// (equal to z for z >= 0 and to sigmoid(z) - 0.5 for z < 0).
-__device__ __forceinline__ void mingru_cell(float zh, float zg, float zp, float st, float x,
-                                            float& out, float& h) {
-    const float th = tanh_fast(0.5f * zh), tg = tanh_fast(0.5f * zg), tp = tanh_fast(0.5f * zp);
-    const float sg = fmaf(tg, 0.5f, 0.5f), p = fmaf(tp, 0.5f, 0.5f);
-    const float gh = 0.5f + fmaxf(zh, 0.5f * th);
-    out = fmaf(sg, gh - st, st);
-    h = fmaf(p, out - x, x);
-}
-
-// The same cell for two units at once with the packed fp32 instructions of sm_100
-// (`fma.rn.f32x2` and friends: two results per issue slot, the same roundings as the scalar
-// forms, so the results are bit-identical to mingru_cell).  The cell phase is bound by
-// instruction issue (two worker warps per scheduler), not by the FMA or SFU pipes.
+// Two units at once with the packed fp32 instructions of sm_100 (`fma.rn.f32x2` and friends:
+// two results per issue slot, the same roundings as the scalar forms).  The cell phase is
+// bound by instruction issue and latency (two worker warps per scheduler), not by the FMA pipe.
 __device__ __forceinline__ uint64_t f2pack(float a, float b) {
     uint64_t r;
     asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
@@ -397,11 +394,6 @@ __device__ __forceinline__ uint64_t f2mul(uint64_t a, uint64_t b) {
     asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
     return r;
 }
-__device__ __forceinline__ uint64_t f2add(uint64_t a, uint64_t b) {
-    uint64_t r;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
 __device__ __forceinline__ uint64_t f2sub(uint64_t a, uint64_t b) {
     uint64_t r;
     asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
@@ -412,22 +404,20 @@ __device__ __forceinline__ uint64_t f2fma(uint64_t a, uint64_t b, uint64_t c) {
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
     return r;
 }
-__device__ __forceinline__ void mingru_cell_pair(float zh0, float zh1, float zg0, float zg1, float zp0,
-                                                 float zp1, float st0, float st1, float x0, float x1,
+// hzh, hzg, hzp: zh/2, zg/2, zp/2 of two units
+__device__ __forceinline__ void mingru_cell_pair(float hzh0, float hzh1, float hzg0, float hzg1, float hzp0,
+                                                 float hzp1, float st0, float st1, float x0, float x1,
                                                  float& out0, float& out1, float& h0, float& h1) {
-    const uint64_t half2 = f2pack(0.5f, 0.5f);
-    const uint64_t zh = f2pack(zh0, zh1), st = f2pack(st0, st1), x = f2pack(x0, x1);
-    float a0, a1, b0, b1, c0, c1;
-    f2unpack(f2mul(zh, half2), a0, a1);
-    f2unpack(f2mul(f2pack(zg0, zg1), half2), b0, b1);
-    f2unpack(f2mul(f2pack(zp0, zp1), half2), c0, c1);
-    const uint64_t th = f2pack(tanh_fast(a0), tanh_fast(a1));
-    const uint64_t tg = f2pack(tanh_fast(b0), tanh_fast(b1));
-    const uint64_t tp = f2pack(tanh_fast(c0), tanh_fast(c1));
+    const uint64_t half2 = f2pack(0.5f, 0.5f), quarter2 = f2pack(0.25f, 0.25f), two2 = f2pack(2.0f, 2.0f);
+    const uint64_t st = f2pack(st0, st1), x = f2pack(x0, x1);
+    const uint64_t th = f2pack(tanh_fast(hzh0), tanh_fast(hzh1));
+    const uint64_t tg = f2pack(tanh_fast(hzg0), tanh_fast(hzg1));
+    const uint64_t tp = f2pack(tanh_fast(hzp0), tanh_fast(hzp1));
     const uint64_t sg = f2fma(tg, half2, half2), p = f2fma(tp, half2, half2);
+    // g(zh) = 0.5 + max(zh, 0.5 th) = 0.5 + 2 max(zh/2, 0.25 th): every step is exact
     float m0, m1;
-    f2unpack(f2mul(th, half2), m0, m1);
-    const uint64_t gh = f2add(half2, f2pack(fmaxf(zh0, m0), fmaxf(zh1, m1)));
+    f2unpack(f2mul(th, quarter2), m0, m1);
+    const uint64_t gh = f2fma(two2, f2pack(fmaxf(hzh0, m0), fmaxf(hzh1, m1)), half2);
     const uint64_t out = f2fma(sg, f2sub(gh, st), st);
     const uint64_t h = f2fma(p, f2sub(out, x), x);
     f2unpack(out, out0, out1);
@@ -539,8 +529,8 @@ __device__ __forceinline__ void l2_prefetch_for_box(const Params& P, int tile, i
 // Weight stages: the image is laid out in consumption order, so stage s of a tile starts
 // where stage s-1 ended; every tile replays the same sequence (it stays L2 resident).
 // One lane per ring slot.  In a CTA pair every CTA stages its own half of the rows of each
-// stage (contiguous in the image); the odd CTA waits for its copy to land and then arrives on
-// the even CTA's "full" barrier, where the MMA thread waits.
+// stage (contiguous in the image) with a tensor copy whose completion is counted on the even
+// CTA's "full" barrier, where the MMA thread waits; one CTA per tile uses plain bulk copies.
 template <bool PAIR, int GAME, int HID>
 __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& P, int lane,
                                                   uint32_t rank, uint32_t bar0_cta0) {
@@ -569,17 +559,22 @@ __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& 
             bytes = head_bytes<GAME, HID>(PAIR);
             off = enc_bytes + (size_t)stages_gate * kGateStageBytes;
         }
-        if (PAIR) {
-            bytes >>= 1;
-            off += (size_t)rank * bytes;
-        }
         CFX_WAIT(B_EMPTY + lane, (use & 1) ^ 1, W_B_EMPTY);
-        mbar_arrive_expect_tx(sm.bar(B_FULL + lane), bytes);
-        bulk_g2s(smem_u32(sm.b_ring() + lane * C::kBSlot), P.image + off, bytes, sm.bar(B_FULL + lane));
-        if (PAIR && rank != 0) {
-            // local barrier (one arrival per phase here): wait for the copy, tell the even CTA
-            CFX_WAIT(B_FULL + lane, use & 1, W_B_FULL);
-            mbar_arrive_cluster(bar0_cta0 + 8u * (uint32_t)(B_FULL + lane));
+        const uint32_t dst = smem_u32(sm.b_ring() + lane * C::kBSlot);
+        if (PAIR) {
+            // Each CTA copies its half of the stage into its own shared memory; both copies are
+            // counted on the EVEN CTA's "full" barrier (where the MMA thread waits), which
+            // expects the bytes of the whole stage.  The odd CTA needs no barrier of its own
+            // and no forwarding hop.
+            const int region = s < kEncStages ? 0 : (s < kEncStages + stages_gate ? 1 : 2);
+            const size_t base = region == 0 ? 0 : (region == 1 ? enc_bytes : enc_bytes + (size_t)stages_gate * kGateStageBytes);
+            const uint32_t half = bytes >> 1;
+            const int y = (int)((off - base + (size_t)rank * half) >> 7);   // rows of 128 bytes
+            if (rank == 0) mbar_arrive_expect_tx(sm.bar(B_FULL + lane), bytes);
+            tensor_g2s_2d_pair(dst, &P.w_map[region], 0, y, bar0_cta0 + 8u * (uint32_t)(B_FULL + lane));
+        } else {
+            mbar_arrive_expect_tx(sm.bar(B_FULL + lane), bytes);
+            bulk_g2s(dst, P.image + off, bytes, sm.bar(B_FULL + lane));
         }
         s += C::kNB;
         normalise();
@@ -819,21 +814,22 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
         // ---- heads: N = 48 (64 in a pair), one stage with all K blocks
         {
             const uint32_t a_cur = tmem + ((P.L & 1) ? kColA1 : kColA0);
-#pragma unroll
-            for (int kb = 0; kb < kKBlocks; kb++) CFX_WAIT_LEADER(A_KB + kb, akb_use & 1, W_A_KB);
-            akb_use++;
             const int slot = bslot;
             CFX_WAIT_PROBED(b_ready, B_FULL + slot, bpar, W_B_FULL);
-            tc_fence_after_sync();
             b_advance();
             const uint64_t bd = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
+            // K block kb of the last layer's output is complete when slice kb's cells are done
 #pragma unroll
-            for (int kb = 0; kb < kKBlocks; kb++)
+            for (int kb = 0; kb < kKBlocks; kb++) {
+                CFX_WAIT_LEADER(A_KB + kb, akb_use & 1, W_A_KB);
+                tc_fence_after_sync();
 #pragma unroll
                 for (int ks = 0; ks < 4; ks++)
                     MMA_TS(tmem + kColHead, a_cur + kb * 32 + ks * 8,
                            bd + (uint64_t)((kb * C::kHeadKbBytes + ks * 32) >> 4), idesc_head,
                            (kb | ks) != 0 ? 1u : 0u);
+            }
+            akb_use++;
             MMA_COMMIT(sm.bar(B_EMPTY + slot));
             MMA_COMMIT(sm.bar(H_FULL));
             CFX_MARK(8);
@@ -1189,7 +1185,7 @@ k_policy_fused(const __grid_constant__ Params P) {
         auto init = [&](int first, int count, uint32_t arrivals) {
             for (int i = 0; i < count; i++) mbar_init(sm.bar(first + i), arrivals);
         };
-        init(B_FULL, C::kNB, both);
+        init(B_FULL, C::kNB, 1);   // pair: the even CTA's barrier also counts the odd CTA's bytes
         init(B_EMPTY, C::kNB, 1);
         init(S_FULL, C::kNS, 1);
         init(S_DONE, C::kNS, 1);
@@ -1325,6 +1321,7 @@ struct FusedPlan {
     float* state = nullptr;
     const float* params = nullptr;
     CUtensorMap state_map[fused::kMaxLayers];
+    CUtensorMap w_map[3];          // pair mode: operand image regions (encoder, gates, heads)
     int sm_count = 0;
     int pair = 0;        // 1: launch as clusters of two CTAs (cta_group::2 MMAs)
     int max_pairs = 0;   // co-resident clusters of two
@@ -1434,6 +1431,30 @@ int fused_create(FusedPlan** out, int device, int n, int H, int L, int A, int pr
             cudaGetLastError();
         }
     }
+    memset(p->w_map, 0, sizeof(p->w_map));
+    if (p->pair) {
+        // The operand image seen as rows of 64 16-bit values (128 bytes), one tensor per region;
+        // a box is what ONE CTA of a pair copies of a stage: half of a two-chunk encoder stage,
+        // half of a two-K-block gate stage, half of the head stage.  The image is already
+        // swizzled, so the copies are not.
+        const bool classic = game == CFX_GAME_CLASSIC;
+        const int kblocks = H / 64;
+        const int enc_chunks = classic ? fused::Gm<CFX_GAME_CLASSIC>::kEncChunks : fused::Gm<CFX_GAME_FULL>::kEncChunks;
+        const int head_pair = classic ? fused::Gm<CFX_GAME_CLASSIC>::kHeadPair : fused::Gm<CFX_GAME_FULL>::kHeadPair;
+        const uint64_t rows[3] = {(uint64_t)enc_chunks * H, (uint64_t)L * (H / 64) * kblocks * 192,
+                                  (uint64_t)kblocks * head_pair};
+        const uint32_t box[3] = {(uint32_t)H, 192u, (uint32_t)(kblocks * head_pair / 2)};
+        uint8_t* base = p->image;
+        for (int r = 0; r < 3; r++) {
+            if (!make_tmap_2d(&p->w_map[r], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, base, rows[r], 64, 128, box[r], 64,
+                              CU_TENSOR_MAP_SWIZZLE_NONE)) {
+                fused_destroy(p);
+                set_error("fused_create: cuTensorMapEncodeTiled failed for the operand image");
+                return CFX_ERR_CUDA;
+            }
+            base += rows[r] * 128;
+        }
+    }
     *out = p;
     return CFX_OK;
 }
@@ -1477,6 +1498,7 @@ int fused_forward(FusedPlan* p, const FusedArgs& a, cudaStream_t st, int* launch
         return CFX_ERR_CUDA;
     }
     for (int l = 0; l < p->L; l++) P.state_map[l] = p->state_map[l];
+    for (int r = 0; r < 3; r++) P.w_map[r] = p->w_map[r];
     const ArenaLayout o = ArenaLayout::make(p->H, p->L, p->A, classic ? kClassicObs : kObs);
     P.records = a.records;
     P.rec_bytes = classic ? kClassicRec : kRec;

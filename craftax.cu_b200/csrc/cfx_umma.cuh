@@ -189,6 +189,17 @@ __device__ __forceinline__ void tensor_g2s_2d(uint32_t dst_smem, const CUtensorM
         "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
+// The same copy issued by a CTA of a pair (cta_group::2): the data lands in the issuing CTA's
+// shared memory, the completion (complete_tx) may be counted on an mbarrier of EITHER CTA of
+// the pair; `cluster_bar` is a shared::cluster address (mapa).  No multicast.
+__device__ __forceinline__ void tensor_g2s_2d_pair(uint32_t dst_smem, const CUtensorMap* map, int x,
+                                                   int y, uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2 "
+        "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst_smem),
+        "l"(map), "r"(x), "r"(y), "r"(cluster_bar)
+        : "memory");
+}
 // 2-D tiled tensor copy shared -> global (bulk async-group completion).
 __device__ __forceinline__ void tensor_s2g_2d(const CUtensorMap* map, uint32_t src_smem, int x,
                                               int y) {
