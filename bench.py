@@ -466,17 +466,23 @@ def run_ref_cublas(args):
 
 
 def run_sweep(args):
-    """Synthetic fused-forward sweep on one GPU: batch x hidden {128, 256} x MinGRU depth x
-    operand type (the instantiations built), one JSON line per point with the fused-roofline
-    fraction.  Points of the published sweep that are not built (hidden 512, tf32 operands) are
-    listed once as unavailable."""
+    """Synthetic fused-forward sweep: batch x hidden {128, 256} x MinGRU depth x operand type
+    (the instantiations built), one JSON line per point with the fused-roofline fraction.  Under
+    torchrun every rank sweeps its own GPU with its own env slice (`--envs`-independent: the batch
+    sizes are per GPU) and a point's time is the max over ranks.  Points of the published sweep
+    that are not built (hidden 512, tf32 operands) are listed once as unavailable, with the reason."""
     import cfx
     from cfx.synth import synthetic_records, init_weights
-    rank, _, local = dist_env()
-    if rank != 0:
-        return
+    from cfx.sharding import max_over_ranks
+    rank, world, local = dist_env()
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     peaks = load_peaks()
-    base = synthetic_records(8192, seed=4)
+    base = synthetic_records(8192, seed=4 + rank)
     for n in (8192, 65536, 262144, 1048576, 2097152):
         rec = np.tile(base, (n // 8192, 1))
         d_rec = cfx.DeviceBuffer.from_host(rec, local)
@@ -487,26 +493,40 @@ def run_sweep(args):
             pol = cfx.Policy(n, H, L, A, prec, device=local)
             pol.set_weights(init_weights(H, L, A, seed=0))
             for _ in range(3):
-                pol.forward_device(d_rec, None, None, actions=d_act, logits_av=d_lav, seed=1, bump_step=True)
+                pol.forward_device(d_rec, None, None, actions=d_act, logits_av=d_lav, seed=1,
+                                   env_offset=rank * n, bump_step=True)
             pol.check()
             steps = 20 if n <= 262144 else 8
+            if dist is not None:
+                import torch
+                dist.barrier()
+                torch.cuda.synchronize()
             t = cfx.Timer(local)
             t.start(pol.stream)
             for _ in range(steps):
-                pol.forward_device(d_rec, None, None, actions=d_act, logits_av=d_lav, seed=1, bump_step=True)
+                pol.forward_device(d_rec, None, None, actions=d_act, logits_av=d_lav, seed=1,
+                                   env_offset=rank * n, bump_step=True)
             t.stop(pol.stream)
             pol.check()
-            ms = t.elapsed_ms() / steps
+            ms = max_over_ranks([t.elapsed_ms() / steps], dist)[0]
             flops, byts = algorithmic_work(H, L)
             t_roof = max(n * byts / (peaks["hbm_gbs"] * 1e9), n * flops / (peaks["bf16_tflops"] * 1e12))
-            print(json.dumps({"sweep": "fused forward", "envs": n, "hidden": H, "layers": L,
-                              "operands": prec, "ms_per_step": ms, "env_steps_per_s": n / (ms * 1e-3),
-                              "fused_roofline_ms": t_roof * 1e3, "fused_roofline_frac": t_roof * 1e3 / ms,
-                              "peak_source": peaks["source"]}), flush=True)
+            if rank == 0:
+                print(json.dumps({"sweep": "fused forward", "n_gpus": world, "envs_per_gpu": n, "hidden": H,
+                                  "layers": L, "operands": prec, "ms_per_step": ms,
+                                  "env_steps_per_s": world * n / (ms * 1e-3),
+                                  "fused_roofline_ms": t_roof * 1e3, "fused_roofline_frac": t_roof * 1e3 / ms,
+                                  "peak_source": peaks["source"]}), flush=True)
             pol.close()
         d_rec.free(); d_act.free(); d_lav.free()
-    print(json.dumps({"sweep": "fused forward", "unavailable":
-                      "hidden 512 and tf32 operands are not instantiated in this library"}), flush=True)
+    if rank == 0:
+        print(json.dumps({"sweep": "fused forward", "unavailable": {
+            "hidden 512": "the 16-bit input and output of a 512-wide layer fill all 512 tensor-memory columns of a "
+                          "128-env tile, leaving none for the accumulators",
+            "tf32 operands": "fp32 activations of K = 256 take 256 tensor-memory columns per buffer; fp16 operands "
+                             "carry the same 11-bit significand"}}), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
 
 
 def run_classic(args):
@@ -651,7 +671,7 @@ def main():
 
 DEFAULT_PRECISION = "f16"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, per env (ncu captures in profiles/)
-NCU_DRAM_BYTES_PER_ENV = {(256, 2): (842.75e6 + 529.81e6) / 262144, (128, 2): (265.93e6 + 109.67e6) / 131072}
+NCU_DRAM_BYTES_PER_ENV = {(256, 2): (838.98e6 + 530.04e6) / 262144, (128, 2): (265.94e6 + 109.82e6) / 131072}
 NCU_DRAM_SOURCE = {(256, 2): "ncu capture of one launch at 262,144 envs",
                    (128, 2): "ncu capture at 131,072 envs, scaled by envs (part of the writes was still in L2)"}
 
