@@ -597,7 +597,7 @@ def run_classic(args):
 def run_ref_rollout(args):
     """Whole rollouts on one B200: the reference's own `run` loop (env kernels + its cuBLAS
     policy, graph replay), its env kernels alone, and the same loop with the policy half
-    swapped for this library's forward (the drop-in binding of INTEGRATION.md).  The three
+    swapped for this library's forward (the drop-in binding a maintainer would add).  The three
     ratios of the target sentence are printed: R1 forward-only vs forward-only comes from
     `--impl cfx` and `--impl ref-cublas`; R2 = this library's forward-only env-steps/s over the
     reference's full-rollout SPS; R3 = swapped rollout over reference rollout."""

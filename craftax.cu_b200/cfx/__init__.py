@@ -12,7 +12,7 @@ import os
 import numpy as np
 
 PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-# CFX_LIB names another build of the same library (documented in README.md)
+# CFX_LIB (environment) names another build of the same library, e.g. a debug build
 LIB_PATH = os.environ.get("CFX_LIB") or os.path.join(PKG, "libcfx.so")
 
 OBS, MAP, TAIL, REC = 843, 792, 51, 996
