@@ -123,7 +123,7 @@ def test_classic_fused_matches_oracle(cfx, gpu, oracle, prec, n):
     assert err < tol
     assert np.abs(pol.get_state() - want_st).max() < tol
     if prec == "f16":
-        assert agree >= 0.99
+        assert agree >= 0.995
     a, lp = cfx.sample_actions(d["logits_av"], u, num_actions=A)
     assert np.array_equal(a, d["actions"])
     assert np.array_equal(lp.view(np.uint32), d["logprobs"].view(np.uint32))

@@ -98,7 +98,7 @@ def test_classic_large_batch_properties(cfx, gpu, oracle):
     agree = float((d16["logits_av"][:, :actions].argmax(1) == d32["logits_av"][:, :actions].argmax(1)).mean())
     print(f"[classic 262144 envs] max|dlogit|={err:.3e} greedy={agree:.5f}")
     assert err < 2e-2
-    assert agree >= 0.99
+    assert agree >= 0.995
     assert np.abs(st16 - st32).max() < 2e-2
     parts = [run("f16", 0, n // 2), run("f16", n // 2, n)]
     for key in ("logits_av", "actions", "logprobs", "values"):
