@@ -307,6 +307,23 @@ class RefCuda:
             raise RuntimeError("refcu_lockstep: a cfx call failed (see stderr)")
         return dict(zip(cls.LOCKSTEP_KEYS, out.tolist()))
 
+    @classmethod
+    def play(cls, layers, n, steps, seed, load_path, swapped, precision, record_n, record_every,
+             frames_path, levels_path):
+        """The reference's `play` loop (cu_run_play) and its recorders; swapped != 0 takes the
+        policy half of every step from libcfx (which must be loaded first).  Returns the
+        frame size in bytes and the byte offset of the action field inside a frame."""
+        L = C.CDLL(cls.path(layers))
+        if not hasattr(L, "refcu_play"):
+            raise RuntimeError("reference shim built without the play loop")
+        L.refcu_play.argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_char_p, C.c_int, C.c_int, C.c_int,
+                                 C.c_int, C.c_int, C.c_char_p, C.c_char_p]
+        rc = L.refcu_play(n, steps, seed, os.fsencode(load_path), 1 if swapped else 0, precision, -1,
+                          record_n, record_every, os.fsencode(frames_path), os.fsencode(levels_path))
+        if rc != 0:
+            raise RuntimeError("refcu_play failed (see stderr)")
+        return int(L.refcu_frame_bytes()), int(L.refcu_frame_action_offset())
+
     def set_weights(self, params):
         p = np.ascontiguousarray(params, np.float32)
         assert p.size == self.L.refcu_param_count()

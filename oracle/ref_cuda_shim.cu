@@ -18,6 +18,7 @@
  * on the same GPU, and timing the reference's cuBLAS pipeline beside ours.
  */
 #define CRAFTAX_CU_LIB 1
+#include <stddef.h>
 #include CFX_REF_CU
 
 enum { REFCU_BF16 = 0, REFCU_TF32 = 1, REFCU_FP32 = 2 };
@@ -411,6 +412,76 @@ double refcu_rollout_swap_sps(int n, int iters, unsigned long long seed, int gra
     cu_vec_free(&v);
     return sps;
 }
+/* ---- the reference's `play` mode on the new handle ----
+ * cu_run_play (:12383-12447) replays a trained policy and writes, per step, one level/done byte
+ * per env (k_dump_levels) and the frames of the recorded envs (k_record_frames, CfFrame
+ * :12296-12309) for its offline renderer.  refcu_play runs the same loop with the same,
+ * unmodified recorders and the same file formats; swapped = 0 calls cu_run_play itself,
+ * swapped = 1 takes the step from refcu_step_swapped (policy half = cfx_policy_forward at
+ * `precision`) with the weights loaded from the same CFW1 file by cfx_policy_load_cfw1. */
+int refcu_frame_bytes(void) { return (int)sizeof(CfFrame); }
+int refcu_frame_action_offset(void) { return (int)offsetof(CfFrame, action); }
+
+int refcu_play(int n, int steps, unsigned long long seed, const char* load_path, int swapped, int precision,
+               int record_env, int record_n, int record_every, const char* frames_path,
+               const char* levels_path) {
+    if (!swapped)
+        return cu_run_play(n, steps, seed, load_path, record_env, record_n, record_every, frames_path, levels_path);
+    if (record_every < 1) record_every = 1;
+    CuVec v; CuPolicy p;
+    cu_vec_init(&v, n, seed);
+    cu_policy_init(&p, n);   /* record row and sampler outputs of the loop */
+    int dev = 0;
+    CU_CHECK(cudaGetDevice(&dev));
+    cfx_policy* cp = NULL;
+    if (cfx_policy_create(&cp, dev, n, CF_NN_HIDDEN, CF_NN_LAYERS, CRAFTAX_NUM_ACTIONS, precision) != CFX_OK ||
+        cfx_policy_load_cfw1(cp, load_path) != CFX_OK) {
+        fprintf(stderr, "cfx: %s\n", cfx_last_error());
+        return 1;
+    }
+    int rec0 = 0, recn = 0;
+    if (record_n > 0) recn = record_n < n ? record_n : n;
+    else if (record_env >= 0 && record_env < n) { rec0 = record_env; recn = 1; }
+    FILE* ff = (frames_path && recn) ? fopen(frames_path, "wb") : NULL;
+    FILE* lf = levels_path ? fopen(levels_path, "wb") : NULL;
+    CfFrame* d_frame = NULL;
+    CfFrame* h_frame = NULL;
+    uint8_t* d_lv = NULL;
+    uint8_t* h_lv = (uint8_t*)malloc((size_t)n);
+    if (recn) {
+        CU_CHECK(cudaMalloc(&d_frame, (size_t)recn * sizeof(CfFrame)));
+        h_frame = (CfFrame*)malloc((size_t)recn * sizeof(CfFrame));
+    }
+    CU_CHECK(cudaMalloc(&d_lv, (size_t)n));
+    refcu_roll r = {&v, &p, seed, cp};
+    for (int step = 0; step < steps; step++) {
+        refcu_step_swapped(&r);
+        if (lf) {
+            k_dump_levels<<<(n + 255) / 256, 256, 0, p.stream>>>(v.d_envs, v.d_terminals, n, d_lv);
+            CU_CHECK(cudaMemcpyAsync(h_lv, d_lv, (size_t)n, cudaMemcpyDeviceToHost, p.stream));
+        }
+        int rec_now = ff && step % record_every == 0;
+        if (rec_now) {
+            k_record_frames<<<recn, 256, 0, p.stream>>>(v.d_envs, rec0, p.d_act, v.d_rewards, v.d_terminals,
+                                                        d_frame);
+            CU_CHECK(cudaMemcpyAsync(h_frame, d_frame, (size_t)recn * sizeof(CfFrame), cudaMemcpyDeviceToHost,
+                                     p.stream));
+        }
+        CU_CHECK(cudaStreamSynchronize(p.stream));
+        if (lf) fwrite(h_lv, 1, (size_t)n, lf);
+        if (rec_now) fwrite(h_frame, sizeof(CfFrame), (size_t)recn, ff);
+    }
+    if (ff) fclose(ff);
+    if (lf) fclose(lf);
+    int rc = cfx_policy_check(cp, p.stream) == CFX_OK ? 0 : 1;
+    cudaFree(d_frame); cudaFree(d_lv);
+    free(h_frame); free(h_lv);
+    cfx_policy_destroy(cp);
+    cu_policy_free(&p);
+    cu_vec_free(&v);
+    return rc;
+}
+
 /* ---- lock-step rollout: the reference's CUDA env, driven by this library's forward, with the
  * reference's strict-fp32 cuBLAS pipeline consuming the same records beside it ----
  * Protocol of the reference's runverify (:12501-12507, :12545-12603): the env advances with

@@ -188,3 +188,44 @@ def test_cfw1_files_cross_load_with_the_reference(cfx, oracle, refcu, L, tmp_pat
     other.close()
     pol.close()
     ref.close()
+
+
+def test_play_recording_with_the_forward_swapped_in(cfx, oracle, refcu, tmp_path):
+    """The reference's `play` mode (cu_run_play, craftax_full.cu:12383-12447: replay a policy from
+    a CFW1 file, write one level/done byte per env and step and the CfFrame records of the
+    chosen envs) with the policy half of every step taken from cfx_policy_forward: same
+    recorders, same file formats; two runs with the same seed write identical files (what its
+    --record-env workflow relies on), and the first step's actions agree with the reference's
+    own play run on all but a few envs (fp16 against its default GEMM mode, same Philox draws)."""
+    if not refcu.available(2):
+        pytest.skip("oracle/_ref/libcfref_cuda_l2.so not built")
+    cfx.lib()
+    n, steps, recn, every = 1024, 12, 256, 4
+    pol = cfx.Policy(32, H, L, A, "fp32")
+    pol.init_weights(1234)
+    wfile = str(tmp_path / "w.cfw1")
+    pol.save(wfile)
+    pol.close()
+    out = {}
+    try:
+        for tag, swapped in (("ref", 0), ("cfx1", 1), ("cfx2", 1)):
+            fr, lv = str(tmp_path / f"{tag}.frames"), str(tmp_path / f"{tag}.levels")
+            fb, aoff = refcu.play(L, n, steps, 7, wfile, swapped, cfx.PREC_F16, recn, every, fr, lv)
+            out[tag] = (open(fr, "rb").read(), open(lv, "rb").read())
+    except RuntimeError as e:
+        if "without the play loop" in str(e):
+            pytest.skip(str(e))
+        raise
+    n_rec = (steps + every - 1) // every
+    for tag in out:
+        assert len(out[tag][1]) == n * steps, tag
+        assert len(out[tag][0]) == n_rec * recn * fb, tag
+    assert out["cfx1"] == out["cfx2"]                       # deterministic replay
+    def actions(blob, k):
+        fr = np.frombuffer(blob, np.uint8).reshape(n_rec, recn, fb)[k]
+        return fr[:, aoff:aoff + 4].copy().view(np.int32)[:, 0]
+    a_ref, a_cfx = actions(out["ref"][0], 0), actions(out["cfx1"][0], 0)
+    assert (a_cfx >= 0).all() and (a_cfx < A).all()
+    agree = float((a_ref == a_cfx).mean())
+    print(f"[play] first-step action agreement with the reference's own play run: {agree:.4f}")
+    assert agree >= 0.95
