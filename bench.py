@@ -635,7 +635,7 @@ def run_ref_rollout(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="cfx", choices=["cfx", "reference", "ref-cublas", "ref-rollout", "sweep", "classic"])
     ap.add_argument("--ref-mode", default="bf16", choices=["bf16", "tf32", "fp32"])
