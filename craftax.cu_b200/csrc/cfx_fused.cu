@@ -17,17 +17,19 @@
 //                              the next slice's MMAs while the cell runs)  HEAD [448,512)
 //                  encoder phase: operand-chunk ring [0,256) (8 x 32 columns), accumulator
 //                              [256,512)
-//   shared memory  weight ring | state ring (the record ring lives inside its slots) | tail /
-//                  classic record buffer | biases, barriers: see Cfg
-//   warps          0 weight loads (one lane per slot), 1 MMA issue (one thread) + TMEM alloc,
-//                  2 record loads (one lane per slot + the tail lane), 3 state ring (one lane per
-//                  slot: load, store, and the L2 prefetch), 4..11 workers (expand, cell, sampler)
+//   shared memory  weight ring | state ring (four of the six record slots live inside its slots)
+//                  | two record slots / classic record buffer | biases, barriers: see Cfg
+//   warps          0 weight loads, 1 MMA issue + TMEM alloc, 2 record fills of worker warpgroup 1
+//                  + state box loads + the L2 prefetch, 3 record fills of warpgroup 0 + state
+//                  box stores (one thread each), 4..11 workers (expand, cell, sampler)
 //   launch modes   clusters of two CTAs sharing 256-row MMAs (PAIR, the default) or one CTA per
 //                  tile; full game or classic game (GAME): see Cfg and Gm
 //   hidden size    256 (the figures in this comment) or 128 (HID): two gate slices of two K
 //                  blocks per layer, A0 / A1 of 64 columns, encoder accumulator N = 128: see Hd
 // One round of (mbarrier wait, arrive.expect_tx, bulk copy) costs its issuing thread about
-// 500 cycles on B200, so every copy role gives each ring slot a lane of its own.
+// 500 cycles on B200.  Every copy role is ONE thread that walks its ring in order: the slots of
+// a ring come free in the order they were filled, and several lanes of one warp, each in its own
+// loop, serve their slots far more slowly than one thread serves them all.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -65,29 +67,35 @@ template <int HID> struct Hd {
     (void)kH; (void)kSlices; (void)kStateItems; (void)kKBlocks; (void)kEncCopyBytes
 
 // What differs between the two games the kernel is instantiated for.
-//  full game (craftax_full.cu): 996-byte record = 792 map bytes + 51 raw floats, 843 features
-//    in 14 chunks of 64 (12 full map chunks, one of 24 bytes, one with the 51 floats), records
-//    fetched chunk by chunk through a ring (13 fills; the tail has a buffer of its own), 43 actions;
+//  full game (craftax_full.cu): 996-byte record = 792 map bytes + 51 raw floats, 843 features.
+//    The record goes through the record ring in 16 chunks of 64 RECORD bytes: chunks 0-11 are 64
+//    map bytes each (four K steps), chunk 12 is 24 map bytes and floats 0-9 (three K steps),
+//    chunks 13 and 14 are 16 floats each and chunk 15 the last 9 floats (one K step each).  The
+//    weight image has 14 blocks of 64 K columns: blocks 0-11 belong to chunks 0-11, block 12 to
+//    chunks 12 and 13 (K columns 0-47 and 48-63), block 13 to chunks 14 and 15 (K columns 0-15
+//    and 16-31).  43 actions;
 //  classic game (craftax_classic.cu): 148-byte record, 1345 one-hot / scalar features in 22
-//    chunks, the whole tile's records (18.5 KB) fetched by one TMA box, 17 actions.
+//    chunks (one weight block each), the whole tile's records (18.5 KB) fetched by one TMA box,
+//    17 actions.
 template <int GAME> struct Gm;
 template <> struct Gm<CFX_GAME_FULL> {
-    static constexpr int kA = 43, kEncChunks = 14, kRecFills = 13, kRecBytes = kRec;
+    static constexpr int kA = 43, kEncChunks = 16, kEncBlocks = 14, kRecBytes = kRec;
     static constexpr int kHeadSingle = 48, kHeadPair = 64;   // head MMA N (pairs need N % 32 == 0)
 };
 template <> struct Gm<CFX_GAME_CLASSIC> {
-    static constexpr int kA = 17, kEncChunks = 22, kRecFills = 0, kRecBytes = kClassicRec;
+    static constexpr int kA = 17, kEncChunks = 22, kEncBlocks = 22, kRecBytes = kClassicRec;
     static constexpr int kHeadSingle = 32, kHeadPair = 32;
 };
 
 constexpr int kNBMax = 8;        // weight ring slots (one stage each): see Cfg
-// Ring shapes of the CTA-pair mode
-// (measured at 262,144 envs, h256x2: four weight slots with four state slots 0.407 ms, three
-// weight slots with six state slots 0.419 ms: the weight ring's depth is what hides the L2
-// round trip of a stage and the odd CTA's forwarding hop)
-constexpr int kPairNS = 4;       // state slots of 16 KB; the record ring lives inside them
-constexpr int kSSlot = 16384, kNSMax = 6;
+// Ring shapes (measured at 262,144 envs, h256x2, CTA pairs: four weight slots with four state
+// slots beat three weight slots with six state slots by 3 %, and six state slots with every
+// record slot inside one of them lost 2.6 % against four state slots plus two record slots of
+// their own: the weight ring's depth hides the L2 round trip of a stage, and the two record
+// slots outside the state ring are filled for the next tile while the gate layers still run)
+constexpr int kSSlot = 16384, kNSMax = 4;
 constexpr int kRBoxBytes = 32 * 80, kRSlot = 4 * kRBoxBytes, kNRMax = 6;
+constexpr int kOwnRSlots = 2;    // record slots outside the state slots (the classic record buffer's place)
 constexpr int kAexpSlots = 8;
 constexpr int kKBlocksMax = 4;
 
@@ -105,8 +113,8 @@ template <int GAME, int HID> __host__ __device__ constexpr int head_bytes(bool p
     return Hd<HID>::kKBlocks * (pair ? Gm<GAME>::kHeadPair : Gm<GAME>::kHeadSingle) * 128;
 }
 template <int GAME, int HID> __host__ __device__ constexpr size_t enc_bytes() {
-    static_assert(Gm<GAME>::kEncChunks % 2 == 0, "an encoder stage carries two chunks");
-    return (size_t)Gm<GAME>::kEncChunks * Hd<HID>::kEncBlockBytes;
+    static_assert(Gm<GAME>::kEncBlocks % 2 == 0, "an encoder stage carries two blocks");
+    return (size_t)Gm<GAME>::kEncBlocks * Hd<HID>::kEncBlockBytes;
 }
 
 // A lane that handles every G-th item of an N-slot ring waits on its slot's "empty" barrier
@@ -114,8 +122,8 @@ template <int GAME, int HID> __host__ __device__ constexpr size_t enc_bytes() {
 // i.e. while G <= N (its previous item, G back, already needed the slot use N+G back).
 // A ring shared by several consumers is only sound if every slot is always consumed by the
 // same consumer (a consumer that skips slots owned by others could otherwise be two phases
-// off): the record ring (4 slots, fills alternate between the worker warpgroups) and the
-// state ring (4 slots, slices alternate) satisfy this; each weight ring has one consumer.
+// off): the record ring (one consumer, warpgroup 1) and the state ring (4 slots, slices
+// alternate) satisfy this; each weight ring has one consumer.
 
 
 template <int GAME, int HID> __host__ __device__ constexpr size_t image_bytes(int L) {   // room for either head layout
@@ -127,10 +135,10 @@ template <int GAME, int HID> __host__ __device__ constexpr size_t image_bytes(in
 constexpr uint32_t kColA0 = 0, kColA1 = 128, kColG = 256, kColHead = 448;
 constexpr uint32_t kColAexp = 0, kColAcc = 256;
 
-constexpr int kTailBytes = 3 * kRSlot;   // the 204 tail bytes of every record: 3 box sets
+constexpr int kOwnBytes = kOwnRSlots * kRSlot;   // two record slots, or the classic tile's records
 enum Bar {
-    B_FULL = 0, B_EMPTY = B_FULL + kNBMax, S_FULL = B_EMPTY + kNBMax, S_DONE = S_FULL + kNSMax,
-    ST_READY = S_DONE + kNSMax, R_FULL = ST_READY + kNSMax, R_EMPTY = R_FULL + kNRMax,
+    B_FULL = 0, B_EMPTY = B_FULL + kNBMax, S_FULL = B_EMPTY + kNBMax, S_FREE = S_FULL + kNSMax,
+    ST_READY = S_FREE + kNSMax, R_FULL = ST_READY + kNSMax, R_EMPTY = R_FULL + kNRMax,
     AEXP_FULL = R_EMPTY + kNRMax, AEXP_EMPTY = AEXP_FULL + kAexpSlots,
     ACC_FULL = AEXP_EMPTY + kAexpSlots, A_KB = ACC_FULL + 1, G_FULL = A_KB + kKBlocksMax,
     G_EMPTY = G_FULL + 1, H_FULL = G_EMPTY + 1, H_EMPTY = H_FULL + 1, REC_DONE = H_EMPTY + 1,
@@ -142,34 +150,33 @@ enum Bar {
 //  one CTA per tile: weight ring 2 x 64 KB (whole two-block stages), state ring 4 x 16 KB;
 //  CTA pair (cta_group::2): every CTA stages half of each weight stage, 4 x 32 KB, state ring
 //    4 x 16 KB.
-//  In both modes the record ring (one 10 KB slot per state slot) lives INSIDE the state slots:
-//  records are needed only while the encoder runs, state boxes only while the gate layers run;
-//  REC_DONE and S_DONE order the two uses per tile.
+//  In both modes four of the six record slots (10 KB each) live INSIDE the state slots: records
+//  are needed only while the encoder runs, state boxes only while the gate layers run; REC_DONE
+//  and S_FREE order the two uses per tile.  The other two slots have room of their own, so the
+//  first chunks of the next tile are fetched while the gate layers of this one still run.
 template <bool PAIR, int GAME, int HID> struct Cfg {
     static constexpr int kH = HID, kStateItems = Hd<HID>::kStateItems;
     static constexpr int kNB = PAIR ? 4 : 2;             // stages of two blocks (128 KB of weights in flight)
     static constexpr int kBSlot = PAIR ? 32768 : 65536;
-    static constexpr int kWLanes = kNB;                  // one lane per slot
     static constexpr int kHeadRows = PAIR ? Gm<GAME>::kHeadPair : Gm<GAME>::kHeadSingle;   // N of the head MMA
     static constexpr int kHeadKbBytes = (PAIR ? kHeadRows / 2 : kHeadRows) * 128;   // one K block of the head rows a CTA stages
     static constexpr int kM = PAIR ? 256 : 128;
     // state ring slots: even, so that slot parity = warpgroup; at most one layer's boxes
-    static constexpr int kNS = PAIR && kPairNS <= kStateItems ? kPairNS : 4;
+    static constexpr int kNS = 4;
     // record ring inside the state slots (full game only: the classic records need no ring)
     static constexpr bool kAlias = GAME == CFX_GAME_FULL;
-    static constexpr int kNR = GAME != CFX_GAME_FULL ? 0 : kNS;
-    static constexpr int kRStride = kAlias ? kSSlot : kRSlot;
+    static constexpr int kOwn = GAME == CFX_GAME_FULL ? kOwnRSlots : 0;   // record slots beside the state slots
+    static constexpr int kNR = GAME != CFX_GAME_FULL ? 0 : kOwn + kNS;
     static constexpr int kOffB = 0;
     static constexpr int kOffS = kOffB + kNB * kBSlot;
-    static constexpr int kOffR = kAlias ? kOffS : kOffS + kNS * kSSlot;
-    static constexpr int kOffT = kAlias ? kOffS + kNS * kSSlot : kOffR + kNR * kRSlot;
-    static constexpr int kOffBias = kOffT + kTailBytes;       // b_enc[256] fp32, b_av[48] fp32
+    static constexpr int kOffT = kOffS + kNS * kSSlot;         // own record slots / classic records
+    static constexpr int kOffBias = kOffT + kOwnBytes;         // b_enc[256] fp32, b_av[48] fp32
     static constexpr int kOffBars = kOffBias + (kH + kHeadMax) * 4;
     static constexpr int kOffMisc = kOffBars + NUM_BARS * 8;  // tmem base, abort flag
     static constexpr int kSmemBytes = kOffMisc + 16 + 1024;   // + alignment slack
     static_assert(kNB <= kNBMax && kNR <= kNRMax && kNS <= kNSMax && kNS % 2 == 0 && kNS <= kStateItems &&
-                      kNR * kRSlot <= kNS * kSSlot && kSmemBytes <= 232448 && (!kAlias || kNR == kNS) &&
-                      kHeadRows <= kHeadMax && 128 * Gm<GAME>::kRecBytes <= kTailBytes + 128 * kRec, "layout");
+                      kRSlot <= kSSlot && kSmemBytes <= 232448 && kNS == 4 &&
+                      kHeadRows <= kHeadMax && 128 * kClassicRec <= kOwnBytes, "layout");
 };
 
 constexpr int kWorkerWarp0 = 4, kNumWarps = 12, kThreads = kNumWarps * 32;
@@ -177,7 +184,7 @@ constexpr int kWorkerWarp0 = 4, kNumWarps = 12, kThreads = kNumWarps * 32;
 // wait-site codes recorded in the status word when a bounded wait gives up
 enum WaitCode : uint32_t {
     W_B_EMPTY = 1, W_B_FULL, W_R_EMPTY, W_R_FULL, W_S_EMPTY, W_S_FULL, W_ST_READY, W_AEXP_EMPTY,
-    W_AEXP_FULL, W_ACC_FULL, W_A_KB, W_G_FULL, W_G_EMPTY, W_H_FULL, W_H_EMPTY, W_REC_DONE, W_S_DONE, W_T_FULL, W_T_EMPTY
+    W_AEXP_FULL, W_ACC_FULL, W_A_KB, W_G_FULL, W_G_EMPTY, W_H_FULL, W_H_EMPTY, W_REC_DONE, W_S_FREE, W_T_FULL, W_T_EMPTY
 };
 
 struct Params {
@@ -218,13 +225,15 @@ __host__ __device__ inline uint32_t sw128_off(uint32_t row, uint32_t byte_col) {
            (byte_col & 15);
 }
 
-// Encoder K order: K' in [0,800) = the 792 map bytes then 8 zero columns; K' in [800,864) =
-// the 51 tail floats then 13 zero columns.  Returns the feature index or -1 for padding.
-template <int GAME> __host__ __device__ inline int enc_feature(int chunk, int c) {
-    if (GAME == CFX_GAME_CLASSIC) return chunk * 64 + c < kClassicObs ? chunk * 64 + c : -1;
-    if (chunk < 12) return chunk * 64 + c;
-    if (chunk == 12) return c < 24 ? 768 + c : -1;
-    return c < kTail ? kMap + c : -1;
+// Feature behind K column c of encoder weight block `blk`, or -1 for padding.  Full game
+// (feature kMap + i is raw float i of the record): blocks 0-11 map bytes 64 blk + c; block 12
+// = map bytes 768-791, floats 0-9, 14 zero columns, floats 10-25; block 13 = floats 26-41,
+// floats 42-50, zero columns.
+template <int GAME> __host__ __device__ inline int enc_feature(int blk, int c) {
+    if (GAME == CFX_GAME_CLASSIC) return blk * 64 + c < kClassicObs ? blk * 64 + c : -1;
+    if (blk < 12) return blk * 64 + c;
+    if (blk == 12) return c < 24 ? 768 + c : (c < 34 ? kMap + (c - 24) : (c < 48 ? -1 : kMap + 10 + (c - 48)));
+    return c < 16 ? kMap + 26 + c : (c < 25 ? kMap + 42 + (c - 16) : -1);
 }
 
 template <typename T16>
@@ -426,16 +435,19 @@ __device__ __forceinline__ void mingru_cell_pair(float hzh0, float hzh1, float h
 
 struct Smem {
     uint8_t* base;
-    int off_s, off_r, r_stride, off_t, off_bias, off_bars, off_misc, b_slot_bytes;
+    int off_s, off_t, off_bias, off_bars, off_misc, b_slot_bytes;
     template <bool PAIR, int GAME, int HID> __device__ __forceinline__ void layout() {
         using C = Cfg<PAIR, GAME, HID>;
-        off_s = C::kOffS; off_r = C::kOffR; r_stride = C::kRStride; off_t = C::kOffT;
+        off_s = C::kOffS; off_t = C::kOffT;
         off_bias = C::kOffBias; off_bars = C::kOffBars; off_misc = C::kOffMisc; b_slot_bytes = C::kBSlot;
     }
     __device__ __forceinline__ uint32_t bar(int i) const { return smem_u32(base + off_bars + i * 8); }
     __device__ __forceinline__ uint8_t* b_ring() const { return base; }
     __device__ __forceinline__ uint8_t* s_slot(int s) const { return base + off_s + s * kSSlot; }
-    __device__ __forceinline__ uint8_t* r_slot(int s) const { return base + off_r + s * r_stride; }
+    // record slots 0 and 1 have room of their own, slot s >= 2 is state slot s - 2
+    __device__ __forceinline__ uint8_t* r_slot(int s) const {
+        return s < kOwnRSlots ? base + off_t + s * kRSlot : base + off_s + (s - kOwnRSlots) * kSSlot;
+    }
     __device__ __forceinline__ uint8_t* t_buf() const { return base + off_t; }
     __device__ __forceinline__ float* bias() const { return reinterpret_cast<float*>(base + off_bias); }
     __device__ __forceinline__ uint32_t* tmem_base() const { return reinterpret_cast<uint32_t*>(base + off_misc); }
@@ -459,6 +471,9 @@ struct Smem {
 #define CFX_WAIT(barid, parity, code) \
     if (!mbar_wait(sm.bar(barid), (parity), sm.abort_flag(), (code))) return
 #define CFX_WAITW(barid, parity, code) CFX_WAIT(barid, parity, code)
+// the two ring-feeding threads: no back-off between probes
+#define CFX_WAIT_FAST(barid, parity, code) \
+    if (!mbar_wait<false>(sm.bar(barid), (parity), sm.abort_flag(), (code))) return
 // The MMA role runs on ONE thread; the other lanes of its warp go straight to the exit.  (A
 // converged warp with an elected lane, one shuffle per wait and a __syncwarp per stage, was
 // 10 % slower end to end.)  It polls with test_wait: it never suspends.  The first probe is
@@ -469,23 +484,28 @@ struct Smem {
         !mbar_wait_spin(sm.bar(barid), (parity), sm.abort_flag(), (code)))            \
     return
 
-// Record ring schedule.  Fill kc of a tile carries map chunk kc (64 features of all 128 envs)
-// and lands in slot kc % NR (NR = 4 or 6).  Even chunks are expanded by worker warpgroup 1, odd
-// chunks and the tail by warpgroup 0, so even slots belong to wg 1 and odd slots to wg 0 for
-// the whole launch.  That is what makes the phase-parity waits sound: a waiter may be at most
-// one phase ahead of its barrier, and the warpgroup that waits for a fill has itself consumed
-// the previous fill of the same slot.  (A schedule in which the other warpgroup consumed a
-// slot's next fill raised a launch failure: it passed its wait two phases early and arrived on
-// the slot's "empty" barrier out of turn.)  Slot 0 takes one fill per tile more than the others.
+// Record ring schedule (full game).  Fill kc of a tile carries record bytes [64 kc, 64 kc + 64)
+// of all 128 envs.  Worker warpgroup 1 is free as soon as the previous tile's heads are done,
+// warpgroup 0 samples the previous tile's actions first: warpgroup 1 converts chunks 0, 1, 2 and
+// then the even chunks, warpgroup 0 the odd chunks from 3 on, so that the MMA thread, which
+// consumes the chunks in order, finds the two warpgroups working on neighbouring chunks.  Each
+// warpgroup has three ring slots of its own and one lane of the record warp that issues its
+// fills in order.  With one producer and one consumer per slot, both sides keep a slot's phase
+// as a running count of their own uses.  (The classic game shares its record buffer between
+// the warpgroups: even chunks warpgroup 1, odd ones warpgroup 0.)
 __device__ __forceinline__ int rec_owner(int kc) { return (kc & 1) ^ 1; }
-template <int NR> __device__ __forceinline__ int rec_slot(int kc) { return kc % NR; }
-template <int NR> __device__ __forceinline__ uint32_t rec_phase(uint32_t it, int kc) {   // phase index of fill kc
-    constexpr int kRecFills = Gm<CFX_GAME_FULL>::kRecFills;
-    constexpr uint32_t fills0 = (kRecFills + NR - 1) / NR, fills = kRecFills / NR;
-    static_assert(NR % 2 == 0 && fills0 == fills + 1 && kRecFills % NR == 1, "slot 0 takes the odd fill");
-    return ((kc % NR) == 0 ? fills0 : fills) * it + (uint32_t)(kc / NR);
+constexpr int kHeadStart = 3, kWgRSlots = 3;
+__device__ __forceinline__ int full_owner(int kc) { return kc < kHeadStart ? 1 : ((kc & 1) ^ 1); }
+__device__ __forceinline__ int full_first(int wg) { return wg == 1 ? 0 : kHeadStart; }
+// the chunk the same warpgroup converts after chunk kc (beyond the last chunk: none)
+__device__ __forceinline__ int full_next(int kc) { return kc < kHeadStart - 1 ? kc + 1 : kc + 2; }
+// position of chunk kc in its warpgroup's sequence, and the ring slot it lands in
+__device__ __forceinline__ int full_index(int kc) {
+    return kc < kHeadStart ? kc : ((kc & 1) ? (kc - kHeadStart) >> 1 : kHeadStart + ((kc - kHeadStart - 1) >> 1));
 }
-constexpr int kLastWg1 = 12;
+__device__ __forceinline__ int full_rslot(int kc) {
+    return (full_owner(kc) == 1 ? 0 : kWgRSlots) + full_index(kc) % kWgRSlots;
+}
 
 // Software prefetch into L2.  The rings are far too small to cover HBM latency at the rate the
 // encoder and the cell consume, so every byte a ring will load is requested from HBM ahead of
@@ -536,19 +556,19 @@ __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& 
                                                   uint32_t rank, uint32_t bar0_cta0) {
     using C = Cfg<PAIR, GAME, HID>;
     CFX_DIMS(HID);
-    constexpr int kEncChunks = Gm<GAME>::kEncChunks;
-    constexpr int kEncStages = kEncChunks / kStageBlocks;
+    constexpr int kEncStages = Gm<GAME>::kEncBlocks / kStageBlocks;
     const int stages_gate = P.L * kSlices * (kKBlocks / kStageBlocks);
     const size_t enc_bytes = fused::enc_bytes<GAME, HID>();
-    static_assert(C::kWLanes == C::kNB, "one lane per slot: the lane's k-th stage is the slot's k-th fill");
-    // this lane's stages: every kNB-th of the launch-wide stage sequence, starting at `lane`
+    // One lane walks the launch-wide stage sequence: the slots come free in the order they were
+    // filled.  (One lane per slot, diverged inside one warp, delivered stages late: a lane whose
+    // slot had come free waited for the warp to leave another lane's suspended wait.)
     const int per_tile = kEncStages + stages_gate + 1;
-    int tile = P.tile_begin + blockIdx.x, s = lane;
-    auto normalise = [&]() {
-        while (s >= per_tile) { s -= per_tile; tile += gridDim.x; }
-    };
-    normalise();
-    for (uint32_t use = 0; tile < P.num_tiles_loop; use++) {
+    int tile = P.tile_begin + blockIdx.x, s = 0;
+    int slot = 0;
+    uint32_t par = 1;   // parity of the "empty" phase to wait for: the first pass finds every slot free
+    (void)lane;
+    CFX_MARK_INIT(3);
+    for (; tile < P.num_tiles_loop;) {
         uint32_t bytes;
         size_t off;
         if (s < kEncStages) {
@@ -559,8 +579,9 @@ __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& 
             bytes = head_bytes<GAME, HID>(PAIR);
             off = enc_bytes + (size_t)stages_gate * kGateStageBytes;
         }
-        CFX_WAIT(B_EMPTY + lane, (use & 1) ^ 1, W_B_EMPTY);
-        const uint32_t dst = smem_u32(sm.b_ring() + lane * C::kBSlot);
+        CFX_WAIT_FAST(B_EMPTY + slot, par, W_B_EMPTY);
+        CFX_MARK(1);
+        const uint32_t dst = smem_u32(sm.b_ring() + slot * C::kBSlot);
         if (PAIR) {
             // Each CTA copies its half of the stage into its own shared memory; both copies are
             // counted on the EVEN CTA's "full" barrier (where the MMA thread waits), which
@@ -570,105 +591,144 @@ __device__ __forceinline__ void role_weight_loads(const Smem& sm, const Params& 
             const size_t base = region == 0 ? 0 : (region == 1 ? enc_bytes : enc_bytes + (size_t)stages_gate * kGateStageBytes);
             const uint32_t half = bytes >> 1;
             const int y = (int)((off - base + (size_t)rank * half) >> 7);   // rows of 128 bytes
-            if (rank == 0) mbar_arrive_expect_tx(sm.bar(B_FULL + lane), bytes);
-            tensor_g2s_2d_pair(dst, &P.w_map[region], 0, y, bar0_cta0 + 8u * (uint32_t)(B_FULL + lane));
+            if (rank == 0) mbar_arrive_expect_tx(sm.bar(B_FULL + slot), bytes);
+            tensor_g2s_2d_pair(dst, &P.w_map[region], 0, y, bar0_cta0 + 8u * (uint32_t)(B_FULL + slot));
         } else {
-            mbar_arrive_expect_tx(sm.bar(B_FULL + lane), bytes);
-            bulk_g2s(dst, P.image + off, bytes, sm.bar(B_FULL + lane));
+            mbar_arrive_expect_tx(sm.bar(B_FULL + slot), bytes);
+            bulk_g2s(dst, P.image + off, bytes, sm.bar(B_FULL + slot));
         }
-        s += C::kNB;
-        normalise();
+        CFX_MARK(2);
+        if (++s == per_tile) { s = 0; tile += gridDim.x; }
+        if (++slot == C::kNB) { slot = 0; par ^= 1u; }
     }
+    CFX_MARK_FLUSH();
 }
 
 // Records: the [n][996] byte array is viewed as [n/4][3984] (four records per 16-byte
-// aligned row); env 4g+i of a tile sits in row g at byte 996 i.  A 64-byte feature chunk of
-// all 128 envs is fetched as four boxes (one per i) of 32 rows x 80 bytes starting at the
-// 16-byte boundary below 996 i + 64 c; the 204 tail bytes take three more such box sets.
-template <bool PAIR, int GAME, int HID>
-__device__ __forceinline__ void role_record_loads(const Smem& sm, const Params& P, int lane) {
-    using C = Cfg<PAIR, GAME, HID>;
-    constexpr int kNR = C::kNR;
-    constexpr int kRecFills = Gm<GAME>::kRecFills;
-    uint32_t it = 0;
-    if constexpr (GAME == CFX_GAME_CLASSIC) {
-        // classic: the records of the whole tile are one box, 32 rows of four 148-byte records
-        // (a [n/4][148] array of 32-bit words), into the buffer the full game uses for its tail
-        const uint32_t dst = smem_u32(sm.t_buf());
-        for (int tile = P.tile_begin + blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
-            CFX_WAIT(T_EMPTY, (it & 1) ^ 1, W_T_EMPTY);
-            mbar_arrive_expect_tx(sm.bar(T_FULL), 128 * kClassicRec);
-            tensor_g2s_2d(dst, &P.rec_map, 0, tile * 32, sm.bar(T_FULL));
-        }
-    } else if (lane < kNR) {
-        // lane `lane` owns ring slot `lane` and issues all four boxes of the fills that land on it
-        const uint32_t slot_addr = smem_u32(sm.r_slot(lane));
-        for (int tile = P.tile_begin + blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
-            // ring inside the state slots: before the first fill of the tile the previous
-            // tile's last state box must have left this slot
-            if (C::kAlias) CFX_WAIT(S_DONE + lane, (it & 1) ^ 1, W_S_DONE);
-            for (int kc = lane; kc < kRecFills; kc += kNR) {
-                CFX_WAIT(R_EMPTY + lane, (rec_phase<kNR>(it, kc) & 1) ^ 1, W_R_EMPTY);
-                mbar_arrive_expect_tx(sm.bar(R_FULL + lane), kRSlot);
+// aligned row); env 4g+i of a tile sits in row g at byte 996 i.  A 64-byte chunk of all 128
+// records is fetched as four boxes (one per i) of 32 rows x 80 bytes starting at the 16-byte
+// boundary below 996 i + 64 c (the last chunk's boxes reach past the row: zero fill).
+__device__ __forceinline__ void record_fill(const Smem& sm, const Params& P, int tile, int kc, int slot) {
+    mbar_arrive_expect_tx(sm.bar(R_FULL + slot), kRSlot);
+    const uint32_t slot_addr = smem_u32(sm.r_slot(slot));
 #pragma unroll
-                for (int i = 0; i < 4; i++)
-                    tensor_g2s_2d(slot_addr + i * kRBoxBytes, &P.rec_map, (kRec * i + 64 * kc) & ~15,
-                                  tile * 32, sm.bar(R_FULL + lane));
-            }
-        }
-    } else {
-        // the tail lane: three box sets cover the 51 raw floats (204 bytes from byte 792) of
-        // every record; they go to a buffer of their own, read by warpgroup 0 only
-        const uint32_t dst = smem_u32(sm.t_buf());
-        for (int tile = P.tile_begin + blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
-            CFX_WAIT(T_EMPTY, (it & 1) ^ 1, W_T_EMPTY);
-            mbar_arrive_expect_tx(sm.bar(T_FULL), kTailBytes);
-#pragma unroll
-            for (int s3 = 0; s3 < 3; s3++)
-#pragma unroll
-                for (int i = 0; i < 4; i++)
-                    tensor_g2s_2d(dst + s3 * kRSlot + i * kRBoxBytes, &P.rec_map,
-                                  ((kRec * i + kMap) & ~15) + 80 * s3, tile * 32, sm.bar(T_FULL));
-        }
-    }
+    for (int i = 0; i < 4; i++)
+        tensor_g2s_2d(slot_addr + i * kRBoxBytes, &P.rec_map, (kRec * i + 64 * kc) & ~15, tile * 32,
+                      sm.bar(R_FULL + slot));
 }
 
 // State boxes: layer l, tile rows, 32 units -> one 16 KB box, 128-byte swizzled; box j of a
-// layer belongs to slice j / 2 and worker warpgroup j & 1.  Lane `lane` owns ring slot `lane`
-// and serves the boxes that fall on it one after the other: load, wait until the workers have
-// replaced the contents with the new state, write it back (rows beyond n are clipped by the
-// tensor map), and only then load the next box into the slot.  One lane per slot needs no
-// "slot empty" barrier and saves a hand-off.
+// layer belongs to slice j / 2 and worker warpgroup j & 1, and box b of a tile uses ring slot
+// b % 4.  The workers replace a box's contents with the new state in place; it is then written
+// back (rows beyond n are clipped by the tensor map) and the slot is loaded again.
+//
+// Two threads in two warps feed the rings, each a plain sequence of waits and copies.  (Several
+// lanes of one warp, one per ring slot, each in its own loop, ran at a fraction of that speed:
+// a lane whose barrier had completed took 600-700 cycles to get from one statement to the
+// next while the warp served the other lanes.)
+//   load thread:  per tile, the record fills of worker warpgroup 1, then the state box loads;
+//   store thread: per tile, the record fills of worker warpgroup 0, then the state box stores.
+// The record phase and the state phase of a tile do not overlap in time, so neither thread
+// holds the other's work up.  The load thread takes a state slot when the store thread reports
+// that the previous box has been read out of it (S_FREE); that includes state slot 0 before it
+// is used as warpgroup 1's third record slot.  The store thread's own record slots are state
+// slots 1-3, free once its stores of the previous tile have been read.
 template <bool PAIR, int GAME, int HID>
-__device__ __forceinline__ void role_state_ring(const Smem& sm, const Params& P, int lane) {
+__device__ __forceinline__ void role_loads(const Smem& sm, const Params& P) {
     using C = Cfg<PAIR, GAME, HID>;
     CFX_DIMS(HID);
     constexpr int kNS = C::kNS;
-    uint32_t cnt = 0, uses = 0, it = 0;
-    const uint32_t slot_addr = smem_u32(sm.s_slot(lane));
+    static_assert(kStateItems % kNS == 0 && (GAME != CFX_GAME_FULL || C::kOwn == kWgRSlots - 1),
+                  "box b of a tile uses slot b % kNS; warpgroup 1's third record slot is state slot 0");
+    uint32_t it = 0;
+    uint32_t epar = (1u << kNRMax) - 1u;   // record slots: parity of the "empty" phase to wait for
+    uint32_t fpar = (1u << kNS) - 1u;      // state slots: parity of the "free" phase to wait for
+    CFX_MARK_INIT(4);
     for (int tile = P.tile_begin + blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, it++) {
+        if constexpr (GAME == CFX_GAME_CLASSIC) {
+            // classic: the records of the whole tile are one box, 32 rows of four 148-byte
+            // records (a [n/4][148] array of 32-bit words)
+            CFX_WAIT_FAST(T_EMPTY, (it & 1) ^ 1, W_T_EMPTY);
+            mbar_arrive_expect_tx(sm.bar(T_FULL), 128 * kClassicRec);
+            tensor_g2s_2d(smem_u32(sm.t_buf()), &P.rec_map, 0, tile * 32, sm.bar(T_FULL));
+        } else {
+            for (int kc = full_first(1); kc < Gm<GAME>::kEncChunks; kc = full_next(kc)) {
+                const int slot = full_rslot(kc);
+                if (slot >= C::kOwn && full_index(kc) < kWgRSlots) {   // first fill of the tile into state slot 0
+                    CFX_WAIT_FAST(S_FREE + slot - C::kOwn, (fpar >> (slot - C::kOwn)) & 1u, W_S_FREE);
+                    fpar ^= 1u << (slot - C::kOwn);
+                }
+                CFX_WAIT_FAST(R_EMPTY + slot, (epar >> slot) & 1u, W_R_EMPTY);
+                epar ^= 1u << slot;
+                record_fill(sm, P, tile, kc, slot);
+            }
+        }
+        int b = 0;
         for (int l = 0; l < P.L; l++) {
-            for (int j = 0; j < kStateItems; j++, cnt++) {
-                if ((int)(cnt % kNS) != lane) continue;
-                // this lane's first box of the tile (every slot gets at least one box per tile):
-                // every record of the tile has been expanded
-                const int b = l * kStateItems + j;
-                if (C::kAlias && b < kNS) CFX_WAIT(REC_DONE, it & 1, W_REC_DONE);
-                mbar_arrive_expect_tx(sm.bar(S_FULL + lane), kSSlot);
-                tensor_g2s_2d(slot_addr, &P.state_map[l], j * kHalfUnits, tile * kTile,
-                              sm.bar(S_FULL + lane));
-                l2_prefetch_for_box<HID>(P, tile, l, j);
-                CFX_WAIT(ST_READY + lane, uses & 1, W_ST_READY);
-                uses++;
-                tensor_s2g_2d(&P.state_map[l], slot_addr, j * kHalfUnits, tile * kTile);
+            for (int j = 0; j < kStateItems; j++, b++) {
+                const int slot = b % kNS;
+                // the first box of the tile: every record of the tile has been expanded
+                if (C::kAlias && b == 0) CFX_WAIT_FAST(REC_DONE, it & 1, W_REC_DONE);
+                if (!(C::kAlias && b == 0)) {   // (slot 0 was taken for the records already)
+                    CFX_WAIT_FAST(S_FREE + slot, (fpar >> slot) & 1u, W_S_FREE);
+                    fpar ^= 1u << slot;
+                }
+                CFX_MARK(1);
+                mbar_arrive_expect_tx(sm.bar(S_FULL + slot), kSSlot);
+                tensor_g2s_2d(smem_u32(sm.s_slot(slot)), &P.state_map[l], j * kHalfUnits, tile * kTile,
+                              sm.bar(S_FULL + slot));
+                CFX_MARK(2);
+                // the L2 prefetches that go with the two boxes of a slice, after both loads
+                if (j & 1) {
+                    l2_prefetch_for_box<HID>(P, tile, l, j - 1);
+                    l2_prefetch_for_box<HID>(P, tile, l, j);
+                }
+            }
+        }
+    }
+    CFX_MARK_FLUSH();
+}
+
+template <bool PAIR, int GAME, int HID>
+__device__ __forceinline__ void role_stores(const Smem& sm, const Params& P) {
+    using C = Cfg<PAIR, GAME, HID>;
+    CFX_DIMS(HID);
+    constexpr int kNS = C::kNS;
+    static_assert(kStateItems % 2 == 0, "the two boxes of a slice are written back together");
+    uint32_t epar = (1u << kNRMax) - 1u;   // record slots: parity of the "empty" phase to wait for
+    uint32_t spar = 0;                     // state slots: parity of the "new state ready" phase
+    CFX_MARK_INIT(5);
+    for (int tile = P.tile_begin + blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x) {
+        if constexpr (GAME == CFX_GAME_FULL) {
+            for (int kc = full_first(0); kc < Gm<GAME>::kEncChunks; kc = full_next(kc)) {
+                const int slot = full_rslot(kc);
+                CFX_WAIT_FAST(R_EMPTY + slot, (epar >> slot) & 1u, W_R_EMPTY);
+                epar ^= 1u << slot;
+                record_fill(sm, P, tile, kc, slot);
+            }
+        }
+        int b = 0;
+        for (int l = 0; l < P.L; l++) {
+            for (int j = 0; j < kStateItems; j++, b++) {
+                const int slot = b % kNS;
+                CFX_WAIT_FAST(ST_READY + slot, (spar >> slot) & 1u, W_ST_READY);
+                spar ^= 1u << slot;
+                CFX_MARK(3);
+                tensor_s2g_2d(&P.state_map[l], smem_u32(sm.s_slot(slot)), j * kHalfUnits, tile * kTile);
                 bulk_commit_group();
-                bulk_wait_group_read<0>();
-                // this lane's last box of the tile has left the slot: records may come in
-                if (C::kAlias && b >= P.L * kStateItems - kNS) mbar_arrive(sm.bar(S_DONE + lane));
+                if (j & 1) {
+                    // a slot is free as soon as its box has been read out of shared memory
+                    bulk_wait_group_read<1>();
+                    mbar_arrive(sm.bar(S_FREE + (b - 1) % kNS));
+                    bulk_wait_group_read<0>();
+                    mbar_arrive(sm.bar(S_FREE + slot));
+                    CFX_MARK(4);
+                }
             }
         }
     }
     bulk_wait_group<0>();
+    CFX_MARK_FLUSH();
 }
 
 // ------------------------------------------------------------------ MMA role
@@ -716,55 +776,83 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
     // under the MMA issue; only a failed probe falls into the bounded wait.  Probing one stage
     // early is sound: the previous use of that slot has already been consumed by this thread,
     // so its barrier is at most one phase behind.
-    auto probe_b_next = [&]() -> bool {
+    // The probes are deferred ones (CFX_PROBE): their result is read a stage later.
+    auto probe_b_next = [&]() {
         const bool wrap = bslot + 1 == kNB;
-        return mbar_test_wait(sm.bar(B_FULL + (wrap ? 0 : bslot + 1)), wrap ? bpar ^ 1u : bpar);
+        CFX_PROBE(cfx_p_b, sm.bar(B_FULL + (wrap ? 0 : bslot + 1)), wrap ? bpar ^ 1u : bpar);
     };
-    auto probe_a = [&](uint32_t cnt) -> bool {
-        return mbar_test_wait(sm.bar(AEXP_FULL + (int)(cnt % kAexpSlots)), (cnt / kAexpSlots) & 1);
+    auto probe_a = [&](uint32_t cnt) {
+        CFX_PROBE(cfx_p_a, sm.bar(AEXP_FULL + (int)(cnt % kAexpSlots)), (cnt / kAexpSlots) & 1);
     };
-#define CFX_WAIT_PROBED(ready, barid, parity, code) \
-    if (!(ready) && !mbar_wait_spin(sm.bar(barid), (parity), sm.abort_flag(), (code))) return
+#define CFX_WAIT_PROBED(name, barid, parity, code)                                                  \
+    {                                                                                               \
+        uint32_t ready_;                                                                            \
+        CFX_PROBE_READ(name, ready_);                                                               \
+        if (ready_ == 0 && !mbar_wait_spin(sm.bar(barid), (parity), sm.abort_flag(), (code))) return; \
+    }
     CFX_MARK_INIT(0);
     for (int tile = P.tile_begin + blockIdx.x; tile < P.num_tiles_loop; tile += gridDim.x, tcnt++) {
         CFX_MARK(0);
         // the encoder accumulator overlaps the head accumulator of the previous tile:
         // wait until the sampler threads have read it
         CFX_WAIT_LEADER(H_EMPTY, (tcnt & 1) ^ 1, W_H_EMPTY);
-        bool a_ready = probe_a(acnt), b_ready = mbar_test_wait(sm.bar(B_FULL + bslot), bpar);
-        // ---- encoder: operand chunks of 64 features, N = 256 units; one weight stage per two chunks
-        for (int kp = 0; kp < kEncChunks / kStageBlocks; kp++) {
+        probe_a(acnt);
+        CFX_PROBE(cfx_p_b, sm.bar(B_FULL + bslot), bpar);
+        // ---- encoder: N = kH units; one weight stage (two blocks of 64 K columns) per two
+        // chunks, except the full game's last stage, which four short chunks consume
+        // one operand chunk: wait for it, issue its K steps against the block at descriptor bd
+#define CFX_ENC_CHUNK(kc, bd, ksteps)                                                              \
+        {                                                                                          \
+            const int as = acnt % kAexpSlots;                                                      \
+            CFX_WAIT_PROBED(cfx_p_a, AEXP_FULL + as, (acnt / kAexpSlots) & 1, W_AEXP_FULL);        \
+            CFX_MARK(2);                                                                           \
+            tc_fence_after_sync();                                                                 \
+            if ((kc) + 1 < kEncChunks) probe_a(acnt + 1);                                          \
+            const uint32_t a_col = tmem + kColAexp + as * 32;                                      \
+            if ((kc) == 0) MMA_TS(tmem + kColAcc, a_col, (bd), idesc_enc, 0);                      \
+            else MMA_TS(tmem + kColAcc, a_col, (bd), idesc_enc, 1);                                \
+            if ((ksteps) > 1) {                                                                    \
+                MMA_TS(tmem + kColAcc, a_col + 8, (bd) + 2, idesc_enc, 1);                         \
+                MMA_TS(tmem + kColAcc, a_col + 16, (bd) + 4, idesc_enc, 1);                        \
+            }                                                                                      \
+            if ((ksteps) > 3) MMA_TS(tmem + kColAcc, a_col + 24, (bd) + 6, idesc_enc, 1);          \
+            MMA_COMMIT(sm.bar(AEXP_EMPTY + as));                                                   \
+            acnt++;                                                                                \
+            CFX_MARK(4);                                                                           \
+        }
+        constexpr int kFullStages = GAME == CFX_GAME_FULL ? 6 : kEncChunks / kStageBlocks;
+        for (int kp = 0; kp < kFullStages; kp++) {
             const int slot = bslot;
-            CFX_WAIT_PROBED(b_ready, B_FULL + slot, bpar, W_B_FULL);
+            CFX_WAIT_PROBED(cfx_p_b, B_FULL + slot, bpar, W_B_FULL);
             CFX_MARK(3);
-            b_ready = probe_b_next();
+            probe_b_next();
             b_advance();
             const uint64_t bd0 = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
 #pragma unroll
-            for (int c2 = 0; c2 < kStageBlocks; c2++, acnt++) {
+            for (int c2 = 0; c2 < kStageBlocks; c2++) {
                 const int kc = kStageBlocks * kp + c2;
-                const int as = acnt % kAexpSlots;
-                CFX_WAIT_PROBED(a_ready, AEXP_FULL + as, (acnt / kAexpSlots) & 1, W_AEXP_FULL);
-                CFX_MARK(2);
-                tc_fence_after_sync();
-                a_ready = kc + 1 < kEncChunks ? probe_a(acnt + 1) : false;
-                const uint32_t a_col = tmem + kColAexp + as * 32;
-                const uint64_t bd = bd0 + (uint64_t)(c2 * kEncBlkStep);
-                if (kc == 0) MMA_TS(tmem + kColAcc, a_col, bd, idesc_enc, 0);
-                else MMA_TS(tmem + kColAcc, a_col, bd, idesc_enc, 1);
-                // short chunks: full game chunk 12 carries 24 map bytes (two K steps), the classic
-                // game's last chunk one feature (one K step)
-                const int ksteps = GAME == CFX_GAME_FULL ? (kc == 12 ? 2 : 4) : (kc == kEncChunks - 1 ? 1 : 4);
-                if (ksteps > 1) MMA_TS(tmem + kColAcc, a_col + 8, bd + 2, idesc_enc, 1);
-                if (ksteps > 2) {
-                    MMA_TS(tmem + kColAcc, a_col + 16, bd + 4, idesc_enc, 1);
-                    MMA_TS(tmem + kColAcc, a_col + 24, bd + 6, idesc_enc, 1);
-                }
-                MMA_COMMIT(sm.bar(AEXP_EMPTY + as));
-                CFX_MARK(4);
+                // the classic game's last chunk carries one feature (one K step)
+                const int ksteps = GAME == CFX_GAME_CLASSIC && kc == kEncChunks - 1 ? 1 : 4;
+                CFX_ENC_CHUNK(kc, bd0 + (uint64_t)(c2 * kEncBlkStep), ksteps);
             }
             MMA_COMMIT(sm.bar(B_EMPTY + slot));
         }
+        if constexpr (GAME == CFX_GAME_FULL) {
+            // blocks 12 and 13: chunk 12 = K columns 0-47 of block 12 (three K steps), chunk 13
+            // = columns 48-63; chunk 14 = columns 0-15 of block 13, chunk 15 = columns 16-31
+            const int slot = bslot;
+            CFX_WAIT_PROBED(cfx_p_b, B_FULL + slot, bpar, W_B_FULL);
+            CFX_MARK(3);
+            probe_b_next();
+            b_advance();
+            const uint64_t bd0 = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
+            CFX_ENC_CHUNK(12, bd0, 3);
+            CFX_ENC_CHUNK(13, bd0 + 6, 1);
+            CFX_ENC_CHUNK(14, bd0 + (uint64_t)kEncBlkStep, 1);
+            CFX_ENC_CHUNK(15, bd0 + (uint64_t)(kEncBlkStep + 2), 1);
+            MMA_COMMIT(sm.bar(B_EMPTY + slot));
+        }
+#undef CFX_ENC_CHUNK
         MMA_COMMIT(sm.bar(ACC_FULL));
 
         // ---- MinGRU layers: 4 slices of 64 units, one stage per two K blocks, N = 192 (zh|zg|zp)
@@ -785,9 +873,9 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
 #pragma unroll
                 for (int kp = 0; kp < kKBlocks / kStageBlocks; kp++) {
                     const int slot = bslot;
-                    CFX_WAIT_PROBED(b_ready, B_FULL + slot, bpar, W_B_FULL);
+                    CFX_WAIT_PROBED(cfx_p_b, B_FULL + slot, bpar, W_B_FULL);
                     CFX_MARK(6);
-                    b_ready = probe_b_next();
+                    probe_b_next();
                     b_advance();
                     const uint64_t bd0 = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
 #pragma unroll
@@ -815,7 +903,7 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
         {
             const uint32_t a_cur = tmem + ((P.L & 1) ? kColA1 : kColA0);
             const int slot = bslot;
-            CFX_WAIT_PROBED(b_ready, B_FULL + slot, bpar, W_B_FULL);
+            CFX_WAIT_PROBED(cfx_p_b, B_FULL + slot, bpar, W_B_FULL);
             b_advance();
             const uint64_t bd = bdesc0 + (uint64_t)(slot * (kBSlot >> 4));
             // K block kb of the last layer's output is complete when slice kb's cells are done
@@ -847,7 +935,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
     using Op = Op16<T16>;
     using C = Cfg<PAIR, GAME, HID>;
     CFX_DIMS(HID);
-    constexpr int kA = Gm<GAME>::kA, kEncChunks = Gm<GAME>::kEncChunks, kRecFills = Gm<GAME>::kRecFills;
+    constexpr int kA = Gm<GAME>::kA, kEncChunks = Gm<GAME>::kEncChunks;
     constexpr int kHeadCols = (kA + 1 + 15) / 16 * 16;   // head accumulator columns that are read
     // barriers the MMA thread waits on live in the even CTA of a pair
     auto arrive_mma = [&](int barid) {
@@ -862,6 +950,7 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
     const float* bias = sm.bias();
     const uint32_t rec_row_off = ii * kRBoxBytes + gi * 80;
     uint32_t tcnt = 0, gcnt = 0, it = 0;
+    uint32_t rpar = 0;   // full game: phase parity of every record slot, one bit per slot
     // the sampler offset is constant for the launch (the bump happens after every block is done)
     const unsigned long long step0 = P.uniforms == nullptr ? *P.step_ctr : 0ull;
     CFX_MARK_INIT(1 + wg);
@@ -873,14 +962,27 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
             valid && P.prev_terminals != nullptr && P.prev_terminals[env] != 0.0f;
 
         // ---- expand: record bytes -> 16-bit operand rows in the TMEM chunk ring.
-        // wg 1 converts the even chunks, wg 0 the odd ones and the tail; a warp writes all 32
-        // columns of its rows.
+        // Full game: wg 1 converts chunks 0-2 and the even ones after them, wg 0 (which samples
+        // the previous tile's actions first) the odd ones from 3 on.  Classic game: wg 1 converts
+        // the even chunks, wg 0 the odd ones.  A warp writes all 32 columns of its rows.
+        // Full game: the two barriers of a chunk are probed one chunk ahead, so that the
+        // probes' shared-memory round trips (~200 cycles each, also when the barrier is already
+        // complete) run under the previous chunk's conversion; only a failed probe falls into
+        // the wait loop.  Probing ahead is sound: this warp has itself passed the previous phase
+        // of both barriers.
+        if (GAME == CFX_GAME_FULL) {
+            const int kc0 = full_first(wg);
+            const uint32_t acnt0 = it * kEncChunks + kc0;
+            CFX_PROBE(cfx_p_ae, sm.bar(AEXP_EMPTY + (int)(acnt0 % kAexpSlots)), ((acnt0 / kAexpSlots) & 1) ^ 1);
+            CFX_PROBE(cfx_p_r, sm.bar(R_FULL + full_rslot(kc0)), (rpar >> full_rslot(kc0)) & 1u);
+        }
         for (int kc = 0; kc < kEncChunks; kc++) {
-            // even chunks: wg 1, odd chunks: wg 0; the full game's tail chunk: wg 0
-            if ((GAME == CFX_GAME_CLASSIC || kc < kRecFills ? rec_owner(kc) : 0) != wg) continue;
+            if ((GAME == CFX_GAME_CLASSIC ? rec_owner(kc) : full_owner(kc)) != wg) continue;
             const uint32_t acnt = it * kEncChunks + kc;
             const int as = acnt % kAexpSlots;
-            CFX_WAITW(AEXP_EMPTY + as, ((acnt / kAexpSlots) & 1) ^ 1, W_AEXP_EMPTY);
+            uint32_t ae_ok = 0;
+            if (GAME == CFX_GAME_FULL) CFX_PROBE_READ(cfx_p_ae, ae_ok);
+            if (ae_ok == 0) CFX_WAITW(AEXP_EMPTY + as, ((acnt / kAexpSlots) & 1) ^ 1, W_AEXP_EMPTY);
             CFX_MARK(2);
             tc_fence_after_sync();
             uint32_t regs[32];
@@ -926,44 +1028,54 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 }
                 __syncwarp();
                 if (kc >= kEncChunks - 2 && lane == 0) mbar_arrive(sm.bar(T_EMPTY));   // last chunk of this warp
-            } else if (kc < 13) {
-                constexpr int kNRw = C::kNR;
-                const int slot = rec_slot<kNRw>(kc);
-                CFX_WAITW(R_FULL + slot, rec_phase<kNRw>(it, kc) & 1, W_R_FULL);
-                CFX_MARK(3);
-                const uint8_t* src = sm.r_slot(slot) + rec_row_off + ((kRec * ii) & 15);
-#pragma unroll
-                for (int q = 0; q < 16; q++) {
-                    uint32_t w32 = *reinterpret_cast<const uint32_t*>(src + 4 * q);
-                    if (kc == 12 && q >= 6) w32 = 0;  // record bytes 792.. are not map bytes
-                    Op::bytes4(w32, regs[2 * q], regs[2 * q + 1]);
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(sm.bar(R_EMPTY + slot));
             } else {
-                CFX_WAITW(T_FULL, it & 1, W_T_FULL);
-                const uint32_t rem = (kRec * ii + kMap) & 15;
+                const int slot = full_rslot(kc);
+                uint32_t r_ok;
+                CFX_PROBE_READ(cfx_p_r, r_ok);
+                if (r_ok == 0) CFX_WAITW(R_FULL + slot, (rpar >> slot) & 1u, W_R_FULL);
+                rpar ^= 1u << slot;
+                CFX_MARK(3);
+                if (full_next(kc) < kEncChunks) {
+                    const int slot1 = full_rslot(full_next(kc));
+                    const uint32_t acnt1 = it * kEncChunks + full_next(kc);
+                    CFX_PROBE(cfx_p_ae, sm.bar(AEXP_EMPTY + (int)(acnt1 % kAexpSlots)),
+                              ((acnt1 / kAexpSlots) & 1) ^ 1);
+                    CFX_PROBE(cfx_p_r, sm.bar(R_FULL + slot1), (rpar >> slot1) & 1u);
+                }
+                // this env's 64 record bytes of the chunk (4-byte aligned in the slot)
+                const uint8_t* src = sm.r_slot(slot) + rec_row_off + ((kRec * ii) & 15);
+                auto word = [&](int q) { return *reinterpret_cast<const uint32_t*>(src + 4 * q); };
+                if (kc < 12) {          // 64 map bytes
 #pragma unroll
-                for (int q = 0; q < 32; q++) {
-                    float v[2];
+                    for (int q = 0; q < 16; q++) Op::bytes4(word(q), regs[2 * q], regs[2 * q + 1]);
+                } else {
 #pragma unroll
-                    for (int e = 0; e < 2; e++) {
-                        const int f = 2 * q + e;  // tail float index
-                        v[e] = 0.0f;
-                        if (f < kTail) {
-                            const uint32_t off = rem + 4 * f;
-                            const uint32_t sidx = off / 80, within = off - sidx * 80;
-                            v[e] = *reinterpret_cast<const float*>(
-                                sm.t_buf() + sidx * kRSlot + rec_row_off + within);
-                        }
+                    for (int q = 0; q < 32; q++) regs[q] = 0u;
+                    if (kc == 12) {     // 24 map bytes, then raw floats 0-9
+#pragma unroll
+                        for (int q = 0; q < 6; q++) Op::bytes4(word(q), regs[2 * q], regs[2 * q + 1]);
+#pragma unroll
+                        for (int q = 0; q < 5; q++)
+                            regs[12 + q] = Op::pack(__uint_as_float(word(6 + 2 * q)), __uint_as_float(word(7 + 2 * q)));
+                    } else if (kc < 15) {   // 16 raw floats
+#pragma unroll
+                        for (int q = 0; q < 8; q++)
+                            regs[q] = Op::pack(__uint_as_float(word(2 * q)), __uint_as_float(word(2 * q + 1)));
+                    } else {            // the last 9 raw floats; the record ends after them
+#pragma unroll
+                        for (int q = 0; q < 4; q++)
+                            regs[q] = Op::pack(__uint_as_float(word(2 * q)), __uint_as_float(word(2 * q + 1)));
+                        regs[4] = Op::pack(__uint_as_float(word(8)), 0.0f);
                     }
-                    regs[q] = Op::pack(v[0], v[1]);
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(sm.bar(T_EMPTY));
+                if (lane == 0) {
+                    mbar_arrive(sm.bar(R_EMPTY + slot));
+                    // this warp has read its last record byte of the tile; when all have, the
+                    // state boxes may come in
+                    if (full_next(kc) >= kEncChunks) mbar_arrive(sm.bar(REC_DONE));
+                }
             }
-            if (C::kAlias && (kc == kLastWg1 || kc == kEncChunks - 1) && lane == 0)
-                mbar_arrive(sm.bar(REC_DONE));
             {
                 uint32_t lo[16], hi[16];
 #pragma unroll
@@ -1010,17 +1122,26 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
 
         // ---- MinGRU layers: both warpgroups work on every 64-unit slice; wg handles units
         // [64 j + 32 wg, 64 j + 32 wg + 32) = state box 2 j + wg of the layer
+        // Here too the next barrier is probed while other work runs: the state box while the
+        // accumulator is read, the next accumulator (or the heads) while the cell's last stores
+        // drain.
+        CFX_PROBE_CLEAR(cfx_p_g);
         for (int l = 0; l < P.L; l++) {
             const uint32_t a_cur = tmem + lane_base + ((l & 1) ? kColA1 : kColA0);
             const uint32_t a_next = tmem + lane_base + ((l & 1) ? kColA0 : kColA1);
             for (int j = 0; j < kSlices; j++, gcnt++) {
-                CFX_WAITW(G_FULL, gcnt & 1, W_G_FULL);
+                {
+                    uint32_t g_ok;
+                    CFX_PROBE_READ(cfx_p_g, g_ok);
+                    if (g_ok == 0) CFX_WAITW(G_FULL, gcnt & 1, W_G_FULL);
+                }
                 CFX_MARK(6);
                 tc_fence_after_sync();
                 const int box = 2 * j + wg;
                 const uint32_t scnt = (it * P.L + l) * kStateItems + box;
                 constexpr int kNS = C::kNS;
                 const int slot = scnt % kNS;
+                CFX_PROBE(cfx_p_s, sm.bar(S_FULL + slot), (scnt / kNS) & 1);
                 const uint32_t gcol = tmem + lane_base + kColG + kHalfUnits * wg;
                 uint8_t* rbase = sm.s_slot(slot) + (row >> 3) * 1024 + (row & 7) * 128;
                 const int xr = row & 7;
@@ -1048,7 +1169,11 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                 __syncwarp();
                 if (lane == 0) arrive_mma(G_EMPTY);
                 CFX_MARK(7);
-                CFX_WAITW(S_FULL + slot, (scnt / kNS) & 1, W_S_FULL);
+                {
+                    uint32_t s_ok;
+                    CFX_PROBE_READ(cfx_p_s, s_ok);
+                    if (s_ok == 0) CFX_WAITW(S_FULL + slot, (scnt / kNS) & 1, W_S_FULL);
+                }
                 CFX_MARK(8);
 #pragma unroll
                 for (int hf = 0; hf < 2; hf++) {
@@ -1091,6 +1216,9 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                     }
                     tmem_st8(a_next + 16 * box + 8 * hf, hn);
                 }
+                // the next accumulator: the heads after the last slice of the last layer
+                if (l == P.L - 1 && j == kSlices - 1) CFX_PROBE(cfx_p_g, sm.bar(H_FULL), tcnt & 1);
+                else CFX_PROBE(cfx_p_g, sm.bar(G_FULL), (gcnt + 1) & 1);
                 tmem_wait_st();
                 tc_fence_before_sync();
                 fence_proxy_async_smem();
@@ -1110,7 +1238,11 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
         if (wg == 0 && valid)
             u = P.uniforms != nullptr ? P.uniforms[env]
                                       : philox_uniform(P.seed, P.env_offset + (uint64_t)env, step0);
-        CFX_WAITW(H_FULL, tcnt & 1, W_H_FULL);
+        {
+            uint32_t h_ok;
+            CFX_PROBE_READ(cfx_p_g, h_ok);
+            if (h_ok == 0) CFX_WAITW(H_FULL, tcnt & 1, W_H_FULL);
+        }
         CFX_MARK(10);
         tc_fence_after_sync();
         if (wg == 0) {
@@ -1131,21 +1263,39 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
 #pragma unroll
                 for (int a = 0; a < kA; a++) logits[a] = __uint_as_float(hv[a]) + bias[kH + a];
                 const float value = __uint_as_float(hv[kA]) + bias[kH + kA];
-                if (P.logits_av != nullptr && (kA + 1) % 4 != 0) {
+                if constexpr ((kA + 1) % 8 != 4) {
                     float* dst = P.logits_av + (size_t)env * (kA + 1);   // rows are not 16-byte aligned
+                    if (P.logits_av != nullptr) {
 #pragma unroll
-                    for (int a = 0; a < kA; a++) dst[a] = logits[a];
-                    dst[kA] = value;
+                        for (int a = 0; a < kA; a++) dst[a] = logits[a];
+                        dst[kA] = value;
+                    }
                 } else if (P.logits_av != nullptr) {
-                    float4* dst = reinterpret_cast<float4*>(P.logits_av + (size_t)env * (kA + 1));
+                    // A row is 176 bytes: 32-byte aligned for even envs, 16 bytes off for odd
+                    // ones.  It goes out as five 32-byte stores and one 16-byte store (in front
+                    // for odd envs, at the end for even ones): whole sectors, and 6 store
+                    // instructions per warp instead of 11.  (The store burst of the sampler
+                    // holds up every shared-memory and barrier operation of the SM behind it.)
+                    constexpr int kRow = kA + 1;
+                    static_assert(kRow % 8 == 4, "row = five 32-byte pieces and one 16-byte piece");
+                    float rowv[kRow];
 #pragma unroll
-                    for (int q = 0; q < (kA + 1) / 4; q++) {
-                        float4 v4;
-                        v4.x = logits[4 * q];
-                        v4.y = logits[4 * q + 1];
-                        v4.z = logits[4 * q + 2];
-                        v4.w = (4 * q + 3 < kA) ? logits[(4 * q + 3 < kA) ? 4 * q + 3 : 0] : value;
-                        dst[q] = v4;
+                    for (int a = 0; a < kA; a++) rowv[a] = logits[a];
+                    rowv[kA] = value;
+                    float* dst = P.logits_av + (size_t)env * kRow;
+                    const bool odd = (env & 1) != 0;
+                    float4 v4;
+                    v4.x = odd ? rowv[0] : rowv[kRow - 4];
+                    v4.y = odd ? rowv[1] : rowv[kRow - 3];
+                    v4.z = odd ? rowv[2] : rowv[kRow - 2];
+                    v4.w = odd ? rowv[3] : rowv[kRow - 1];
+                    *reinterpret_cast<float4*>(dst + (odd ? 0 : kRow - 4)) = v4;
+#pragma unroll
+                    for (int q = 0; q < kRow / 8; q++) {
+                        float v8[8];
+#pragma unroll
+                        for (int e = 0; e < 8; e++) v8[e] = odd ? rowv[8 * q + 4 + e] : rowv[8 * q + e];
+                        st_global_v8(dst + 8 * q + (odd ? 4 : 0), v8);
                     }
                 }
                 float lp;
@@ -1172,6 +1322,14 @@ k_policy_fused(const __grid_constant__ Params P) {
     using C = Cfg<PAIR, GAME, HID>;
     CFX_DIMS(HID);
     constexpr int kA = Gm<GAME>::kA;
+    // predicates of the deferred probes: MMA thread (weights, operand chunks), workers (operand
+    // slot, records, state box, next accumulator)
+    CFX_PROBE_DECL(cfx_p_b);
+    CFX_PROBE_DECL(cfx_p_a);
+    CFX_PROBE_DECL(cfx_p_ae);
+    CFX_PROBE_DECL(cfx_p_r);
+    CFX_PROBE_DECL(cfx_p_s);
+    CFX_PROBE_DECL(cfx_p_g);
     extern __shared__ uint8_t smem_raw[];
     Smem sm;
     sm.base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -1188,7 +1346,7 @@ k_policy_fused(const __grid_constant__ Params P) {
         init(B_FULL, C::kNB, 1);   // pair: the even CTA's barrier also counts the odd CTA's bytes
         init(B_EMPTY, C::kNB, 1);
         init(S_FULL, C::kNS, 1);
-        init(S_DONE, C::kNS, 1);
+        init(S_FREE, C::kNS, 1);
         init(ST_READY, C::kNS, 4);
         init(R_FULL, C::kNR, 1);
         init(R_EMPTY, C::kNR, 4);
@@ -1200,9 +1358,9 @@ k_policy_fused(const __grid_constant__ Params P) {
         init(G_EMPTY, 1, 8 * both);
         init(H_FULL, 1, 1);
         init(H_EMPTY, 1, 4 * both);
-        init(REC_DONE, 1, 8);
-        init(T_FULL, 1, 1);
-        init(T_EMPTY, 1, GAME == CFX_GAME_CLASSIC ? 8 : 4);   // classic: both warpgroups read the buffer
+        init(REC_DONE, 1, 8);      // full game: every worker warp, after its last chunk
+        init(T_FULL, 1, 1);        // classic game: the record buffer, read by both warpgroups
+        init(T_EMPTY, 1, 8);
         *sm.abort_flag() = 0;
         fence_mbar_init();
     }
@@ -1235,13 +1393,13 @@ k_policy_fused(const __grid_constant__ Params P) {
     const uint32_t bar0_cta0 = PAIR ? map_to_cta(sm.bar(0), 0u) : 0u;
 
     if (warp == 0) {
-        if (lane < C::kWLanes) role_weight_loads<PAIR, GAME, HID>(sm, P, lane, rank, bar0_cta0);
+        if (lane == 0) role_weight_loads<PAIR, GAME, HID>(sm, P, lane, rank, bar0_cta0);
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) role_mma<T16, PAIR, GAME, HID>(sm, P, tmem);
     } else if (warp == 2) {
-        if (lane < C::kNR + 1) role_record_loads<PAIR, GAME, HID>(sm, P, lane);
+        if (lane == 0) role_loads<PAIR, GAME, HID>(sm, P);
     } else if (warp == 3) {
-        if (lane < C::kNS) role_state_ring<PAIR, GAME, HID>(sm, P, lane);
+        if (lane == 0) role_stores<PAIR, GAME, HID>(sm, P);
     } else {
         role_worker<T16, PAIR, GAME, HID>(sm, P, tmem, warp, lane, bar0_cta0);
     }
@@ -1439,7 +1597,7 @@ int fused_create(FusedPlan** out, int device, int n, int H, int L, int A, int pr
         // swizzled, so the copies are not.
         const bool classic = game == CFX_GAME_CLASSIC;
         const int kblocks = H / 64;
-        const int enc_chunks = classic ? fused::Gm<CFX_GAME_CLASSIC>::kEncChunks : fused::Gm<CFX_GAME_FULL>::kEncChunks;
+        const int enc_chunks = classic ? fused::Gm<CFX_GAME_CLASSIC>::kEncBlocks : fused::Gm<CFX_GAME_FULL>::kEncBlocks;
         const int head_pair = classic ? fused::Gm<CFX_GAME_CLASSIC>::kHeadPair : fused::Gm<CFX_GAME_FULL>::kHeadPair;
         const uint64_t rows[3] = {(uint64_t)enc_chunks * H, (uint64_t)L * (H / 64) * kblocks * 192,
                                   (uint64_t)kblocks * head_pair};

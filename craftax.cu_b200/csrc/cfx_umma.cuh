@@ -98,12 +98,32 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// 32-byte global store (sm_100: 256-bit stores); the address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(float* p, const float (&v)[8]) {
+    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(v[0]), "f"(v[1]),
+                 "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
+                 : "memory");
+}
+
+// Deferred probe.  mbar_test_wait reads its predicate right away, so the caller stalls for the
+// probe's shared-memory round trip (150-200 cycles inside the fused kernel, also when the phase
+// is long complete).  Here the predicate stays in a named register that is read later, and
+// whatever is issued in between overlaps the round trip.  A name is declared once per kernel,
+// at the top of the kernel body (CFX_PROBE_DECL), and cleared before its first read.
+#define CFX_PROBE_DECL(name) asm volatile(".reg .pred " #name ";\n\tsetp.ne.u32 " #name ", 0, 0;")
+#define CFX_PROBE(name, bar, parity)                                                   \
+    asm volatile("mbarrier.test_wait.parity.shared::cta.b64 " #name ", [%0], %1;" ::   \
+                     "r"(bar), "r"(parity) : "memory")
+#define CFX_PROBE_CLEAR(name) asm volatile("setp.ne.u32 " #name ", 0, 0;")
+#define CFX_PROBE_READ(name, out) asm volatile("selp.u32 %0, 1, 0, " #name ";" : "=r"(out) : : "memory")
+
 // Bounded wait: spins on try_wait; after kWaitLimitNs without completion (or as soon as
 // another thread of the CTA has given up) it records `code` in *abort_flag (shared
 // memory) and returns false.  Callers then skip their work and fall through to the
 // common exit, so a lost signal ends the kernel with an error status instead of a hang.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
+template <bool kBackoff = true>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile uint32_t* abort_flag, uint32_t code,
                                           uint64_t limit_ns = kWaitLimitNs) {
@@ -113,7 +133,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        __nanosleep(100);   // back off between probes: 1 % faster kernel than polling flat out
+        // back off between probes: 1 % faster kernel than polling flat out when whole warps wait;
+        // a single copy-issuing thread polls without it (its wake-up time is on the ring's path)
+        if (kBackoff) __nanosleep(100);
         // the timer and the abort flag are looked at only every 4096 failed polls: reading
         // %globaltimer costs a few hundred ns and must stay off the normal path
         if ((++spins & 4095u) == 0) {
