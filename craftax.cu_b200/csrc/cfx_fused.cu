@@ -142,7 +142,7 @@ enum Bar {
     AEXP_FULL = R_EMPTY + kNRMax, AEXP_EMPTY = AEXP_FULL + kAexpSlots,
     ACC_FULL = AEXP_EMPTY + kAexpSlots, A_KB = ACC_FULL + 1, G_FULL = A_KB + kKBlocksMax,
     G_EMPTY = G_FULL + 1, H_FULL = G_EMPTY + 1, H_EMPTY = H_FULL + 1, REC_DONE = H_EMPTY + 1,
-    T_FULL = REC_DONE + 1, T_EMPTY = T_FULL + 1, NUM_BARS = T_EMPTY + 1
+    ACC_READ = REC_DONE + 1, T_FULL = ACC_READ + 1, T_EMPTY = T_FULL + 1, NUM_BARS = T_EMPTY + 1
 };
 
 // Shared memory map (offsets from a 1024-byte aligned base) and the shapes that depend on the
@@ -184,7 +184,7 @@ constexpr int kWorkerWarp0 = 4, kNumWarps = 12, kThreads = kNumWarps * 32;
 // wait-site codes recorded in the status word when a bounded wait gives up
 enum WaitCode : uint32_t {
     W_B_EMPTY = 1, W_B_FULL, W_R_EMPTY, W_R_FULL, W_S_EMPTY, W_S_FULL, W_ST_READY, W_AEXP_EMPTY,
-    W_AEXP_FULL, W_ACC_FULL, W_A_KB, W_G_FULL, W_G_EMPTY, W_H_FULL, W_H_EMPTY, W_REC_DONE, W_S_FREE, W_T_FULL, W_T_EMPTY
+    W_AEXP_FULL, W_ACC_FULL, W_A_KB, W_G_FULL, W_G_EMPTY, W_H_FULL, W_H_EMPTY, W_REC_DONE, W_S_FREE, W_T_FULL, W_T_EMPTY, W_ACC_READ
 };
 
 struct Params {
@@ -861,13 +861,13 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
             for (int j = 0; j < kSlices; j++, gcnt++) {
                 CFX_WAIT_LEADER(G_EMPTY, (gcnt & 1) ^ 1, W_G_EMPTY);
                 CFX_MARK(5);
-                // The gate accumulator overlaps the encoder accumulator, which the encoder
-                // epilogue of BOTH worker warpgroups reads until they have signalled their K
-                // blocks: the first gate MMA of a tile waits for all of them, not only for the K
-                // block it multiplies.
+                // The gate accumulator overlaps the encoder accumulator: the first gate MMA of a
+                // tile waits until every worker warp has moved its part of it to registers.
+                // (An early version waited only for the K block it multiplied while a warpgroup
+                // was still reading the accumulator: about one launch in a hundred changed 32
+                // rows of one tile.)
                 if (l == 0 && j == 0) {
-#pragma unroll
-                    for (int kb = 0; kb < kKBlocks; kb++) CFX_WAIT_LEADER(A_KB + kb, akb_use & 1, W_A_KB);
+                    CFX_WAIT_LEADER(ACC_READ, tcnt & 1, W_ACC_READ);
                     CFX_MARK(9);
                 }
 #pragma unroll
@@ -882,7 +882,7 @@ __device__ __forceinline__ void role_mma(const Smem& sm, const Params& P, uint32
                     for (int c2 = 0; c2 < kStageBlocks; c2++) {
                         const int kb = kStageBlocks * kp + c2;
                         // the layer's input arrives K block by K block (slice kb of the previous layer)
-                        if (j == 0 && l != 0) {
+                        if (j == 0) {
                             CFX_WAIT_LEADER(A_KB + kb, akb_use & 1, W_A_KB);
                             CFX_MARK(9);
                         }
@@ -1090,32 +1090,41 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
             CFX_MARK(4);
         }
 
-        // ---- encoder epilogue: accumulator + bias -> layer-0 input A0 (wg = unit half)
+        // ---- encoder epilogue: accumulator + bias -> layer-0 input A0.  Like in the gate
+        // layers, warpgroup wg handles units [64 kb + 32 wg, 64 kb + 32 wg + 32) of K block kb.
+        // The whole accumulator goes to registers first and is handed back at once (ACC_READ):
+        // the gate accumulator overlaps it, and the first slice's MMAs then start on K block 0
+        // while the later blocks are still being converted.
         CFX_WAITW(ACC_FULL, tcnt & 1, W_ACC_FULL);
         CFX_MARK(5);
         tc_fence_after_sync();
-#pragma unroll 2
-        for (int b = 0; b < kH / 32; b++) {   // this warpgroup's kH / 2 units, 16 at a time
-            uint32_t acc[16], pk[8];
-            tmem_ld16(tmem + lane_base + kColAcc + (kH / 2) * wg + 16 * b, acc);
+        {
+            uint32_t acc[kKBlocks][32];
+#pragma unroll
+            for (int kb = 0; kb < kKBlocks; kb++) {
+                uint32_t t0[16], t1[16];
+                tmem_ld16(tmem + lane_base + kColAcc + kSliceUnits * kb + kHalfUnits * wg, t0);
+                tmem_ld16(tmem + lane_base + kColAcc + kSliceUnits * kb + kHalfUnits * wg + 16, t1);
+#pragma unroll
+                for (int q = 0; q < 16; q++) { acc[kb][q] = t0[q]; acc[kb][16 + q] = t1[q]; }
+            }
             tmem_wait_ld();
-            const float* bb = bias + (kH / 2) * wg + 16 * b;
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) arrive_mma(ACC_READ);
 #pragma unroll
-            for (int q = 0; q < 8; q++)
-                pk[q] = Op::pack(__uint_as_float(acc[2 * q]) + bb[2 * q],
-                                 __uint_as_float(acc[2 * q + 1]) + bb[2 * q + 1]);
-            tmem_st8(tmem + lane_base + kColA0 + (kH / 4) * wg + 8 * b, pk);
-        }
-        tmem_wait_st();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) {
-            // the K blocks this warpgroup wrote; two arrivals each stand for the two
-            // warpgroups that arrive per K block in the gate layers
+            for (int kb = 0; kb < kKBlocks; kb++) {
+                uint32_t pk[16];
+                const float* bb = bias + kSliceUnits * kb + kHalfUnits * wg;
 #pragma unroll
-            for (int kb = 0; kb < kKBlocks / 2; kb++) {
-                arrive_mma(A_KB + (kKBlocks / 2) * wg + kb);
-                arrive_mma(A_KB + (kKBlocks / 2) * wg + kb);
+                for (int q = 0; q < 16; q++)
+                    pk[q] = Op::pack(__uint_as_float(acc[kb][2 * q]) + bb[2 * q],
+                                     __uint_as_float(acc[kb][2 * q + 1]) + bb[2 * q + 1]);
+                tmem_st16(tmem + lane_base + kColA0 + (kSliceUnits / 2) * kb + (kHalfUnits / 2) * wg, pk);
+                tmem_wait_st();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) arrive_mma(A_KB + kb);
             }
         }
         CFX_MARK(1);
@@ -1358,6 +1367,7 @@ k_policy_fused(const __grid_constant__ Params P) {
         init(G_EMPTY, 1, 8 * both);
         init(H_FULL, 1, 1);
         init(H_EMPTY, 1, 4 * both);
+        init(ACC_READ, 1, 8 * both);
         init(REC_DONE, 1, 8);      // full game: every worker warp, after its last chunk
         init(T_FULL, 1, 1);        // classic game: the record buffer, read by both warpgroups
         init(T_EMPTY, 1, 8);
