@@ -671,7 +671,7 @@ def main():
 
 DEFAULT_PRECISION = "f16"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, per env (ncu captures in profiles/)
-NCU_DRAM_BYTES_PER_ENV = {(256, 2): (824.78e6 + 531.57e6) / 262144, (128, 2): (265.94e6 + 109.82e6) / 131072}
+NCU_DRAM_BYTES_PER_ENV = {(256, 2): (824.78e6 + 531.57e6) / 262144, (128, 2): (265.90e6 + 111.43e6) / 131072}
 NCU_DRAM_SOURCE = {(256, 2): "ncu capture of one launch at 262,144 envs",
                    (128, 2): "ncu capture at 131,072 envs, scaled by envs (part of the writes was still in L2)"}
 
