@@ -1280,9 +1280,9 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                         dst[kA] = value;
                     }
                 } else if (P.logits_av != nullptr) {
-                    // A row is 176 bytes: 32-byte aligned for even envs, 16 bytes off for odd
-                    // ones.  It goes out as five 32-byte stores and one 16-byte store (in front
-                    // for odd envs, at the end for even ones): whole sectors, and 6 store
+                    // A row is 176 bytes: 32-byte aligned for every other env, 16 bytes off for the
+                    // ones between.  It goes out as five 32-byte stores and one 16-byte store (in
+                    // front for the rows that are off, at the end for the others): whole sectors, and 6 store
                     // instructions per warp instead of 11.  (The store burst of the sampler
                     // holds up every shared-memory and barrier operation of the SM behind it.)
                     constexpr int kRow = kA + 1;
@@ -1292,7 +1292,8 @@ __device__ __forceinline__ void role_worker(const Smem& sm, const Params& P, uin
                     for (int a = 0; a < kA; a++) rowv[a] = logits[a];
                     rowv[kA] = value;
                     float* dst = P.logits_av + (size_t)env * kRow;
-                    const bool odd = (env & 1) != 0;
+                    // (the array itself need only be 16-byte aligned: what counts is the row's address)
+                    const bool odd = (reinterpret_cast<uintptr_t>(dst) & 31u) != 0;
                     float4 v4;
                     v4.x = odd ? rowv[0] : rowv[kRow - 4];
                     v4.y = odd ? rowv[1] : rowv[kRow - 3];

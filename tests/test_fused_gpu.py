@@ -310,3 +310,36 @@ def test_repeated_launches_are_bit_identical(cfx, gpu, oracle):
                 bad = np.nonzero(a != b)[0]
                 assert bad.size == 0, (rep, name, bad.size, bad[:8])
     pol.close()
+
+
+def test_logits_rows_in_an_array_that_is_only_16_byte_aligned(cfx, gpu, oracle):
+    """logits_av need only be 16-byte aligned.  The kernel writes a 176-byte row as five 32-byte
+    stores and one 16-byte store, placed by the row's own address; an array that starts 16
+    bytes into an allocation swaps the roles of the even and the odd rows and must give the
+    same rows, with nothing written outside them."""
+    n = 288   # ragged: the last tile has 32 rows
+    rng = np.random.default_rng(5)
+    rec = oracle.synthetic_records(n, seed=8)
+    params = oracle.init_weights(H, L, A, seed=3)
+    state = rng.normal(0, 1, (L, n, H)).astype(np.float32)
+    u = rng.random(n, dtype=np.float32)
+    pol = cfx.Policy(n, H, L, A, "f16")
+    pol.set_weights(params)
+    d_rec, d_u = cfx.DeviceBuffer.from_host(rec), cfx.DeviceBuffer.from_host(u)
+    d_act = cfx.DeviceBuffer((n,), np.int32)
+    rows = {}
+    for shift in (0, 4):   # floats: 0 and 16 bytes
+        guard = np.full(n * (A + 1) + 8, -7.5, np.float32)
+        d_all = cfx.DeviceBuffer.from_host(guard)
+
+        class View:   # a DeviceBuffer-like view that starts `shift` floats into the allocation
+            ptr = d_all.ptr + 4 * shift
+        pol.set_state(state)
+        pol.forward_device(d_rec, None, d_u, actions=d_act, logits_av=View, seed=1)
+        pol.check()
+        back = d_all.download()
+        assert np.all(back[:shift] == -7.5) and np.all(back[shift + n * (A + 1):] == -7.5)
+        rows[shift] = back[shift:shift + n * (A + 1)].reshape(n, A + 1).copy()
+    assert np.array_equal(rows[0].view(np.uint32), rows[4].view(np.uint32))
+    assert np.all(rows[0] != -7.5)
+    pol.close()
