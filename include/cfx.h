@@ -142,7 +142,7 @@ int cfx_policy_last_launches(const cfx_policy* p);
  * (CuVec.d_actions, read back by the env step), actions int32 [n], logprobs
  * float [n], values float [n]; logits_av float [n][A+1] = logits and value
  * WITH biases added (the reference's scratch holds them before the bias add,
- * :9725-9730); r_state [L][n][H] = post-zero state inputs for BPTT
+ * :9725-9730), 16-byte aligned base; r_state [L][n][H] = post-zero state inputs for BPTT
  * (:9370-9375), 16-byte aligned; fp32, or bf16 (__float2bfloat16 of the same
  * values, the reference's r_state_bf16 mode) when r_state_bf16 != 0.
  * The recurrent state is updated in place.  The step counter is bumped on
