@@ -117,14 +117,14 @@ template <int GAME, int HID> __host__ __device__ constexpr size_t enc_bytes() {
     return (size_t)Gm<GAME>::kEncBlocks * Hd<HID>::kEncBlockBytes;
 }
 
-// A lane that handles every G-th item of an N-slot ring waits on its slot's "empty" barrier
-// by phase parity; that is only sound while it cannot run two phases ahead of the slot,
-// i.e. while G <= N (its previous item, G back, already needed the slot use N+G back).
-// A ring shared by several consumers is only sound if every slot is always consumed by the
-// same consumer (a consumer that skips slots owned by others could otherwise be two phases
-// off): the record ring (one consumer, warpgroup 1) and the state ring (4 slots, slices
-// alternate) satisfy this; each weight ring has one consumer.
-
+// Barriers are waited on by phase parity, which is only sound while the waiter can never be
+// two phases off.  So every slot of a ring has ONE filling thread and ONE consuming warpgroup
+// for the whole launch (a consumer that skipped slots owned by others could be two phases
+// off), and both keep the slot's phase as a running count of their own uses: the record ring
+// (three slots per warpgroup), the state ring (4 slots, boxes alternate between the
+// warpgroups), the weight ring (one consumer).  The operand slots in tensor memory are shared
+// by the two warpgroups (chunk c and chunk c + 8 use the same slot); there the order is carried
+// by the previous tile's H_FULL, which both have passed.
 
 template <int GAME, int HID> __host__ __device__ constexpr size_t image_bytes(int L) {   // room for either head layout
     return enc_bytes<GAME, HID>() + (size_t)L * Hd<HID>::kSlices * Hd<HID>::kKBlocks * kGateBlockBytes +
@@ -465,13 +465,13 @@ struct Smem {
 #endif
 
 // every role runs in its own function: a failed (timed-out) wait returns to the common exit
-// Copy lanes and worker warps: every lane polls with try_wait (suspends while not ready).
+// Copy threads and worker warps poll with try_wait (suspends while not ready).
 // Measured alternatives, all slower on B200: one polling lane per worker warp plus a shuffle
 // (+25 % kernel time), a test_wait probe in front of the loop (+6 %).
 #define CFX_WAIT(barid, parity, code) \
     if (!mbar_wait(sm.bar(barid), (parity), sm.abort_flag(), (code))) return
 #define CFX_WAITW(barid, parity, code) CFX_WAIT(barid, parity, code)
-// the two ring-feeding threads: no back-off between probes
+// the three copy-issuing threads (weights, loads, stores): no back-off between probes
 #define CFX_WAIT_FAST(barid, parity, code) \
     if (!mbar_wait<false>(sm.bar(barid), (parity), sm.abort_flag(), (code))) return
 // The MMA role runs on ONE thread; the other lanes of its warp go straight to the exit.  (A
@@ -489,8 +489,8 @@ struct Smem {
 // warpgroup 0 samples the previous tile's actions first: warpgroup 1 converts chunks 0, 1, 2 and
 // then the even chunks, warpgroup 0 the odd chunks from 3 on, so that the MMA thread, which
 // consumes the chunks in order, finds the two warpgroups working on neighbouring chunks.  Each
-// warpgroup has three ring slots of its own and one lane of the record warp that issues its
-// fills in order.  With one producer and one consumer per slot, both sides keep a slot's phase
+// warpgroup has three ring slots of its own, filled in order by one thread (the load thread for
+// warpgroup 1, the store thread for warpgroup 0: see role_loads).  With one producer and one consumer per slot, both sides keep a slot's phase
 // as a running count of their own uses.  (The classic game shares its record buffer between
 // the warpgroups: even chunks warpgroup 1, odd ones warpgroup 0.)
 __device__ __forceinline__ int rec_owner(int kc) { return (kc & 1) ^ 1; }
@@ -510,8 +510,8 @@ __device__ __forceinline__ int full_rslot(int kc) {
 // Software prefetch into L2.  The rings are far too small to cover HBM latency at the rate the
 // encoder and the cell consume, so every byte a ring will load is requested from HBM ahead of
 // time in 16 KB pieces, and the ring loads then hit L2 (hundreds of cycles instead of
-// thousands).  The state-ring lanes issue the pieces, a few with every state box they serve,
-// which spreads them over the gate phases (one burst per tile delayed that tile's own loads by
+// thousands).  The load thread issues the pieces, a few with every pair of state boxes it
+// loads, which spreads them over the gate phases (one burst per tile delayed that tile's own loads by
 // thousands of cycles) and keeps the distance to the use short (a whole tile ahead, part of
 // the data had been evicted again):
 //   while layer l < L-1 runs   -> the state rows of layer l+1 of the same tile
@@ -548,7 +548,7 @@ __device__ __forceinline__ void l2_prefetch_for_box(const Params& P, int tile, i
 // ------------------------------------------------------------------ producer roles
 // Weight stages: the image is laid out in consumption order, so stage s of a tile starts
 // where stage s-1 ended; every tile replays the same sequence (it stays L2 resident).
-// One lane per ring slot.  In a CTA pair every CTA stages its own half of the rows of each
+// In a CTA pair every CTA stages its own half of the rows of each
 // stage (contiguous in the image) with a tensor copy whose completion is counted on the even
 // CTA's "full" barrier, where the MMA thread waits; one CTA per tile uses plain bulk copies.
 template <bool PAIR, int GAME, int HID>
