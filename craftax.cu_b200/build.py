@@ -18,6 +18,7 @@ UNITS = {
     "cfx_api.cu": [],
     "cfx_strict.cu": ["-fmad=false"],
     "cfx_fused.cu": [],
+    "cfx_record.cu": [],
 }
 
 

@@ -65,6 +65,10 @@ _SIGS = {
     "cfx_classic_expand_obs": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "cfx_classic_done_to_terminals": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "cfx_expand_obs": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    # record write from the reference's device state (the view is a cfx_env_view filled in C)
+    "cfx_record_obs": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "cfx_record_obs_list": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p,
+                                      C.c_void_p]),
     "cfx_sample_actions": (C.c_int, [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int,
                                      C.c_void_p, C.c_void_p, C.c_void_p]),
     "cfx_philox_uniforms": (C.c_int, [C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_int,

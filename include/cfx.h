@@ -245,6 +245,74 @@ int cfx_timer_elapsed_ms(void* timer, float* ms); /* synchronises on the stop ev
 const char* cfx_last_error(void);
 const char* cfx_version(void);
 
+/* ---- record write (reference k_record_obs / cf_record_env_warp, craftax_full.cu:9180-9297,
+ * call site cu_encode_step :11933-11953) ------------------------------------------------
+ * Writes the 996-byte compact record of every env from the env state the reference keeps on
+ * the device, byte for byte what k_record_obs writes: 99 view cells (9 rows x 11 columns
+ * around the player) x 8 bytes {block, item + 1, lit flag, five mob-class bytes (type + 1)},
+ * zero for cells that are off the map or not lit (light_map <= 12), then the 51 raw fp32
+ * scalars of craftax_encode_scalar_observation_tail_at (:2429-2487).
+ * cfx_env_view describes that state without naming the reference's structs: the SoA fields
+ * (CF_SOA_FIELDS, :620-690; element i of env e of a field is field[i * num_envs + e], bool
+ * fields are one byte) and the three byte maps [9][48][48] inside the per-env block of
+ * state_stride bytes.  All pointers are device pointers; nothing is copied or retained.
+ * skip (optional, uint8 [n]): envs whose flag is non-zero are left untouched (the reference
+ * records those after their reset has been joined, k_record_obs_list :9303-9319);
+ * cfx_record_obs_list writes exactly the envs listed in `list` (entries of list_stride bytes
+ * whose first int32 is the env index, e.g. CraftaxResetRec :8707-8711; *count_dev entries).
+ * Asynchronous on `stream`, no allocation, capturable in a CUDA graph. */
+typedef struct cfx_env_view {
+    int32_t num_envs;
+    const uint8_t* state_base;
+    uint64_t state_stride;
+    uint64_t map_offset, item_map_offset, light_map_offset;
+    const int32_t* player_position; /* [2]: row, column */
+    const int32_t* player_level;
+    const int32_t* player_direction;
+    const float* player_health;
+    const int32_t* player_food;
+    const int32_t* player_drink;
+    const int32_t* player_energy;
+    const int32_t* player_mana;
+    const uint8_t* is_sleeping;
+    const uint8_t* is_resting;
+    const int32_t* player_xp;
+    const int32_t* player_dexterity;
+    const int32_t* player_strength;
+    const int32_t* player_intelligence;
+    const int32_t* inv_wood;
+    const int32_t* inv_stone;
+    const int32_t* inv_coal;
+    const int32_t* inv_iron;
+    const int32_t* inv_diamond;
+    const int32_t* inv_sapling;
+    const int32_t* inv_pickaxe;
+    const int32_t* inv_sword;
+    const int32_t* inv_bow;
+    const int32_t* inv_arrows;
+    const int32_t* inv_torches;
+    const int32_t* inv_ruby;
+    const int32_t* inv_sapphire;
+    const int32_t* inv_books;
+    const int32_t* inv_armour;          /* [4] */
+    const int32_t* inv_potions;         /* [6] */
+    const uint8_t* learned_spells;      /* [2] */
+    const int32_t* sword_enchantment;
+    const int32_t* bow_enchantment;
+    const int32_t* armour_enchantments; /* [4] */
+    const int32_t* boss_timesteps_to_spawn_this_round;
+    const float* light_level;
+    const int32_t* monsters_killed;     /* [9] */
+    const int32_t* mob_position;        /* [5 classes][9 levels][3 slots][2] */
+    const uint8_t* mob_mask;            /* [5][9][3] */
+    const int32_t* mob_type_id;         /* [5][9][3] */
+} cfx_env_view;
+
+int cfx_record_obs(int device, const cfx_env_view* view, uint8_t* records, int n,
+                   const uint8_t* skip, void* stream);
+int cfx_record_obs_list(int device, const cfx_env_view* view, uint8_t* records, const void* list,
+                        int list_stride, const int* count_dev, void* stream);
+
 /* ---- classic game (reference craftax_classic.cu, boundary Rollout::step in
  * main_classic.cu:439-474) ------------------------------------------------------------
  * Same handle type and the same calls as the full game (set_weights, state, step counter,

@@ -307,6 +307,24 @@ class RefCuda:
             raise RuntimeError("refcu_lockstep: a cfx call failed (see stderr)")
         return dict(zip(cls.LOCKSTEP_KEYS, out.tolist()))
 
+    RECORD_KEYS = ("differing_bytes", "rows_compared", "reference_ms", "cfx_ms", "rows_with_mob",
+                   "list_differing_bytes")
+
+    @classmethod
+    def record_parity(cls, layers, n, steps, fuzz, seed):
+        """k_record_obs (craftax_full.cu:9284-9297) beside cfx_record_obs on the reference's CUDA env:
+        `steps` steps of random play, then `fuzz` rounds of randomised state; the list variant on
+        the last reset list; both kernels timed at n envs.  libcfx.so must be loaded first."""
+        L = C.CDLL(cls.path(layers))
+        if not hasattr(L, "refcu_record_parity"):
+            raise RuntimeError("reference shim built without the record comparison")
+        L.refcu_record_parity.argtypes = [C.c_int, C.c_int, C.c_int, C.c_ulonglong, C.c_void_p]
+        out = np.zeros(8, np.float64)
+        rc = L.refcu_record_parity(n, steps, fuzz, seed, _p(out))
+        if rc != 0:
+            raise RuntimeError("refcu_record_parity: a cfx call failed (see stderr)")
+        return dict(zip(cls.RECORD_KEYS, out.tolist()))
+
     @classmethod
     def play(cls, layers, n, steps, seed, load_path, swapped, precision, record_n, record_every,
              frames_path, levels_path):

@@ -613,6 +613,199 @@ int refcu_lockstep(int n, int steps, unsigned long long seed, const float* host_
     cu_vec_free(&v);
     return rc;
 }
+
+/* ---- record write: k_record_obs (:9284-9297) beside cfx_record_obs ----
+ * refcu_fill_view describes the reference's device state to the library without naming its
+ * structs (the binding a maintainer would add): the SoA field pointers are read back from the
+ * g_cf_* symbols cu_vec_init set (:10762-10775), the byte maps are located with offsetof.
+ * refcu_record_parity plays `steps` steps with uniformly random actions, writing the records of
+ * every step with both kernels and counting the bytes that differ; it then overwrites the
+ * fields the record reads with random values (`fuzz` rounds: positions on and off the map,
+ * mob slots of every level, type ids in and out of range, random light and block bytes) and
+ * compares again: the writer is a pure function of that memory.  It also times both kernels. */
+static void refcu_fill_view(const CuVec* v, cfx_env_view* w) {
+    memset(w, 0, sizeof(*w));
+    w->num_envs = v->num_envs;
+    w->state_base = (const uint8_t*)v->d_states;
+    w->state_stride = sizeof(CraftaxState);
+    w->map_offset = offsetof(CraftaxWorldState, map);
+    w->item_map_offset = offsetof(CraftaxWorldState, item_map);
+    w->light_map_offset = offsetof(CraftaxWorldState, light_map);
+#define REFCU_VIEW(f, T) { void* q = NULL; CU_CHECK(cudaMemcpyFromSymbol(&q, g_cf_##f, sizeof(q))); w->f = (const T*)q; }
+    REFCU_VIEW(player_position, int32_t) REFCU_VIEW(player_level, int32_t) REFCU_VIEW(player_direction, int32_t)
+    REFCU_VIEW(player_health, float) REFCU_VIEW(player_food, int32_t) REFCU_VIEW(player_drink, int32_t)
+    REFCU_VIEW(player_energy, int32_t) REFCU_VIEW(player_mana, int32_t) REFCU_VIEW(is_sleeping, uint8_t)
+    REFCU_VIEW(is_resting, uint8_t) REFCU_VIEW(player_xp, int32_t) REFCU_VIEW(player_dexterity, int32_t)
+    REFCU_VIEW(player_strength, int32_t) REFCU_VIEW(player_intelligence, int32_t) REFCU_VIEW(inv_wood, int32_t)
+    REFCU_VIEW(inv_stone, int32_t) REFCU_VIEW(inv_coal, int32_t) REFCU_VIEW(inv_iron, int32_t)
+    REFCU_VIEW(inv_diamond, int32_t) REFCU_VIEW(inv_sapling, int32_t) REFCU_VIEW(inv_pickaxe, int32_t)
+    REFCU_VIEW(inv_sword, int32_t) REFCU_VIEW(inv_bow, int32_t) REFCU_VIEW(inv_arrows, int32_t)
+    REFCU_VIEW(inv_torches, int32_t) REFCU_VIEW(inv_ruby, int32_t) REFCU_VIEW(inv_sapphire, int32_t)
+    REFCU_VIEW(inv_books, int32_t) REFCU_VIEW(inv_armour, int32_t) REFCU_VIEW(inv_potions, int32_t)
+    REFCU_VIEW(learned_spells, uint8_t) REFCU_VIEW(sword_enchantment, int32_t) REFCU_VIEW(bow_enchantment, int32_t)
+    REFCU_VIEW(armour_enchantments, int32_t) REFCU_VIEW(boss_timesteps_to_spawn_this_round, int32_t)
+    REFCU_VIEW(light_level, float) REFCU_VIEW(monsters_killed, int32_t) REFCU_VIEW(mob_position, int32_t)
+    REFCU_VIEW(mob_mask, uint8_t) REFCU_VIEW(mob_type_id, int32_t)
+#undef REFCU_VIEW
+}
+
+static __device__ __forceinline__ uint32_t refcu_hash(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t h = a * 0x9E3779B1u ^ (b + 0x7F4A7C15u) * 0x85EBCA77u ^ (c + 0x165667B1u) * 0xC2B2AE3Du;
+    h ^= h >> 15; h *= 0x2C1B3C6Du; h ^= h >> 12; h *= 0x297A2D39u; h ^= h >> 15;
+    return h;
+}
+__global__ void refcu_k_random_actions(float* actions, int n, uint32_t seed, uint32_t step) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e < n) actions[e] = (float)(refcu_hash(seed, step, (uint32_t)e) % CRAFTAX_NUM_ACTIONS);
+}
+__global__ void refcu_k_count_diff(const uint8_t* a, const uint8_t* b, size_t bytes, unsigned long long* out) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    unsigned long long d = 0;
+    for (; i < bytes; i += (size_t)gridDim.x * blockDim.x) d += a[i] != b[i];
+    if (d) atomicAdd(out, d);
+}
+/* overwrites what the record reads: one thread per env (round r of the fuzz) */
+__global__ void refcu_k_fuzz_state(cfx_env_view w, uint32_t seed, uint32_t r) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    const int n = w.num_envs;
+    if (e >= n) return;
+    uint32_t k = 0;
+    auto rnd = [&](uint32_t mod) { return refcu_hash(seed + r * 977u, k++, (uint32_t)e) % mod; };
+    auto I = [&](const int32_t* f, int i) -> int32_t& { return const_cast<int32_t*>(f)[(size_t)i * n + e]; };
+    auto B = [&](const uint8_t* f, int i) -> uint8_t& { return const_cast<uint8_t*>(f)[(size_t)i * n + e]; };
+    auto F = [&](const float* f, int i) -> float& { return const_cast<float*>(f)[(size_t)i * n + e]; };
+    const int level = (int)rnd(CRAFTAX_WG_NUM_LEVELS);
+    I(w.player_level, 0) = level;
+    I(w.player_position, 0) = (int)rnd(CRAFTAX_WG_MAP_SIZE);
+    I(w.player_position, 1) = (int)rnd(CRAFTAX_WG_MAP_SIZE);
+    I(w.player_direction, 0) = (int)rnd(6);
+    F(w.player_health, 0) = (float)rnd(100) * 0.125f;
+    const int32_t* small[] = {w.player_food, w.player_drink, w.player_energy, w.player_mana, w.player_xp,
+                              w.player_dexterity, w.player_strength, w.player_intelligence, w.inv_pickaxe,
+                              w.inv_sword, w.inv_bow, w.inv_books, w.sword_enchantment, w.bow_enchantment};
+    for (int i = 0; i < 14; i++) I(small[i], 0) = (int)rnd(10);
+    const int32_t* counts[] = {w.inv_wood, w.inv_stone, w.inv_coal, w.inv_iron, w.inv_diamond, w.inv_sapling,
+                               w.inv_arrows, w.inv_torches, w.inv_ruby, w.inv_sapphire};
+    for (int i = 0; i < 10; i++) I(counts[i], 0) = (int)rnd(100);
+    for (int i = 0; i < 4; i++) { I(w.inv_armour, i) = (int)rnd(3); I(w.armour_enchantments, i) = (int)rnd(3); }
+    for (int i = 0; i < 6; i++) I(w.inv_potions, i) = (int)rnd(30);
+    B(w.is_sleeping, 0) = (uint8_t)rnd(2); B(w.is_resting, 0) = (uint8_t)rnd(2);
+    B(w.learned_spells, 0) = (uint8_t)rnd(2); B(w.learned_spells, 1) = (uint8_t)rnd(2);
+    I(w.boss_timesteps_to_spawn_this_round, 0) = (int)rnd(5) - 2;
+    F(w.light_level, 0) = (float)rnd(1000) * 0.001f;
+    for (int l = 0; l < CRAFTAX_WG_NUM_LEVELS; l++) I(w.monsters_killed, l) = (int)rnd(16);
+    /* mobs of every class, level and slot: near the player, sometimes off the view or off the map */
+    const int pr = I(w.player_position, 0), pc = I(w.player_position, 1);
+    for (int m = 0; m < 5 * CRAFTAX_WG_NUM_LEVELS * 3; m++) {
+        I(w.mob_type_id, m) = (int)rnd(CRAFTAX_WG_NUM_MOB_TYPES + 2) - 1;
+        B(w.mob_mask, m) = (uint8_t)(rnd(4) != 0);
+        I(w.mob_position, 2 * m) = pr + (int)rnd(13) - 6;
+        I(w.mob_position, 2 * m + 1) = pc + (int)rnd(15) - 7;
+    }
+    /* the three byte maps of the player's level around the player */
+    uint8_t* blk = const_cast<uint8_t*>(w.state_base) + (size_t)e * w.state_stride;
+    for (int dr = -6; dr <= 6; dr++)
+        for (int dc = -7; dc <= 7; dc++) {
+            const int rr = pr + dr, cc = pc + dc;
+            if (rr < 0 || rr >= CRAFTAX_WG_MAP_SIZE || cc < 0 || cc >= CRAFTAX_WG_MAP_SIZE) continue;
+            const size_t o = ((size_t)level * CRAFTAX_WG_MAP_SIZE + rr) * CRAFTAX_WG_MAP_SIZE + cc;
+            blk[w.map_offset + o] = (uint8_t)rnd(40);
+            blk[w.item_map_offset + o] = (uint8_t)rnd(6);
+            blk[w.light_map_offset + o] = (uint8_t)rnd(26);
+        }
+}
+
+/* out[0] differing bytes over all compared rows, out[1] rows compared, out[2] / out[3] ms per call
+ * of k_record_obs / cfx_record_obs at n envs (CUDA events, 20 calls each), out[4] rows with a
+ * visible mob among the compared ones (coverage), out[5] differing bytes of the list variant. */
+int refcu_record_parity(int n, int steps, int fuzz, unsigned long long seed, double* out) {
+    CuVec v; CuPolicy p;
+    cu_vec_init(&v, n, seed);
+    cu_policy_init(&p, n);
+    cudaStream_t st = p.stream;
+    int dev = 0;
+    CU_CHECK(cudaGetDevice(&dev));
+    cfx_env_view w;
+    refcu_fill_view(&v, &w);
+    uint8_t *ra = NULL, *rb = NULL;
+    unsigned long long* d_cnt = NULL;
+    const size_t bytes = (size_t)n * CF_TRAIN_OBS;
+    CU_CHECK(cudaMalloc(&ra, bytes)); CU_CHECK(cudaMalloc(&rb, bytes));
+    CU_CHECK(cudaMalloc(&d_cnt, 4 * sizeof(unsigned long long)));
+    CU_CHECK(cudaMemset(d_cnt, 0, 4 * sizeof(unsigned long long)));
+    int rc = 0;
+    double rows = 0;
+    auto compare = [&]() {
+        CU_CHECK(cudaMemsetAsync(ra, 0xCD, bytes, st));
+        CU_CHECK(cudaMemsetAsync(rb, 0xEF, bytes, st));
+        k_record_obs<<<(int)(((size_t)n * 32 + 255) / 256), 256, 0, st>>>(ra, n);
+        if (cfx_record_obs(dev, &w, rb, n, NULL, st) != CFX_OK) { fprintf(stderr, "cfx: %s\n", cfx_last_error()); rc = 1; }
+        refcu_k_count_diff<<<1024, 256, 0, st>>>(ra, rb, bytes, d_cnt);
+        rows += n;
+    };
+    for (int t = 0; t < steps && rc == 0; t++) {
+        compare();
+        refcu_k_random_actions<<<(n + 255) / 256, 256, 0, st>>>(v.d_actions, n, (uint32_t)seed, (uint32_t)t);
+        refcu_roll r = {&v, &p, seed, NULL};
+        refcu_step_env_only(&r);
+        if ((t & 15) == 15) CU_CHECK(cudaStreamSynchronize(st));
+    }
+    /* the list variant on the last step's reset list (the envs that were just reset) */
+    if (rc == 0) {
+        CU_CHECK(cudaMemsetAsync(ra, 0xCD, bytes, st));
+        CU_CHECK(cudaMemsetAsync(rb, 0xCD, bytes, st));
+        k_record_obs_list<<<128, 256, 0, st>>>(ra, v.d_resets);
+        if (cfx_record_obs_list(dev, &w, rb, v.d_resets, (int)sizeof(CraftaxResetRec), v.d_reset_count, st) != CFX_OK) {
+            fprintf(stderr, "cfx: %s\n", cfx_last_error()); rc = 1;
+        }
+        refcu_k_count_diff<<<1024, 256, 0, st>>>(ra, rb, bytes, d_cnt + 1);
+    }
+    for (int r = 0; r < fuzz && rc == 0; r++) {
+        refcu_k_fuzz_state<<<(n + 127) / 128, 128, 0, st>>>(w, (uint32_t)seed, (uint32_t)r);
+        compare();
+    }
+    CU_CHECK(cudaStreamSynchronize(st));
+    /* timing, on the last state */
+    float ms_ref = 0.f, ms_cfx = 0.f;
+    {
+        cudaEvent_t a, b;
+        CU_CHECK(cudaEventCreate(&a)); CU_CHECK(cudaEventCreate(&b));
+        for (int k = 0; k < 3; k++) k_record_obs<<<(int)(((size_t)n * 32 + 255) / 256), 256, 0, st>>>(ra, n);
+        CU_CHECK(cudaEventRecord(a, st));
+        for (int k = 0; k < 20; k++) k_record_obs<<<(int)(((size_t)n * 32 + 255) / 256), 256, 0, st>>>(ra, n);
+        CU_CHECK(cudaEventRecord(b, st));
+        CU_CHECK(cudaStreamSynchronize(st));
+        CU_CHECK(cudaEventElapsedTime(&ms_ref, a, b));
+        for (int k = 0; k < 3; k++) cfx_record_obs(dev, &w, rb, n, NULL, st);
+        CU_CHECK(cudaEventRecord(a, st));
+        for (int k = 0; k < 20; k++) cfx_record_obs(dev, &w, rb, n, NULL, st);
+        CU_CHECK(cudaEventRecord(b, st));
+        CU_CHECK(cudaStreamSynchronize(st));
+        CU_CHECK(cudaEventElapsedTime(&ms_cfx, a, b));
+        cudaEventDestroy(a); cudaEventDestroy(b);
+    }
+    /* coverage: rows of the last comparison with a mob byte set */
+    unsigned long long cn[4];
+    CU_CHECK(cudaMemcpy(cn, d_cnt, sizeof(cn), cudaMemcpyDeviceToHost));
+    {
+        uint8_t* h = (uint8_t*)malloc(bytes);
+        CU_CHECK(cudaMemcpy(h, rb, bytes, cudaMemcpyDeviceToHost));
+        double with_mob = 0;
+        for (int e = 0; e < n; e++) {
+            int any = 0;
+            for (int c = 0; c < 99 && !any; c++)
+                for (int ch = 3; ch < 8; ch++) any |= h[(size_t)e * CF_TRAIN_OBS + c * 8 + ch] != 0;
+            with_mob += any;
+        }
+        out[4] = with_mob;
+        free(h);
+    }
+    out[0] = (double)cn[0]; out[1] = rows; out[2] = ms_ref / 20.0; out[3] = ms_cfx / 20.0; out[5] = (double)cn[1];
+    cudaFree(ra); cudaFree(rb); cudaFree(d_cnt);
+    cu_policy_free(&p);
+    cu_vec_free(&v);
+    return rc;
+}
 #endif
 
 

@@ -51,7 +51,7 @@ def test_fused_matches_oracle_on_env_records(cfx, gpu, oracle, golden_env, golde
     pol.close()
 
 
-@pytest.mark.parametrize("n,layers", [(32, 2), (96, 3), (160, 2), (416, 1), (128 * 5 + 64, 2)])
+@pytest.mark.parametrize("n,layers", [(32, 2), (96, 3), (160, 2), (416, 1), (128 * 5 + 64, 2), (288, 4)])
 def test_fused_ragged_sizes(cfx, gpu, oracle, n, layers):
     rng = np.random.default_rng(n)
     rec = oracle.synthetic_records(n, seed=4)

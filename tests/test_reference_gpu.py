@@ -229,3 +229,22 @@ def test_play_recording_with_the_forward_swapped_in(cfx, oracle, refcu, tmp_path
     agree = float((a_ref == a_cfx).mean())
     print(f"[play] first-step action agreement with the reference's own play run: {agree:.4f}")
     assert agree >= 0.95
+
+
+@pytest.mark.parametrize("n,steps,fuzz", [(2048, 96, 6), (262144, 4, 2)], ids=["play-and-fuzz", "full-size"])
+def test_record_write_equals_the_reference_kernel(cfx, oracle, refcu, n, steps, fuzz):
+    """cfx_record_obs writes the bytes k_record_obs writes (craftax_full.cu:9180-9297) from the
+    reference's own device state: over random play with resets, on the just-reset envs through
+    the list variant (k_record_obs_list), and on randomised state (mobs of every class on, off and
+    at the edge of the view, type ids out of range, every level, unlit cells)."""
+    if not refcu.available(2):
+        pytest.skip("oracle/_ref/libcfref_cuda_l2.so not built")
+    cfx.lib()
+    r = refcu.record_parity(2, n, steps, fuzz, seed=11)
+    print(f"[record] n={n}: {r['rows_compared']:.0f} rows, {r['differing_bytes']:.0f} differing bytes; "
+          f"k_record_obs {r['reference_ms']:.4f} ms, cfx_record_obs {r['cfx_ms']:.4f} ms; "
+          f"{r['rows_with_mob']:.0f} of the last {n} rows show a mob")
+    assert r["rows_compared"] == n * (steps + fuzz)
+    assert r["differing_bytes"] == 0
+    assert r["list_differing_bytes"] == 0
+    assert r["rows_with_mob"] > n // 4   # the randomised rounds put mobs into most views
