@@ -629,6 +629,12 @@ def run_ref_rollout(args):
         out["swapped_rollout"] = lib.refcu_rollout_swap_sps(n, iters, 1, 1, prec)
         out["R3_swapped_over_reference"] = out["swapped_rollout"] / out["reference_rollout"]
         out["amdahl_cap_env_only_over_reference"] = out["reference_env_only"] / out["reference_rollout"]
+    if hasattr(lib, "refcu_rollout_swap2_sps"):
+        # the record write swapped too (cfx_record_obs instead of k_record_obs)
+        lib.refcu_rollout_swap2_sps.restype = C.c_double
+        lib.refcu_rollout_swap2_sps.argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_int, C.c_int, C.c_int]
+        out["swapped_rollout_and_record"] = lib.refcu_rollout_swap2_sps(n, iters, 1, 1, prec, 1)
+        out["swapped_and_record_over_reference"] = out["swapped_rollout_and_record"] / out["reference_rollout"]
     print(json.dumps(out), flush=True)
 
 

@@ -361,12 +361,25 @@ double refcu_env_only_sps(int n, int iters, unsigned long long seed, int graph) 
 
 #ifdef CFX_REF_WITH_CFX
 #include "cfx.h"
+static void refcu_fill_view(const CuVec* v, cfx_env_view* w);
+/* non-NULL: the record write of the swapped step is cfx_record_obs on this view instead of
+ * k_record_obs (set by refcu_rollout_swap_sps for its swap_record mode) */
+static const cfx_env_view* g_refcu_record_view = NULL;
 static void refcu_step_swapped(void* c) {
     refcu_roll* r = (refcu_roll*)c;
     CuVec* v = r->v; CuPolicy* p = r->p;
     int n = v->num_envs;
     cudaStream_t st = p->stream;
-    k_record_obs<<<(int)(((size_t)n * 32 + 255) / 256), 256, 0, st>>>(p->rec, n);
+    if (g_refcu_record_view != NULL) {
+        int dev = 0;
+        CU_CHECK(cudaGetDevice(&dev));
+        if (cfx_record_obs(dev, g_refcu_record_view, p->rec, n, NULL, st) != CFX_OK) {
+            fprintf(stderr, "cfx: %s\n", cfx_last_error());
+            exit(1);
+        }
+    } else {
+        k_record_obs<<<(int)(((size_t)n * 32 + 255) / 256), 256, 0, st>>>(p->rec, n);
+    }
     CU_CHECK(cudaMemsetAsync(v->d_reset_count, 0, sizeof(int), st));
     CU_CHECK(cudaMemsetAsync(v->d_spawn_count, 0, sizeof(int), st));
     cfx_forward_io io;
@@ -392,10 +405,20 @@ static void refcu_step_swapped(void* c) {
 
 /* precision: a CFX_PREC_* code.  The reference policy is created too (its init allocates the
  * record scratch and the sampler outputs the loop writes); its weights are handed over. */
+double refcu_rollout_swap2_sps(int n, int iters, unsigned long long seed, int graph, int precision,
+                               int swap_record);
 double refcu_rollout_swap_sps(int n, int iters, unsigned long long seed, int graph, int precision) {
+    return refcu_rollout_swap2_sps(n, iters, seed, graph, precision, 0);
+}
+/* swap_record != 0: the record write is taken from the library too (cfx_record_obs) */
+double refcu_rollout_swap2_sps(int n, int iters, unsigned long long seed, int graph, int precision,
+                               int swap_record) {
     CuVec v; CuPolicy p;
     cu_vec_init(&v, n, seed);
     cu_policy_init(&p, n);
+    cfx_env_view view;
+    refcu_fill_view(&v, &view);
+    g_refcu_record_view = swap_record ? &view : NULL;
     int dev = 0;
     CU_CHECK(cudaGetDevice(&dev));
     cfx_policy* cp = NULL;
@@ -407,6 +430,7 @@ double refcu_rollout_swap_sps(int n, int iters, unsigned long long seed, int gra
     CU_CHECK(cudaDeviceSynchronize());
     refcu_roll r = {&v, &p, seed, cp};
     double sps = refcu_time_steps(&p, n, iters, graph, refcu_step_swapped, &r);
+    g_refcu_record_view = NULL;
     cfx_policy_destroy(cp);
     cu_policy_free(&p);
     cu_vec_free(&v);
