@@ -638,12 +638,41 @@ def run_ref_rollout(args):
     print(json.dumps(out), flush=True)
 
 
+def run_record(args):
+    """The record write alone: the reference's k_record_obs and this library's cfx_record_obs on
+    the reference's CUDA env (a few steps of random play, then randomised state), bytes
+    compared, both kernels timed with CUDA events (20 calls each)."""
+    rank, _, local = dist_env()
+    if rank != 0:
+        return
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import cfx
+    import oracle as O
+    n = args.envs
+    if cfx.device_count() < 1 or not O.RefCuda.available(2):
+        print(json.dumps({"impl": "record", "unavailable":
+                          "needs a GPU and oracle/_ref/libcfref_cuda_l2.so (reference sources absent)"}))
+        return
+    cfx.lib()
+    r = O.RefCuda.record_parity(2, n, 4, 2, seed=1)
+    # bytes the kernel must move per env: the record, the 3 x 99 map bytes, ~100 SoA words
+    algo = 996 + 3 * 99 + 4 * 100
+    peaks = load_peaks()
+    out = {"impl": "record", "envs": n, "differing_bytes": r["differing_bytes"], "rows_compared": r["rows_compared"],
+           "reference_k_record_obs_ms": r["reference_ms"], "cfx_record_obs_ms": r["cfx_ms"],
+           "speedup": r["reference_ms"] / r["cfx_ms"],
+           "roofline": {"bound": "hbm", "bytes_per_env": algo, "achieved": n * algo / (r["cfx_ms"] * 1e-3) / 1e9,
+                        "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": n * algo / (r["cfx_ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"]}}
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="cfx", choices=["cfx", "reference", "ref-cublas", "ref-rollout", "sweep", "classic"])
+    ap.add_argument("--impl", default="cfx", choices=["cfx", "reference", "ref-cublas", "ref-rollout", "sweep", "classic", "record"])
     ap.add_argument("--ref-mode", default="bf16", choices=["bf16", "tf32", "fp32"])
     ap.add_argument("--envs", type=int, default=262144, help="envs per GPU")
     ap.add_argument("--hidden", type=int, default=256)
@@ -671,6 +700,8 @@ def main():
         run_sweep(args)
     elif args.impl == "classic":
         run_classic(args)
+    elif args.impl == "record":
+        run_record(args)
     else:
         run_cfx(args)
 
