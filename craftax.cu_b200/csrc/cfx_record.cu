@@ -5,14 +5,15 @@
 // tail scalars; every one of its ~110 scalar loads then fetches 4 bytes of a sector on its own,
 // one after the other.  Here a block of four warps owns 32 consecutive envs and works in two
 // phases:
-//   1. thread per env (one warp): the ~50 SoA fields and the 14 mob slots of the player's level
-//      (type, mask, position, light at the position) are loaded by thread e for env e, so that
-//      the warp's loads of a field are one 128-byte line and all loads of a thread are
-//      independent; the thread leaves the 51 tail floats, the visible mobs (an earlier slot of a
-//      class that a later slot covers is dropped) and (level, top, left) in shared memory;
-//   2. warp per env (8 envs per warp): the 99 view cells, 8 bytes each from three byte maps, go
-//      out as coalesced 8-byte stores, then one lane per visible mob stores its byte, then the
-//      tail goes out as coalesced 4-byte stores from shared memory.
+//   1. lane per env: the ~50 SoA fields and the 14 mob slots of the player's level (type, mask,
+//      position, light at the position) are loaded by lane e for env e, so that a warp's loads
+//      of a field are one 128-byte line and all loads of a lane are independent; each warp takes
+//      a quarter of the fields; they leave the 51 tail floats, the visible mobs (an earlier slot
+//      of a class that a later slot covers is dropped) and (level, top, left) in shared memory;
+//   2. warp per env (8 envs per warp, the next env's loads in flight while one is stored): the
+//      99 view cells, 8 bytes each from three byte maps, go out as coalesced 8-byte stores,
+//      then one lane per visible mob stores its byte, then the tail goes out as coalesced
+//      4-byte stores from shared memory.
 // The bytes are the reference's: the same predicates, the same "last slot of a class wins a
 // cell" order, the same float expressions (sqrtf(x) * 0.1f, x * 0.1f, x * 0.5f, x * 0.25f; no
 // fused multiply-add can form).  HBM traffic per env: 996 B written, 27 map sectors (9 rows of
@@ -59,118 +60,131 @@ __device__ __forceinline__ T soa(const T* f, int elem, int n, int e) {
 // flat index of (class, level, slot) in the mob fields (CFM, :715)
 __device__ __forceinline__ int mob_index(int c, int level, int i) { return (c * kLevels + level) * kSlots + i; }
 
-// phase 1: everything of env e that does not depend on the cell
-__device__ __forceinline__ void gather_env(const cfx_env_view& V, int e, int t, Shared& S) {
+// phase 1: everything of env e that does not depend on the cell.  Lane t of EVERY warp of the
+// block works on env t of the block; warp `part` takes a quarter of the work:
+//   part 0: tail scalars 0-25        part 1: tail scalars 26-49
+//   part 2: mob classes 0-2 + the boss flag (tail scalar 50)        part 3: mob classes 3-4
+__device__ __forceinline__ void gather_env(const cfx_env_view& V, int e, int t, int part, Shared& S) {
     const int n = V.num_envs;
     const int level = soa(V.player_level, 0, n, e);
-    const int mob_level = jax_index(level, kLevels);
-    const int top = soa(V.player_position, 0, n, e) - kRows / 2;
-    const int left = soa(V.player_position, 1, n, e) - kCols / 2;
-    S.level[t] = level; S.top[t] = top; S.left[t] = left; S.env[t] = e;
-    const uint8_t* light = V.state_base + (size_t)e * V.state_stride + V.light_map_offset +
-                           (size_t)mob_level * kMapSize * kMapSize;
-
-    // visible mobs of the player's level, class-major, slot-minor (:9195-9236):
-    // packed = valid | cell << 8 | channel << 4 | value
-    bool melee_or_ranged = false;
-#pragma unroll
-    for (int m = 0; m < kMobs; m++) {
-        const int c = m / kSlots, i = m % kSlots;
-        uint32_t pk = 0;
-        if (i < (c == 2 ? 2 : 3)) {
-            const int idx = mob_index(c, mob_level, i);
-            const int type_id = soa(V.mob_type_id, idx, n, e);
-            const bool mask = soa(V.mob_mask, idx, n, e) != 0;
-            if (c == 0 || c == 2) melee_or_ranged = melee_or_ranged || mask;
-            const int mr = soa(V.mob_position, idx * 2, n, e), mc = soa(V.mob_position, idx * 2 + 1, n, e);
-            const int lr = mr - top, lc = mc - left;
-            if (type_id >= 0 && type_id < kMobTypes && mask && lr >= 0 && lr < kRows && lc >= 0 && lc < kCols &&
-                mr >= 0 && mr < kMapSize && mc >= 0 && mc < kMapSize && light[mr * kMapSize + mc] > kLit)
-                pk = 0x80000000u | (uint32_t)(lr * kCols + lc) << 8 | (uint32_t)(3 + c) << 4 | (uint32_t)(type_id + 1);
-        }
-        S.mobs[t][m] = pk;
-    }
-    // "last slot wins": within a class a later slot on the same cell replaces an earlier one
-    // (:9222-9231), so the earlier one is dropped here and the stores of phase 2 need no order
-#pragma unroll
-    for (int c = 0; c < kClasses; c++)
-#pragma unroll
-        for (int i = 0; i < kSlots - 1; i++)
-#pragma unroll
-            for (int i2 = i + 1; i2 < kSlots; i2++) {
-                const uint32_t a = S.mobs[t][c * kSlots + i], b = S.mobs[t][c * kSlots + i2];
-                if ((a & b & 0x80000000u) && ((a ^ b) & 0xFF00u) == 0) S.mobs[t][c * kSlots + i] = 0;
-            }
-
-    // the 51 scalars in the order of craftax_encode_scalar_observation_tail_at (:2429-2487)
     float* o = S.tail[t];
     int k = 0;
     auto sq10 = [&](const int32_t* f, int i) { o[k++] = sqrtf((float)soa(f, i, n, e)) * (1.0f / 10.0f); };
     auto mul = [&](const int32_t* f, int i, float m) { o[k++] = (float)soa(f, i, n, e) * m; };
     auto flag = [&](bool b) { o[k++] = b ? 1.0f : 0.0f; };
-    sq10(V.inv_wood, 0); sq10(V.inv_stone, 0); sq10(V.inv_coal, 0); sq10(V.inv_iron, 0); sq10(V.inv_diamond, 0);
-    sq10(V.inv_sapphire, 0); sq10(V.inv_ruby, 0); sq10(V.inv_sapling, 0); sq10(V.inv_torches, 0); sq10(V.inv_arrows, 0);
-    mul(V.inv_books, 0, 1.0f / 2.0f);
-    mul(V.inv_pickaxe, 0, 1.0f / 4.0f);
-    mul(V.inv_sword, 0, 1.0f / 4.0f);
-    o[k++] = (float)soa(V.sword_enchantment, 0, n, e);
-    o[k++] = (float)soa(V.bow_enchantment, 0, n, e);
-    o[k++] = (float)soa(V.inv_bow, 0, n, e);
+    // the 51 scalars in the order of craftax_encode_scalar_observation_tail_at (:2429-2487)
+    if (part == 0) {
+        sq10(V.inv_wood, 0); sq10(V.inv_stone, 0); sq10(V.inv_coal, 0); sq10(V.inv_iron, 0);
+        sq10(V.inv_diamond, 0); sq10(V.inv_sapphire, 0); sq10(V.inv_ruby, 0); sq10(V.inv_sapling, 0);
+        sq10(V.inv_torches, 0); sq10(V.inv_arrows, 0);
+        mul(V.inv_books, 0, 1.0f / 2.0f);
+        mul(V.inv_pickaxe, 0, 1.0f / 4.0f);
+        mul(V.inv_sword, 0, 1.0f / 4.0f);
+        o[k++] = (float)soa(V.sword_enchantment, 0, n, e);
+        o[k++] = (float)soa(V.bow_enchantment, 0, n, e);
+        o[k++] = (float)soa(V.inv_bow, 0, n, e);
 #pragma unroll
-    for (int i = 0; i < 6; i++) sq10(V.inv_potions, i);
-    o[k++] = soa(V.player_health, 0, n, e) * (1.0f / 10.0f);
-    mul(V.player_food, 0, 1.0f / 10.0f); mul(V.player_drink, 0, 1.0f / 10.0f);
-    mul(V.player_energy, 0, 1.0f / 10.0f); mul(V.player_mana, 0, 1.0f / 10.0f);
-    mul(V.player_xp, 0, 1.0f / 10.0f); mul(V.player_dexterity, 0, 1.0f / 10.0f);
-    mul(V.player_strength, 0, 1.0f / 10.0f); mul(V.player_intelligence, 0, 1.0f / 10.0f);
-    const int direction_index = soa(V.player_direction, 0, n, e) - 1;
+        for (int i = 0; i < 6; i++) sq10(V.inv_potions, i);
+        o[k++] = soa(V.player_health, 0, n, e) * (1.0f / 10.0f);
+        mul(V.player_food, 0, 1.0f / 10.0f); mul(V.player_drink, 0, 1.0f / 10.0f);
+        mul(V.player_energy, 0, 1.0f / 10.0f);   // scalar 25
+        return;
+    }
+    if (part == 1) {
+        k = 26;
+        mul(V.player_mana, 0, 1.0f / 10.0f);
+        mul(V.player_xp, 0, 1.0f / 10.0f); mul(V.player_dexterity, 0, 1.0f / 10.0f);
+        mul(V.player_strength, 0, 1.0f / 10.0f); mul(V.player_intelligence, 0, 1.0f / 10.0f);
+        const int direction_index = soa(V.player_direction, 0, n, e) - 1;
 #pragma unroll
-    for (int i = 0; i < 4; i++) flag(i == direction_index);
+        for (int i = 0; i < 4; i++) flag(i == direction_index);
 #pragma unroll
-    for (int i = 0; i < 4; i++) mul(V.inv_armour, i, 1.0f / 2.0f);
+        for (int i = 0; i < 4; i++) mul(V.inv_armour, i, 1.0f / 2.0f);
 #pragma unroll
-    for (int i = 0; i < 4; i++) o[k++] = (float)soa(V.armour_enchantments, i, n, e);
-    o[k++] = soa(V.light_level, 0, n, e);
-    flag(soa(V.is_sleeping, 0, n, e) != 0);
-    flag(soa(V.is_resting, 0, n, e) != 0);
-    flag(soa(V.learned_spells, 0, n, e) != 0);
-    flag(soa(V.learned_spells, 1, n, e) != 0);
-    mul(V.player_level, 0, 1.0f / 10.0f);
-    flag(soa(V.monsters_killed, level, n, e) >= kKilledToClear);
-    // craftax_wg_is_boss_vulnerable (:1988-2003): no melee and no ranged mob alive on the level
-    flag(!melee_or_ranged && soa(V.boss_timesteps_to_spawn_this_round, 0, n, e) <= 0);
+        for (int i = 0; i < 4; i++) o[k++] = (float)soa(V.armour_enchantments, i, n, e);
+        o[k++] = soa(V.light_level, 0, n, e);
+        flag(soa(V.is_sleeping, 0, n, e) != 0);
+        flag(soa(V.is_resting, 0, n, e) != 0);
+        flag(soa(V.learned_spells, 0, n, e) != 0);
+        flag(soa(V.learned_spells, 1, n, e) != 0);
+        mul(V.player_level, 0, 1.0f / 10.0f);
+        flag(soa(V.monsters_killed, level, n, e) >= kKilledToClear);   // scalar 49
+        return;
+    }
+    // visible mobs of the player's level, class-major, slot-minor (:9195-9236):
+    // packed = valid | cell << 8 | channel << 4 | value
+    const int mob_level = jax_index(level, kLevels);
+    const int top = soa(V.player_position, 0, n, e) - kRows / 2;
+    const int left = soa(V.player_position, 1, n, e) - kCols / 2;
+    const uint8_t* light = V.state_base + (size_t)e * V.state_stride + V.light_map_offset +
+                           (size_t)mob_level * kMapSize * kMapSize;
+    const int c0 = part == 2 ? 0 : 3, c1 = part == 2 ? 3 : kClasses;
+    bool melee_or_ranged = false;
+    for (int c = c0; c < c1; c++) {
+        uint32_t pk[kSlots];
+#pragma unroll
+        for (int i = 0; i < kSlots; i++) {
+            pk[i] = 0;
+            if (i < (c == 2 ? 2 : 3)) {
+                const int idx = mob_index(c, mob_level, i);
+                const int type_id = soa(V.mob_type_id, idx, n, e);
+                const bool mask = soa(V.mob_mask, idx, n, e) != 0;
+                if (c == 0 || c == 2) melee_or_ranged = melee_or_ranged || mask;
+                const int mr = soa(V.mob_position, idx * 2, n, e), mc = soa(V.mob_position, idx * 2 + 1, n, e);
+                const int lr = mr - top, lc = mc - left;
+                if (type_id >= 0 && type_id < kMobTypes && mask && lr >= 0 && lr < kRows && lc >= 0 && lc < kCols &&
+                    mr >= 0 && mr < kMapSize && mc >= 0 && mc < kMapSize && light[mr * kMapSize + mc] > kLit)
+                    pk[i] = 0x80000000u | (uint32_t)(lr * kCols + lc) << 8 | (uint32_t)(3 + c) << 4 |
+                            (uint32_t)(type_id + 1);
+            }
+        }
+        // "last slot wins": a later slot of the class on the same cell replaces an earlier one
+        // (:9222-9231); the earlier one is dropped here, so the stores of phase 2 need no order
+#pragma unroll
+        for (int i = 0; i < kSlots - 1; i++)
+#pragma unroll
+            for (int i2 = i + 1; i2 < kSlots; i2++)
+                if ((pk[i] & pk[i2] & 0x80000000u) && ((pk[i] ^ pk[i2]) & 0xFF00u) == 0) pk[i] = 0;
+#pragma unroll
+        for (int i = 0; i < kSlots; i++) S.mobs[t][c * kSlots + i] = pk[i];
+    }
+    if (part == 2) {
+        // craftax_wg_is_boss_vulnerable (:1988-2003): no melee and no ranged mob alive on the level
+        o[kTail - 1] = !melee_or_ranged && soa(V.boss_timesteps_to_spawn_this_round, 0, n, e) <= 0 ? 1.0f : 0.0f;
+    } else {
+        S.level[t] = level; S.top[t] = top; S.left[t] = left;
+    }
 }
 
-// phase 2: one warp writes the record of the env that thread t gathered
-__device__ __forceinline__ void write_env(const Params& P, const Shared& S, int t, int lane) {
+// phase 2: the cells of one env.  The three byte loads per cell of all four rounds are issued
+// at once (load_cells); the caller holds them in registers while it stores the previous env.
+struct Cells { uint32_t l[4], b[4], it[4]; };
+__device__ __forceinline__ void load_cells(const cfx_env_view& V, const Shared& S, int t, int lane, Cells& c) {
     const int e = S.env[t];
     if (e < 0) return;
-    const cfx_env_view& V = P.v;
-    uint8_t* rec = P.records + (size_t)e * kRec;
     const int level = S.level[t], top = S.top[t], left = S.left[t];
     const uint8_t* blk = V.state_base + (size_t)e * V.state_stride + (size_t)level * kMapSize * kMapSize;
-    const uint8_t* map = blk + V.map_offset;
-    const uint8_t* item = blk + V.item_map_offset;
-    const uint8_t* lit = blk + V.light_map_offset;
-    // map cells: 8 bytes each {block, item + 1, lit, five mob classes = 0}  (:9241-9269);
-    // the loads of all four rounds are issued before the first store
-    uint32_t l[4], b[4], it[4];
-    bool in[4];
 #pragma unroll
     for (int r = 0; r < 4; r++) {
         const int cell = lane + 32 * r;
         const int wr = top + cell / kCols, wc = left + cell % kCols;
-        in[r] = cell < kCells && wr >= 0 && wr < kMapSize && wc >= 0 && wc < kMapSize;
-        const int o = in[r] ? wr * kMapSize + wc : 0;
-        l[r] = in[r] ? lit[o] : 0u;
-        b[r] = in[r] ? map[o] : 0u;
-        it[r] = in[r] ? item[o] : 0u;
+        const bool in = cell < kCells && wr >= 0 && wr < kMapSize && wc >= 0 && wc < kMapSize;
+        const int o = in ? wr * kMapSize + wc : 0;
+        c.l[r] = in ? blk[V.light_map_offset + o] : 0u;
+        c.b[r] = in ? blk[V.map_offset + o] : 0u;
+        c.it[r] = in ? blk[V.item_map_offset + o] : 0u;
     }
+}
+// map cells: 8 bytes each {block, item + 1, lit, five mob classes}  (:9241-9269), then the tail
+__device__ __forceinline__ void store_env(const Params& P, const Shared& S, int t, int lane, const Cells& c) {
+    const int e = S.env[t];
+    if (e < 0) return;
+    uint8_t* rec = P.records + (size_t)e * kRec;
 #pragma unroll
     for (int r = 0; r < 4; r++) {
         const int cell = lane + 32 * r;
         if (cell < kCells) {
-            const uint32_t w0 = l[r] > (uint32_t)kLit ? (b[r] | ((it[r] + 1u) & 0xFFu) << 8 | 1u << 16) : 0u;
+            const uint32_t w0 = c.l[r] > (uint32_t)kLit ? (c.b[r] | ((c.it[r] + 1u) & 0xFFu) << 8 | 1u << 16) : 0u;
             uint32_t* dst = reinterpret_cast<uint32_t*>(rec + (size_t)cell * 8);   // 4-byte aligned (996 = 4 x 249)
             dst[0] = w0;
             dst[1] = 0u;
@@ -183,17 +197,27 @@ __device__ __forceinline__ void write_env(const Params& P, const Shared& S, int 
     }
     for (int j = lane; j < kTail; j += 32) *reinterpret_cast<float*>(rec + kMap + 4 * j) = S.tail[t][j];
 }
+// warp `warp` writes envs warp, warp + 4, ... of the block, loading one env ahead
+__device__ __forceinline__ void write_envs(const Params& P, const Shared& S, int warp, int lane) {
+    constexpr int kWarps = kBlockThreads / 32;
+    Cells cur, nxt;
+    load_cells(P.v, S, warp, lane, cur);
+    for (int k = warp; k < kBlockEnvs; k += kWarps) {
+        if (k + kWarps < kBlockEnvs) load_cells(P.v, S, k + kWarps, lane, nxt);
+        store_env(P, S, k, lane, cur);
+        cur = nxt;
+    }
+}
 
 __global__ void __launch_bounds__(kBlockThreads) k_record_rows(const __grid_constant__ Params P) {
     __shared__ Shared S;   // 9 KB
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    if (warp == 0) {
-        const int e = blockIdx.x * kBlockEnvs + t;
-        if (e < P.n && (P.skip == nullptr || P.skip[e] == 0)) gather_env(P.v, e, t, S);
-        else S.env[t] = -1;
-    }
+    const int e = blockIdx.x * kBlockEnvs + lane;
+    const bool live = e < P.n && (P.skip == nullptr || P.skip[e] == 0);
+    if (live) gather_env(P.v, e, lane, warp, S);
+    if (warp == 0) S.env[lane] = live ? e : -1;
     __syncthreads();
-    for (int k = warp; k < kBlockEnvs; k += kBlockThreads / 32) write_env(P, S, k, lane);
+    write_envs(P, S, warp, lane);
 }
 
 // the envs named by a device-side list (first int32 of every entry), 32 entries per block pass
@@ -202,14 +226,13 @@ __global__ void __launch_bounds__(kBlockThreads) k_record_rows_list(const __grid
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int count = *P.count_dev;
     for (int base = blockIdx.x * kBlockEnvs; base < count; base += (int)gridDim.x * kBlockEnvs) {
-        if (warp == 0) {
-            int e = -1;
-            if (base + t < count) e = *reinterpret_cast<const int32_t*>(P.list + (size_t)(base + t) * P.list_stride);
-            if (e >= 0 && e < P.v.num_envs) gather_env(P.v, e, t, S);
-            else S.env[t] = -1;
-        }
+        int e = -1;
+        if (base + lane < count) e = *reinterpret_cast<const int32_t*>(P.list + (size_t)(base + lane) * P.list_stride);
+        const bool live = e >= 0 && e < P.v.num_envs;
+        if (live) gather_env(P.v, e, lane, warp, S);
+        if (warp == 0) S.env[lane] = live ? e : -1;
         __syncthreads();
-        for (int k = warp; k < kBlockEnvs; k += kBlockThreads / 32) write_env(P, S, k, lane);
+        write_envs(P, S, warp, lane);
         __syncthreads();
     }
 }
