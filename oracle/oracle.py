@@ -308,7 +308,7 @@ class RefCuda:
         return dict(zip(cls.LOCKSTEP_KEYS, out.tolist()))
 
     RECORD_KEYS = ("differing_bytes", "rows_compared", "reference_ms", "cfx_ms", "rows_with_mob",
-                   "list_differing_bytes")
+                   "list_differing_bytes", "skip_differing_bytes")
 
     @classmethod
     def record_parity(cls, layers, n, steps, fuzz, seed):

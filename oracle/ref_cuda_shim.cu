@@ -682,6 +682,10 @@ __global__ void refcu_k_random_actions(float* actions, int n, uint32_t seed, uin
     const int e = blockIdx.x * blockDim.x + threadIdx.x;
     if (e < n) actions[e] = (float)(refcu_hash(seed, step, (uint32_t)e) % CRAFTAX_NUM_ACTIONS);
 }
+__global__ void refcu_k_skip_flags(uint8_t* flags, int n, uint32_t seed) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e < n) flags[e] = (uint8_t)(refcu_hash(seed, 77u, (uint32_t)e) % 3u == 0u);
+}
 __global__ void refcu_k_count_diff(const uint8_t* a, const uint8_t* b, size_t bytes, unsigned long long* out) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     unsigned long long d = 0;
@@ -741,7 +745,8 @@ __global__ void refcu_k_fuzz_state(cfx_env_view w, uint32_t seed, uint32_t r) {
 
 /* out[0] differing bytes over all compared rows, out[1] rows compared, out[2] / out[3] ms per call
  * of k_record_obs / cfx_record_obs at n envs (CUDA events, 20 calls each), out[4] rows with a
- * visible mob among the compared ones (coverage), out[5] differing bytes of the list variant. */
+ * visible mob among the compared ones (coverage), out[5] differing bytes of the list variant,
+ * out[6] differing bytes with skip flags on every third env (skipped rows keep their bytes). */
 int refcu_record_parity(int n, int steps, int fuzz, unsigned long long seed, double* out) {
     CuVec v; CuPolicy p;
     cu_vec_init(&v, n, seed);
@@ -788,6 +793,19 @@ int refcu_record_parity(int n, int steps, int fuzz, unsigned long long seed, dou
         refcu_k_fuzz_state<<<(n + 127) / 128, 128, 0, st>>>(w, (uint32_t)seed, (uint32_t)r);
         compare();
     }
+    /* the skip flags: rows whose flag is set keep their bytes in both */
+    if (rc == 0) {
+        uint8_t* flags = NULL;
+        CU_CHECK(cudaMalloc(&flags, (size_t)n));
+        refcu_k_skip_flags<<<(n + 255) / 256, 256, 0, st>>>(flags, n, (uint32_t)seed);
+        CU_CHECK(cudaMemsetAsync(ra, 0xCD, bytes, st));
+        CU_CHECK(cudaMemsetAsync(rb, 0xCD, bytes, st));
+        k_record_obs<<<(int)(((size_t)n * 32 + 255) / 256), 256, 0, st>>>(ra, n, flags);
+        if (cfx_record_obs(dev, &w, rb, n, flags, st) != CFX_OK) { fprintf(stderr, "cfx: %s\n", cfx_last_error()); rc = 1; }
+        refcu_k_count_diff<<<1024, 256, 0, st>>>(ra, rb, bytes, d_cnt + 2);
+        CU_CHECK(cudaStreamSynchronize(st));
+        cudaFree(flags);
+    }
     CU_CHECK(cudaStreamSynchronize(st));
     /* timing, on the last state */
     float ms_ref = 0.f, ms_cfx = 0.f;
@@ -824,7 +842,7 @@ int refcu_record_parity(int n, int steps, int fuzz, unsigned long long seed, dou
         out[4] = with_mob;
         free(h);
     }
-    out[0] = (double)cn[0]; out[1] = rows; out[2] = ms_ref / 20.0; out[3] = ms_cfx / 20.0; out[5] = (double)cn[1];
+    out[0] = (double)cn[0]; out[1] = rows; out[2] = ms_ref / 20.0; out[3] = ms_cfx / 20.0; out[5] = (double)cn[1]; out[6] = (double)cn[2];
     cudaFree(ra); cudaFree(rb); cudaFree(d_cnt);
     cu_policy_free(&p);
     cu_vec_free(&v);

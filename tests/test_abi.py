@@ -72,3 +72,27 @@ def test_create_without_gpu_is_an_error_not_a_fallback(cfx):
         pass
     else:
         raise AssertionError("expand ran without a GPU")
+
+
+def test_record_write_rejects_a_bad_view_before_touching_the_device(cfx):
+    """cfx_record_obs validates its view on the host: no view, no envs, a missing field pointer
+    and a misaligned record array are refused with a message, with or without a GPU."""
+    import ctypes as C
+    lib = cfx.lib()
+    buf = (C.c_uint8 * 4096)()
+    rec = C.addressof(buf)
+    assert lib.cfx_record_obs(0, None, rec, 32, None, None) == 1
+    assert b"cfx_record_obs" in lib.cfx_last_error()
+    # a view is 4 + 4 (pad) + 8 + 8 + 3 * 8 bytes of header, then 40 field pointers
+    view = (C.c_uint64 * 64)()
+    C.cast(view, C.POINTER(C.c_int32))[0] = 32          # num_envs
+    view[1] = rec                                       # state_base
+    view[2] = 1024                                      # state_stride
+    assert lib.cfx_record_obs(0, view, rec, 32, None, None) == 1
+    assert b"field pointer 0" in lib.cfx_last_error()   # player_position is NULL
+    for i in range(6, 6 + 40):
+        view[i] = rec
+    assert lib.cfx_record_obs(0, view, rec + 2, 32, None, None) == 1
+    assert b"aligned" in lib.cfx_last_error()
+    assert lib.cfx_record_obs(0, view, rec, 64, None, None) == 1   # more envs than the view has
+    assert b"num_envs" in lib.cfx_last_error()

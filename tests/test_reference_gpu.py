@@ -247,4 +247,5 @@ def test_record_write_equals_the_reference_kernel(cfx, oracle, refcu, n, steps, 
     assert r["rows_compared"] == n * (steps + fuzz)
     assert r["differing_bytes"] == 0
     assert r["list_differing_bytes"] == 0
+    assert r["skip_differing_bytes"] == 0   # flagged envs are left untouched by both
     assert r["rows_with_mob"] > n // 4   # the randomised rounds put mobs into most views
