@@ -108,7 +108,7 @@ __device__ __forceinline__ void gather_env(const cfx_env_view& V, int e, int t, 
         flag(soa(V.learned_spells, 0, n, e) != 0);
         flag(soa(V.learned_spells, 1, n, e) != 0);
         mul(V.player_level, 0, 1.0f / 10.0f);
-        flag(soa(V.monsters_killed, level, n, e) >= kKilledToClear);   // scalar 49
+        flag((unsigned)level < (unsigned)kLevels && soa(V.monsters_killed, level, n, e) >= kKilledToClear);   // scalar 49
         return;
     }
     // visible mobs of the player's level, class-major, slot-minor (:9195-9236):
@@ -168,7 +168,10 @@ __device__ __forceinline__ void load_cells(const cfx_env_view& V, const Shared& 
     for (int r = 0; r < 4; r++) {
         const int cell = lane + 32 * r;
         const int wr = top + cell / kCols, wc = left + cell % kCols;
-        const bool in = cell < kCells && wr >= 0 && wr < kMapSize && wc >= 0 && wc < kMapSize;
+        // (a level outside [0, 9) never comes out of the env; the reference would read outside
+        // its maps there, here such an env gets unlit cells)
+        const bool in = cell < kCells && wr >= 0 && wr < kMapSize && wc >= 0 && wc < kMapSize &&
+                        (unsigned)level < (unsigned)kLevels;
         const int o = in ? wr * kMapSize + wc : 0;
         c.l[r] = in ? blk[V.light_map_offset + o] : 0u;
         c.b[r] = in ? blk[V.map_offset + o] : 0u;
@@ -205,7 +208,7 @@ __device__ __forceinline__ void write_envs(const Params& P, const Shared& S, int
     for (int k = warp; k < kBlockEnvs; k += kWarps) {
         if (k + kWarps < kBlockEnvs) load_cells(P.v, S, k + kWarps, lane, nxt);
         store_env(P, S, k, lane, cur);
-        cur = nxt;
+        if (k + kWarps < kBlockEnvs) cur = nxt;
     }
 }
 
