@@ -36,6 +36,31 @@ class ForwardIO(C.Structure):
                 ("env_offset", C.c_uint64), ("bump_step", C.c_int), ("r_state_bf16", C.c_int)]
 
 
+# the SoA fields of cfx_env_view, in the order of include/cfx.h: (name, numpy dtype, elements per env)
+ENV_VIEW_FIELDS = (
+    ("player_position", "i4", 2), ("player_level", "i4", 1), ("player_direction", "i4", 1),
+    ("player_health", "f4", 1), ("player_food", "i4", 1), ("player_drink", "i4", 1), ("player_energy", "i4", 1),
+    ("player_mana", "i4", 1), ("is_sleeping", "u1", 1), ("is_resting", "u1", 1), ("player_xp", "i4", 1),
+    ("player_dexterity", "i4", 1), ("player_strength", "i4", 1), ("player_intelligence", "i4", 1),
+    ("inv_wood", "i4", 1), ("inv_stone", "i4", 1), ("inv_coal", "i4", 1), ("inv_iron", "i4", 1),
+    ("inv_diamond", "i4", 1), ("inv_sapling", "i4", 1), ("inv_pickaxe", "i4", 1), ("inv_sword", "i4", 1),
+    ("inv_bow", "i4", 1), ("inv_arrows", "i4", 1), ("inv_torches", "i4", 1), ("inv_ruby", "i4", 1),
+    ("inv_sapphire", "i4", 1), ("inv_books", "i4", 1), ("inv_armour", "i4", 4), ("inv_potions", "i4", 6),
+    ("learned_spells", "u1", 2), ("sword_enchantment", "i4", 1), ("bow_enchantment", "i4", 1),
+    ("armour_enchantments", "i4", 4), ("boss_timesteps_to_spawn_this_round", "i4", 1), ("light_level", "f4", 1),
+    ("monsters_killed", "i4", 9), ("mob_position", "i4", 270), ("mob_mask", "u1", 135), ("mob_type_id", "i4", 135),
+)
+ENV_VIEW_MAPS = ("map", "item_map", "light_map")   # uint8 [9][48][48] inside every env's block
+ENV_MAP_BYTES = 9 * 48 * 48
+
+
+class EnvView(C.Structure):
+    """cfx_env_view of include/cfx.h."""
+    _fields_ = [("num_envs", C.c_int32), ("state_base", C.c_void_p), ("state_stride", C.c_uint64),
+                ("map_offset", C.c_uint64), ("item_map_offset", C.c_uint64), ("light_map_offset", C.c_uint64)] + \
+               [(name, C.c_void_p) for name, _, _ in ENV_VIEW_FIELDS]
+
+
 _SIGS = {
     "cfx_param_count": (C.c_size_t, [C.c_int] * 3),
     "cfx_policy_create": (C.c_int, [C.POINTER(C.c_void_p)] + [C.c_int] * 6),
@@ -407,6 +432,57 @@ def sample_actions(logits, uniforms, num_actions=43, device=0):
     d_p = DeviceBuffer((n,), np.float32, device)
     check(lib().cfx_sample_actions(device, d_l.ptr, ld, num_actions, d_u.ptr, n, d_a.ptr, d_p.ptr, None))
     return d_a.download(), d_p.download()
+
+
+def env_view_from_state(state, device=0):
+    """Uploads a state dict (one [count][n] array per field of ENV_VIEW_FIELDS, one
+    [n][9][48][48] byte array per map) and returns (EnvView, buffers to keep alive).  The per-env
+    block holds the three maps back to back."""
+    n = state["player_level"].shape[1]
+    keep, view = [], EnvView()
+    view.num_envs = n
+    blocks = np.ascontiguousarray(np.stack([state[m].reshape(n, ENV_MAP_BYTES) for m in ENV_VIEW_MAPS], axis=1))
+    d_blocks = DeviceBuffer.from_host(blocks, device)
+    keep.append(d_blocks)
+    view.state_base, view.state_stride = d_blocks.ptr, 3 * ENV_MAP_BYTES
+    view.map_offset, view.item_map_offset, view.light_map_offset = 0, ENV_MAP_BYTES, 2 * ENV_MAP_BYTES
+    for name, dt, cnt in ENV_VIEW_FIELDS:
+        a = np.ascontiguousarray(state[name], np.dtype(dt))
+        assert a.shape == (cnt, n), (name, a.shape)
+        b = DeviceBuffer.from_host(a, device)
+        keep.append(b)
+        setattr(view, name, b.ptr)
+    return view, keep
+
+
+def env_state_from_view(view, device=0):
+    """The reverse: downloads every field and the three maps behind an EnvView (device pointers)
+    into a state dict."""
+    n = view.num_envs
+    L = lib()
+
+    def fetch(ptr, shape, dt):
+        out = np.empty(shape, np.dtype(dt))
+        check(L.cfx_memcpy_d2h(device, out.ctypes.data, ptr, out.nbytes, None))
+        check(L.cfx_stream_sync(device, None))
+        return out
+    st = {name: fetch(getattr(view, name), (cnt, n), dt) for name, dt, cnt in ENV_VIEW_FIELDS}
+    blocks = fetch(view.state_base, (n, view.state_stride), "u1")
+    for m, off in zip(ENV_VIEW_MAPS, (view.map_offset, view.item_map_offset, view.light_map_offset)):
+        st[m] = blocks[:, off:off + ENV_MAP_BYTES].reshape(n, 9, 48, 48).copy()
+    return st
+
+
+def record_obs(view, d_records, n=None, skip=None, device=0, stream=None):
+    """cfx_record_obs: the [n][996] records of the envs behind `view` into a DeviceBuffer."""
+    check(lib().cfx_record_obs(device, C.byref(view), d_records.ptr, view.num_envs if n is None else n,
+                               None if skip is None else skip.ptr, stream))
+
+
+def record_obs_list(view, d_records, d_list, list_stride, d_count, device=0, stream=None):
+    """cfx_record_obs_list: the envs named by the first int32 of every list entry."""
+    check(lib().cfx_record_obs_list(device, C.byref(view), d_records.ptr, d_list.ptr, list_stride, d_count.ptr,
+                                    stream))
 
 
 def philox_uniforms(seed, env_offset, step, n, device=0):

@@ -126,6 +126,155 @@ def classic_forward(params, rec, prev_done, state, H=256, L=3, A=17, want_h_enc=
     return (lav, he) if want_h_enc else lav
 
 
+# ---- record write (reference cf_record_env_warp, craftax_full.cu:9180-9269, scalar tail
+# craftax_encode_scalar_observation_tail_at :2429-2487): a numpy restatement over a dict of
+# arrays, one entry per SoA field of CF_SOA_FIELDS (:620-690) that the record reads, shaped
+# [count][n] like the reference's device layout, plus the three byte maps [n][9][48][48].
+RECORD_FIELDS = {   # name: (dtype, count)
+    "player_position": (np.int32, 2), "player_level": (np.int32, 1), "player_direction": (np.int32, 1),
+    "player_health": (np.float32, 1), "player_food": (np.int32, 1), "player_drink": (np.int32, 1),
+    "player_energy": (np.int32, 1), "player_mana": (np.int32, 1), "is_sleeping": (np.uint8, 1),
+    "is_resting": (np.uint8, 1), "player_xp": (np.int32, 1), "player_dexterity": (np.int32, 1),
+    "player_strength": (np.int32, 1), "player_intelligence": (np.int32, 1), "inv_wood": (np.int32, 1),
+    "inv_stone": (np.int32, 1), "inv_coal": (np.int32, 1), "inv_iron": (np.int32, 1),
+    "inv_diamond": (np.int32, 1), "inv_sapling": (np.int32, 1), "inv_pickaxe": (np.int32, 1),
+    "inv_sword": (np.int32, 1), "inv_bow": (np.int32, 1), "inv_arrows": (np.int32, 1),
+    "inv_torches": (np.int32, 1), "inv_ruby": (np.int32, 1), "inv_sapphire": (np.int32, 1),
+    "inv_books": (np.int32, 1), "inv_armour": (np.int32, 4), "inv_potions": (np.int32, 6),
+    "learned_spells": (np.uint8, 2), "sword_enchantment": (np.int32, 1), "bow_enchantment": (np.int32, 1),
+    "armour_enchantments": (np.int32, 4), "boss_timesteps_to_spawn_this_round": (np.int32, 1),
+    "light_level": (np.float32, 1), "monsters_killed": (np.int32, 9), "mob_position": (np.int32, 270),
+    "mob_mask": (np.uint8, 135), "mob_type_id": (np.int32, 135),
+}
+RECORD_MAPS = ("map", "item_map", "light_map")   # uint8 [n][9][48][48] each
+
+
+def jax_index(i, size):
+    """craftax_wg_jax_index (:1963-1975): a negative index wraps once, then the index is clamped."""
+    i = np.where(i < 0, i + size, i)
+    return np.clip(i, 0, size - 1)
+
+
+def record_from_state(st):
+    """The [n][996] records of a state dict (RECORD_FIELDS + RECORD_MAPS)."""
+    n = st["player_level"].shape[1]
+    rec = np.zeros((n, 996), np.uint8)
+    tail = np.zeros((n, 51), np.float32)
+    f32 = np.float32
+    level = st["player_level"][0].astype(np.int64)
+    mob_level = jax_index(level, 9)
+
+    def sq10(x):
+        return np.sqrt(x.astype(f32)) * f32(1.0 / 10.0)
+    k = 0
+    for name in ("inv_wood", "inv_stone", "inv_coal", "inv_iron", "inv_diamond", "inv_sapphire", "inv_ruby",
+                 "inv_sapling", "inv_torches", "inv_arrows"):
+        tail[:, k] = sq10(st[name][0]); k += 1
+    tail[:, k] = st["inv_books"][0].astype(f32) * f32(0.5); k += 1
+    tail[:, k] = st["inv_pickaxe"][0].astype(f32) * f32(0.25); k += 1
+    tail[:, k] = st["inv_sword"][0].astype(f32) * f32(0.25); k += 1
+    for name in ("sword_enchantment", "bow_enchantment", "inv_bow"):
+        tail[:, k] = st[name][0].astype(f32); k += 1
+    for i in range(6):
+        tail[:, k] = sq10(st["inv_potions"][i]); k += 1
+    tail[:, k] = st["player_health"][0] * f32(1.0 / 10.0); k += 1
+    for name in ("player_food", "player_drink", "player_energy", "player_mana", "player_xp",
+                 "player_dexterity", "player_strength", "player_intelligence"):
+        tail[:, k] = st[name][0].astype(f32) * f32(1.0 / 10.0); k += 1
+    for i in range(4):
+        tail[:, k] = (st["player_direction"][0] - 1 == i); k += 1
+    for i in range(4):
+        tail[:, k] = st["inv_armour"][i].astype(f32) * f32(0.5); k += 1
+    for i in range(4):
+        tail[:, k] = st["armour_enchantments"][i].astype(f32); k += 1
+    tail[:, k] = st["light_level"][0]; k += 1
+    for a in (st["is_sleeping"][0], st["is_resting"][0], st["learned_spells"][0], st["learned_spells"][1]):
+        tail[:, k] = a != 0; k += 1
+    tail[:, k] = st["player_level"][0].astype(f32) * f32(1.0 / 10.0); k += 1
+    env = np.arange(n)
+    tail[:, k] = st["monsters_killed"][np.clip(level, 0, 8), env] >= 8; k += 1   # level is in [0, 9) in every env state
+
+    def midx(c, lvl, i):
+        return (c * 9 + lvl) * 3 + i
+    alive = np.zeros(n, bool)
+    for c, slots in ((0, 3), (2, 2)):   # craftax_wg_is_boss_vulnerable (:1988-2003)
+        for i in range(slots):
+            alive |= st["mob_mask"][midx(c, mob_level, i), env] != 0
+    tail[:, k] = ~alive & (st["boss_timesteps_to_spawn_this_round"][0] <= 0); k += 1
+    assert k == 51
+    rec[:, 792:] = tail.view(np.uint8).reshape(n, 204)
+
+    top = st["player_position"][0].astype(np.int64) - 4
+    left = st["player_position"][1].astype(np.int64) - 5
+    cells = np.zeros((n, 9, 11, 8), np.uint8)
+    rr = top[:, None, None] + np.arange(9)[None, :, None]
+    cc = left[:, None, None] + np.arange(11)[None, None, :]
+    inb = (rr >= 0) & (rr < 48) & (cc >= 0) & (cc < 48)
+    rc, ccl = np.clip(rr, 0, 47), np.clip(cc, 0, 47)
+    e3 = env[:, None, None]
+    lv3 = np.clip(level, 0, 8)[:, None, None]
+    lit = inb & (st["light_map"][e3, lv3, rc, ccl] > 12)
+    cells[..., 0] = np.where(lit, st["map"][e3, lv3, rc, ccl], 0)
+    cells[..., 1] = np.where(lit, (st["item_map"][e3, lv3, rc, ccl].astype(np.int32) + 1) & 255, 0)
+    cells[..., 2] = lit
+    # mobs in class-major, slot-minor order: a later slot of a class overwrites an earlier one (:9195-9236)
+    for c in range(5):
+        for i in range(2 if c == 2 else 3):
+            idx = midx(c, mob_level, i)
+            t = st["mob_type_id"][idx, env]
+            m = st["mob_mask"][idx, env] != 0
+            mr = st["mob_position"][idx * 2, env].astype(np.int64)
+            mc = st["mob_position"][idx * 2 + 1, env].astype(np.int64)
+            lr, lc = mr - top, mc - left
+            ok = (t >= 0) & (t < 8) & m & (lr >= 0) & (lr < 9) & (lc >= 0) & (lc < 11) & \
+                 (mr >= 0) & (mr < 48) & (mc >= 0) & (mc < 48)
+            okl = ok & (st["light_map"][env, mob_level, np.clip(mr, 0, 47), np.clip(mc, 0, 47)] > 12)
+            sel = np.nonzero(okl)[0]
+            cells[sel, lr[sel], lc[sel], 3 + c] = (t[sel] + 1).astype(np.uint8)
+    rec[:, :792] = cells.reshape(n, 792)
+    return rec
+
+
+def synthetic_env_state(n, seed=0):
+    """A random state dict with the value ranges of the game: players anywhere on the map, mobs
+    of every class and slot near the player (some off the view, off the map, unlit, masked out or
+    with a type id out of range), random blocks, items and light around the player."""
+    rng = np.random.default_rng(seed)
+    st = {}
+    for name, (dt, cnt) in RECORD_FIELDS.items():
+        st[name] = np.zeros((cnt, n), dt)
+    st["player_level"][0] = rng.integers(0, 9, n)
+    st["player_position"][:] = rng.integers(0, 48, (2, n))
+    st["player_direction"][0] = rng.integers(0, 6, n)
+    st["player_health"][0] = rng.integers(0, 100, n).astype(np.float32) * np.float32(0.125)
+    for name in ("player_food", "player_drink", "player_energy", "player_mana", "player_xp", "player_dexterity",
+                 "player_strength", "player_intelligence", "inv_pickaxe", "inv_sword", "inv_bow", "inv_books",
+                 "sword_enchantment", "bow_enchantment"):
+        st[name][0] = rng.integers(0, 10, n)
+    for name in ("inv_wood", "inv_stone", "inv_coal", "inv_iron", "inv_diamond", "inv_sapling", "inv_arrows",
+                 "inv_torches", "inv_ruby", "inv_sapphire"):
+        st[name][0] = rng.integers(0, 100, n)
+    st["inv_armour"][:] = rng.integers(0, 3, (4, n))
+    st["armour_enchantments"][:] = rng.integers(0, 3, (4, n))
+    st["inv_potions"][:] = rng.integers(0, 30, (6, n))
+    for name in ("is_sleeping", "is_resting"):
+        st[name][0] = rng.integers(0, 2, n)
+    st["learned_spells"][:] = rng.integers(0, 2, (2, n))
+    st["boss_timesteps_to_spawn_this_round"][0] = rng.integers(-2, 3, n)
+    st["light_level"][0] = rng.integers(0, 1000, n).astype(np.float32) * np.float32(0.001)
+    st["monsters_killed"][:] = rng.integers(0, 16, (9, n))
+    st["mob_type_id"][:] = rng.integers(-1, 9, (135, n))
+    st["mob_mask"][:] = rng.integers(0, 4, (135, n)) != 0
+    pos = np.empty((135, 2, n), np.int64)
+    pos[:, 0] = st["player_position"][0][None, :] + rng.integers(-6, 7, (135, n))
+    pos[:, 1] = st["player_position"][1][None, :] + rng.integers(-7, 8, (135, n))
+    st["mob_position"][:] = pos.reshape(270, n)
+    st["map"] = rng.integers(0, 40, (n, 9, 48, 48)).astype(np.uint8)
+    st["item_map"] = rng.integers(0, 6, (n, 9, 48, 48)).astype(np.uint8)
+    st["light_map"] = rng.integers(0, 26, (n, 9, 48, 48)).astype(np.uint8)
+    return st
+
+
 def max_threads():
     return int(lib().cfxo_max_threads())
 
@@ -324,6 +473,24 @@ class RefCuda:
         if rc != 0:
             raise RuntimeError("refcu_record_parity: a cfx call failed (see stderr)")
         return dict(zip(cls.RECORD_KEYS, out.tolist()))
+
+    @classmethod
+    def record_session(cls, layers, n, steps, fuzz, seed, view):
+        """Plays the reference's CUDA env (`steps` random steps, `fuzz` rounds of randomised
+        state), returns the records its k_record_obs writes and fills `view` (a ctypes mirror of
+        cfx_env_view) with pointers to the live state; call record_session_close when done."""
+        L = C.CDLL(cls.path(layers))
+        L.refcu_record_session_open.argtypes = [C.c_int, C.c_int, C.c_int, C.c_ulonglong, C.c_void_p, C.c_size_t,
+                                                C.c_void_p]
+        rec = np.empty((n, 996), np.uint8)
+        rc = L.refcu_record_session_open(n, steps, fuzz, seed, C.addressof(view), C.sizeof(view), _p(rec))
+        if rc != 0:
+            raise RuntimeError("refcu_record_session_open failed (a session is open, or the view's size differs)")
+        return rec
+
+    @classmethod
+    def record_session_close(cls, layers):
+        C.CDLL(cls.path(layers)).refcu_record_session_close()
 
     @classmethod
     def play(cls, layers, n, steps, seed, load_path, swapped, precision, record_n, record_every,

@@ -848,6 +848,50 @@ int refcu_record_parity(int n, int steps, int fuzz, unsigned long long seed, dou
     cu_vec_free(&v);
     return rc;
 }
+
+/* ---- a state of the reference's CUDA env, its records, and the view on it, handed to the caller ----
+ * refcu_record_session_open plays `steps` steps with random actions, optionally randomises the
+ * state `fuzz` times (refcu_k_fuzz_state), writes the records with k_record_obs into
+ * records_host [n][996] and copies the filled cfx_env_view into view_out; the env stays alive
+ * until refcu_record_session_close, so that the caller can read the state through the view's
+ * device pointers (to run a CPU restatement of the record write on the very same state). */
+static CuVec g_sess_v;
+static CuPolicy g_sess_p;
+static int g_sess_open = 0;
+int refcu_record_session_open(int n, int steps, int fuzz, unsigned long long seed, void* view_out,
+                              size_t view_bytes, uint8_t* records_host) {
+    if (g_sess_open || view_bytes != sizeof(cfx_env_view)) return 1;
+    cu_vec_init(&g_sess_v, n, seed);
+    cu_policy_init(&g_sess_p, n);
+    g_sess_open = 1;
+    cudaStream_t st = g_sess_p.stream;
+    cfx_env_view w;
+    refcu_fill_view(&g_sess_v, &w);
+    for (int t = 0; t < steps; t++) {
+        refcu_k_random_actions<<<(n + 255) / 256, 256, 0, st>>>(g_sess_v.d_actions, n, (uint32_t)seed, (uint32_t)t);
+        refcu_roll r = {&g_sess_v, &g_sess_p, seed, NULL};
+        refcu_step_env_only(&r);
+        if ((t & 15) == 15) CU_CHECK(cudaStreamSynchronize(st));
+    }
+    for (int r = 0; r < fuzz; r++)
+        refcu_k_fuzz_state<<<(n + 127) / 128, 128, 0, st>>>(w, (uint32_t)seed, (uint32_t)r);
+    uint8_t* d_rec = NULL;
+    const size_t bytes = (size_t)n * CF_TRAIN_OBS;
+    CU_CHECK(cudaMalloc(&d_rec, bytes));
+    k_record_obs<<<(int)(((size_t)n * 32 + 255) / 256), 256, 0, st>>>(d_rec, n);
+    CU_CHECK(cudaGetLastError());
+    CU_CHECK(cudaStreamSynchronize(st));
+    CU_CHECK(cudaMemcpy(records_host, d_rec, bytes, cudaMemcpyDeviceToHost));
+    cudaFree(d_rec);
+    memcpy(view_out, &w, sizeof(w));
+    return 0;
+}
+void refcu_record_session_close(void) {
+    if (!g_sess_open) return;
+    cu_policy_free(&g_sess_p);
+    cu_vec_free(&g_sess_v);
+    g_sess_open = 0;
+}
 #endif
 
 
