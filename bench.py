@@ -17,7 +17,9 @@ median repetition is reported, so that a few milliseconds of work are not judged
 sample; `sustained` is the same step run back to back for about a fifth of a second, where a
 1 kW part meets its power cap (its clock record is reported with it).  At N = 1 the line also
 carries the reference's own cuBLAS forward on the same GPU and inputs (`reference_cublas`,
-from the library built out of the reference sources when it is present) and the CPU arm
+from the library built out of the reference sources when it is present), whole rollouts of the
+reference's `run` loop unmodified, with the forward swapped and with the record write swapped
+too (`reference_rollout`; `--no-rollout` or `--no-reference-cublas` skip it), and the CPU arm
 (`cpu_baseline`).
 """
 import argparse
@@ -321,6 +323,8 @@ def run_cfx(args):
     }
     if rank == 0 and world == 1 and not args.no_reference_cublas:
         line["reference_cublas"] = reference_cublas_forward(args, d_rec, d_pt, kernel_ms)
+    if rank == 0 and world == 1 and not args.no_rollout and not args.no_reference_cublas:
+        line["reference_rollout"] = reference_rollout(args, prec)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_forward_rate(H, L, budget_s=args.cpu_budget)
     if rank == 0:
@@ -353,6 +357,44 @@ def reference_cublas_forward(args, d_rec, d_pt, kernel_ms):
             out[f"ratio_{name}"] = ms / kernel_ms
         ref.close()
         return out
+    except Exception as e:   # a comparison arm must not take the product line down
+        return {"unavailable": f"{type(e).__name__}: {e}"}
+
+
+def reference_rollout(args, prec):
+    """Whole rollouts of the reference's `run` loop on this GPU, in this process, after the
+    product arm: unmodified (cu_rollout_step_plain with its cuBLAS policy), with the policy half
+    swapped for cfx_policy_forward, and with the record write swapped for cfx_record_obs as
+    well; plus the two record kernels timed alone.  CUDA-graph replay, CUDA events.  Needs the
+    library built from the reference sources (oracle/_ref/)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    try:
+        import ctypes as C
+        import cfx
+        import oracle as O
+        L, n = args.layers, args.envs
+        if args.hidden != 256 or not O.RefCuda.available(L):
+            return {"unavailable": f"oracle/_ref/libcfref_cuda_l{L}.so not built (reference sources absent)"}
+        lib = C.CDLL(O.RefCuda.path(L))
+        if not hasattr(lib, "refcu_rollout_swap2_sps"):
+            return {"unavailable": "reference shim built without the swapped rollout"}
+        lib.refcu_rollout_sps.restype = C.c_double
+        lib.refcu_rollout_sps.argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_int]
+        lib.refcu_rollout_swap2_sps.restype = C.c_double
+        lib.refcu_rollout_swap2_sps.argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_int, C.c_int, C.c_int]
+        code = {"f16": cfx.PREC_F16, "bf16": cfx.PREC_BF16, "fp32": cfx.PREC_FP32}[prec]
+        iters = 20
+        ref = lib.refcu_rollout_sps(n, iters, 1, 1)
+        fwd = lib.refcu_rollout_swap2_sps(n, iters, 1, 1, code, 0)
+        both = lib.refcu_rollout_swap2_sps(n, iters, 1, 1, code, 1)
+        rec = O.RefCuda.record_parity(L, n, 2, 1, seed=1)
+        return {"unit": UNIT, "iters": iters,
+                "what": "reference run loop (env kernels + policy), graph replay, same process",
+                "reference": ref, "forward_swapped": fwd, "forward_and_record_swapped": both,
+                "ratio_forward_swapped": fwd / ref, "ratio_forward_and_record_swapped": both / ref,
+                "record_write": {"reference_k_record_obs_ms": rec["reference_ms"], "cfx_record_obs_ms": rec["cfx_ms"],
+                                 "ratio": rec["reference_ms"] / rec["cfx_ms"],
+                                 "differing_bytes": rec["differing_bytes"], "rows_compared": rec["rows_compared"]}}
     except Exception as e:   # a comparison arm must not take the product line down
         return {"unavailable": f"{type(e).__name__}: {e}"}
 
@@ -680,6 +722,8 @@ def main():
     ap.add_argument("--precision", default=None, choices=["fp32", "f16", "bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-reference-cublas", action="store_true")
+    ap.add_argument("--no-rollout", action="store_true",
+                    help="skip the whole-rollout comparison (reference run loop, swapped, record write)")
     ap.add_argument("--min-timed-ms", type=float, default=100.0,
                     help="device time to fill with repetitions of the K-step region")
     ap.add_argument("--rep-gap-ms", type=float, default=30.0, help="idle gap between repetitions")
