@@ -362,39 +362,41 @@ def reference_cublas_forward(args, d_rec, d_pt, kernel_ms):
 
 
 def reference_rollout(args, prec):
-    """Whole rollouts of the reference's `run` loop on this GPU, in this process, after the
-    product arm: unmodified (cu_rollout_step_plain with its cuBLAS policy), with the policy half
-    swapped for cfx_policy_forward, and with the record write swapped for cfx_record_obs as
-    well; plus the two record kernels timed alone.  CUDA-graph replay, CUDA events.  Needs the
-    library built from the reference sources (oracle/_ref/)."""
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    """Whole rollouts of the reference's `run` loop on this GPU, in the same run, right after
+    the product arm: unmodified (cu_rollout_step_plain with its cuBLAS policy), with the policy
+    half swapped for cfx_policy_forward, and with the record write swapped for cfx_record_obs as
+    well; plus the two record kernels timed alone.  CUDA-graph replay, CUDA events.  The two
+    arms (`--impl ref-rollout`, `--impl record`) run as child processes with a time limit, so
+    that a failure inside the library built from the reference sources (oracle/_ref/) cannot
+    take the product line down."""
+    import subprocess
+
+    def child(impl, extra, limit):
+        cmd = [sys.executable, os.path.abspath(__file__), "--impl", impl, "--envs", str(args.envs),
+               "--layers", str(args.layers), "--hidden", str(args.hidden)] + extra
+        env = dict(os.environ)
+        for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE"):
+            env.pop(k, None)
+        r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, timeout=limit, env=env)
+        lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+        if r.returncode != 0 or not lines:
+            raise RuntimeError(f"`bench.py --impl {impl}` exited with {r.returncode}")
+        return json.loads(lines[-1])
     try:
-        import ctypes as C
-        import cfx
-        import oracle as O
-        L, n = args.layers, args.envs
-        if args.hidden != 256 or not O.RefCuda.available(L):
-            return {"unavailable": f"oracle/_ref/libcfref_cuda_l{L}.so not built (reference sources absent)"}
-        lib = C.CDLL(O.RefCuda.path(L))
-        if not hasattr(lib, "refcu_rollout_swap2_sps"):
-            return {"unavailable": "reference shim built without the swapped rollout"}
-        lib.refcu_rollout_sps.restype = C.c_double
-        lib.refcu_rollout_sps.argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_int]
-        lib.refcu_rollout_swap2_sps.restype = C.c_double
-        lib.refcu_rollout_swap2_sps.argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_int, C.c_int, C.c_int]
-        code = {"f16": cfx.PREC_F16, "bf16": cfx.PREC_BF16, "fp32": cfx.PREC_FP32}[prec]
-        iters = 20
-        ref = lib.refcu_rollout_sps(n, iters, 1, 1)
-        fwd = lib.refcu_rollout_swap2_sps(n, iters, 1, 1, code, 0)
-        both = lib.refcu_rollout_swap2_sps(n, iters, 1, 1, code, 1)
-        rec = O.RefCuda.record_parity(L, n, 2, 1, seed=1)
-        return {"unit": UNIT, "iters": iters,
-                "what": "reference run loop (env kernels + policy), graph replay, same process",
-                "reference": ref, "forward_swapped": fwd, "forward_and_record_swapped": both,
-                "ratio_forward_swapped": fwd / ref, "ratio_forward_and_record_swapped": both / ref,
-                "record_write": {"reference_k_record_obs_ms": rec["reference_ms"], "cfx_record_obs_ms": rec["cfx_ms"],
-                                 "ratio": rec["reference_ms"] / rec["cfx_ms"],
-                                 "differing_bytes": rec["differing_bytes"], "rows_compared": rec["rows_compared"]}}
+        ro = child("ref-rollout", ["--steps", "20", "--precision", prec], 240)
+        if "unavailable" in ro:
+            return {"unavailable": ro["unavailable"]}
+        out = {"unit": UNIT, "iters": ro["iters"],
+               "what": "reference run loop (env kernels + policy), graph replay, same run and GPU",
+               "reference": ro["reference_rollout"], "forward_swapped": ro.get("swapped_rollout"),
+               "forward_and_record_swapped": ro.get("swapped_rollout_and_record"),
+               "ratio_forward_swapped": ro.get("R3_swapped_over_reference"),
+               "ratio_forward_and_record_swapped": ro.get("swapped_and_record_over_reference")}
+        rec = child("record", [], 120)
+        if "unavailable" not in rec:
+            out["record_write"] = {k: rec[k] for k in ("reference_k_record_obs_ms", "cfx_record_obs_ms", "speedup",
+                                                       "differing_bytes", "rows_compared")}
+        return out
     except Exception as e:   # a comparison arm must not take the product line down
         return {"unavailable": f"{type(e).__name__}: {e}"}
 
