@@ -20,6 +20,8 @@
 // 11 bytes in three maps) and ~100 SoA words read.
 #include <cuda_runtime.h>
 
+#include <cstddef>
+
 #include "cfx_common.cuh"
 
 namespace cfx {
@@ -258,6 +260,8 @@ static int make_params(const char* who, const cfx_env_view* view, uint8_t* recor
 }
 
 static_assert(sizeof(Shared) <= 48 * 1024, "static shared memory");
+static_assert(offsetof(cfx_env_view, mob_type_id) - offsetof(cfx_env_view, player_position) == 39 * sizeof(void*),
+              "the field pointers of cfx_env_view are contiguous (make_params walks them)");
 
 }  // namespace record
 }  // namespace cfx
