@@ -94,6 +94,7 @@ _SIGS = {
     "cfx_record_obs": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "cfx_record_obs_list": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p,
                                       C.c_void_p]),
+    "cfx_classic_record_obs": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "cfx_sample_actions": (C.c_int, [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int,
                                      C.c_void_p, C.c_void_p, C.c_void_p]),
     "cfx_philox_uniforms": (C.c_int, [C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_int,

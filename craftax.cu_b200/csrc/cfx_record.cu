@@ -263,6 +263,79 @@ static_assert(sizeof(Shared) <= 48 * 1024, "static shared memory");
 static_assert(offsetof(cfx_env_view, mob_type_id) - offsetof(cfx_env_view, player_position) == 39 * sizeof(void*),
               "the field pointers of cfx_env_view are contiguous (make_params walks them)");
 
+
+// ------------------------------------------------------------------ classic game
+// record_obs_kernel (craftax_classic.cu:1884-1890) gives every env a thread that writes its 148
+// bytes one by one: 148 store instructions per warp, each touching 32 different records.  Here a
+// block gathers the records of 128 consecutive envs in shared memory, thread per env (the SoA
+// loads of a warp are contiguous), and writes the 18,944 contiguous bytes out as coalesced words.
+constexpr int kClRows = 7, kClCols = 9, kClCells = kClRows * kClCols, kClMap = 64, kClRowBytes = 32;
+constexpr int kClInv = 12, kClOutOfBounds = 1, kClBlockEnvs = 128;
+static_assert(2 * kClCells + kClInv + 6 + 4 == kClassicRec, "classic record layout");
+
+__global__ void __launch_bounds__(kClBlockEnvs) k_classic_record_rows(const __grid_constant__ cfx_classic_env_view V,
+                                                                     uint8_t* __restrict__ records, int n_envs) {
+    __shared__ __align__(16) uint8_t srec[kClBlockEnvs * kClassicRec];
+    const int t = threadIdx.x;
+    const int e0 = blockIdx.x * kClBlockEnvs, e = e0 + t;
+    const int n = V.num_envs;
+    if (e < n_envs) {
+        uint8_t* o = srec + t * kClassicRec;
+        const int pr = V.player_r[e], pc = V.player_c[e];
+        const uint8_t* map = V.map_packed + (size_t)e * V.map_stride;
+        // view rows: blocks (a nibble per map column; 1 outside the map), mob bytes cleared  (:1061-1100)
+#pragma unroll
+        for (int r = 0; r < kClRows; r++) {
+            const int mr = pr - 3 + r;
+            const bool row_in = mr >= 0 && mr < kClMap;
+#pragma unroll
+            for (int c = 0; c < kClCols; c++) {
+                const int mc = pc - 4 + c;
+                uint8_t blk = kClOutOfBounds;
+                if (row_in && mc >= 0 && mc < kClMap) {
+                    const uint8_t b = map[mr * kClRowBytes + (mc >> 1)];
+                    blk = (mc & 1) ? (b >> 4) : (b & 0x0F);
+                }
+                o[r * kClCols + c] = blk;
+                o[kClCells + r * kClCols + c] = 0;
+            }
+        }
+        // mobs inside the view set their bit  (:1102-1125)
+        auto stamp = [&](const int16_t* rr, const int16_t* cc, const uint8_t* mask, int slots, uint8_t bit) {
+            for (int i = 0; i < slots; i++) {
+                if (!mask[(size_t)i * n + e]) continue;
+                const int dr = rr[(size_t)i * n + e] - pr, dc = cc[(size_t)i * n + e] - pc;
+                if (dr < -3 || dr > 3 || dc < -4 || dc > 4) continue;
+                o[kClCells + (dr + 3) * kClCols + (dc + 4)] |= bit;
+            }
+        };
+        stamp(V.zombie_r, V.zombie_c, V.zombie_mask, 3, 1);
+        stamp(V.cow_r, V.cow_c, V.cow_mask, 3, 2);
+        stamp(V.skel_r, V.skel_c, V.skel_mask, 2, 4);
+        stamp(V.arrow_r, V.arrow_c, V.arrow_mask, 3, 8);
+        // inventory, intrinsics, direction, sleeping, light  (:1590-1603)
+        int idx = 2 * kClCells;
+#pragma unroll
+        for (int i = 0; i < kClInv; i++) o[idx++] = (uint8_t)V.inv[(size_t)i * n + e];
+        o[idx++] = (uint8_t)V.health[e];
+        o[idx++] = (uint8_t)V.food[e];
+        o[idx++] = (uint8_t)V.drink[e];
+        o[idx++] = (uint8_t)V.energy[e];
+        o[idx++] = (uint8_t)V.player_dir[e];
+        o[idx++] = V.is_sleeping[e] ? 1 : 0;
+        const uint32_t light = __float_as_uint(V.light_level[e]);
+        o[idx++] = (uint8_t)light; o[idx++] = (uint8_t)(light >> 8);
+        o[idx++] = (uint8_t)(light >> 16); o[idx++] = (uint8_t)(light >> 24);
+    }
+    __syncthreads();
+    // the block's records are contiguous in global memory: 37 words per env
+    const int envs = min(kClBlockEnvs, n_envs - e0);
+    const int words = envs * (kClassicRec / 4);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(records + (size_t)e0 * kClassicRec);
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(srec);
+    for (int w = t; w < words; w += kClBlockEnvs) dst[w] = src[w];
+}
+
 }  // namespace record
 }  // namespace cfx
 
@@ -299,6 +372,26 @@ extern "C" int cfx_record_obs_list(int device, const cfx_env_view* view, uint8_t
     int blocks = (view->num_envs + record::kBlockEnvs - 1) / record::kBlockEnvs;
     if (blocks > 592) blocks = 592;
     record::k_record_rows_list<<<blocks, record::kBlockThreads, 0, (cudaStream_t)stream>>>(P);
+    CFX_CUDA(cudaGetLastError());
+    return CFX_OK;
+}
+
+extern "C" int cfx_classic_record_obs(int device, const cfx_classic_env_view* view, uint8_t* records, int n,
+                                      void* stream) {
+    CFX_REQUIRE(view != nullptr && records != nullptr, "cfx_classic_record_obs: bad argument");
+    CFX_REQUIRE(view->num_envs > 0 && n > 0 && n <= view->num_envs,
+                "cfx_classic_record_obs: n=%d outside (0, num_envs=%d]", n, view->num_envs);
+    CFX_REQUIRE(((uintptr_t)records & 3) == 0, "cfx_classic_record_obs: records must be 4-byte aligned");
+    CFX_REQUIRE(view->map_packed != nullptr && view->map_stride >= 64 * 32,
+                "cfx_classic_record_obs: the view has no packed map");
+    // every field pointer of the view sits between player_r and light_level
+    const void* const* first = reinterpret_cast<const void* const*>(&view->player_r);
+    const void* const* last = reinterpret_cast<const void* const*>(&view->light_level);
+    for (const void* const* q = first; q <= last; q++)
+        CFX_REQUIRE(*q != nullptr, "cfx_classic_record_obs: field pointer %d of the view is NULL", (int)(q - first));
+    CFX_GUARD(device);
+    const unsigned blocks = (unsigned)((n + record::kClBlockEnvs - 1) / record::kClBlockEnvs);
+    record::k_classic_record_rows<<<blocks, record::kClBlockEnvs, 0, (cudaStream_t)stream>>>(*view, records, n);
     CFX_CUDA(cudaGetLastError());
     return CFX_OK;
 }

@@ -336,6 +336,44 @@ int cfx_classic_expand_obs(int device, const uint8_t* records, float* out, int n
 int cfx_classic_done_to_terminals(int device, const int8_t* done, float* out, int num_envs,
                                   void* stream);
 
+/* Classic game: the 148-byte record of every env from the reference's classic device state, byte
+ * for byte what record_obs_kernel / write_compact_obs write (craftax_classic.cu:1574-1604,
+ * :1884-1890; view gathering :1061-1126): 63 block ids of the 7 x 9 view around the player (1 =
+ * out of bounds), 63 mob bit masks (1 zombie, 2 cow, 4 skeleton, 8 arrow), 12 inventory counts,
+ * health, food, drink, energy, direction, sleeping flag, light level as raw fp32.  The view names
+ * the fields of the reference's EnvSoA (:134-194) it reads: per-env fields are [n], slot-major
+ * fields [slots][n]; map_packed holds map_stride bytes per env, 64 rows of 32 bytes, two columns
+ * per byte with the even column in the low nibble. */
+typedef struct cfx_classic_env_view {
+    int32_t num_envs;
+    const uint8_t* map_packed;
+    uint64_t map_stride;
+    const int16_t* player_r;
+    const int16_t* player_c;
+    const int8_t* player_dir;
+    const int8_t* health;
+    const int8_t* food;
+    const int8_t* drink;
+    const int8_t* energy;
+    const uint8_t* is_sleeping;
+    const int8_t* inv;           /* [12][n] */
+    const int16_t* zombie_r;     /* [3][n] */
+    const int16_t* zombie_c;
+    const uint8_t* zombie_mask;
+    const int16_t* cow_r;        /* [3][n] */
+    const int16_t* cow_c;
+    const uint8_t* cow_mask;
+    const int16_t* skel_r;       /* [2][n] */
+    const int16_t* skel_c;
+    const uint8_t* skel_mask;
+    const int16_t* arrow_r;      /* [3][n] */
+    const int16_t* arrow_c;
+    const uint8_t* arrow_mask;
+    const float* light_level;
+} cfx_classic_env_view;
+
+int cfx_classic_record_obs(int device, const cfx_classic_env_view* view, uint8_t* records, int n, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

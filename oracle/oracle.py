@@ -386,6 +386,21 @@ class RefClassic:
             raise RuntimeError("refcl_lockstep: a cfx call failed (see stderr)")
         return dict(zip(self.LOCKSTEP_KEYS, out.tolist()))
 
+    RECORD_KEYS = ("differing_bytes", "rows_compared", "reference_ms", "cfx_ms", "rows_with_mob", "episode_ends")
+
+    def record_parity(self, n, steps, seed):
+        """record_obs_kernel (craftax_classic.cu:1884-1890) beside cfx_classic_record_obs on the
+        reference's classic CUDA env over `steps` steps of random play with auto-reset; both
+        kernels timed at n envs."""
+        if not hasattr(self.L, "refcl_record_parity"):
+            raise RuntimeError("reference classic shim built without the record comparison")
+        self.L.refcl_record_parity.argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_void_p]
+        out = np.zeros(8, np.float64)
+        rc = self.L.refcl_record_parity(n, steps, seed, _p(out))
+        if rc != 0:
+            raise RuntimeError("refcl_record_parity: a cfx call failed (see stderr)")
+        return dict(zip(self.RECORD_KEYS, out.tolist()))
+
     def forward(self, d_params_ptr, d_rec_ptr, d_prev_done_ptr, d_state_ptr, n, seed, step):
         o = {"logits_av": np.empty((n, self.A + 1), np.float32), "h_enc": np.empty((n, self.H), np.float32),
              "actions": np.empty(n, np.int32), "logprobs": np.empty(n, np.float32)}

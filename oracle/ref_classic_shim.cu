@@ -356,6 +356,128 @@ int refcl_lockstep(int n, int steps, unsigned long long seed, const float* host_
     cublasDestroy(blas);
     return rc;
 }
+
+/* ---- record write: record_obs_kernel (craftax_classic.cu:1884-1890) beside cfx_classic_record_obs ----
+ * The view is filled from the reference's EnvSoA (the binding a maintainer would add).  The env
+ * plays `steps` steps with uniformly random actions and auto-reset; the records of every step
+ * are written with both kernels and compared byte by byte; both kernels are then timed.
+ * out[0] differing bytes, out[1] rows compared, out[2] / out[3] ms per call of the reference's /
+ * the library's kernel (CUDA events, 20 calls), out[4] rows of the last step with a mob in view,
+ * out[5] episode ends. */
+static void refcl_fill_view(const EnvSoA& g, cfx_classic_env_view* w) {
+    memset(w, 0, sizeof(*w));
+    w->num_envs = g.n;
+    w->map_packed = g.map_packed; w->map_stride = MAP_PACKED_SIZE;
+    w->player_r = g.player_r; w->player_c = g.player_c; w->player_dir = g.player_dir;
+    w->health = g.health; w->food = g.food; w->drink = g.drink; w->energy = g.energy;
+    w->is_sleeping = g.is_sleeping; w->inv = g.inv;
+    w->zombie_r = g.zombie_r; w->zombie_c = g.zombie_c; w->zombie_mask = g.zombie_mask;
+    w->cow_r = g.cow_r; w->cow_c = g.cow_c; w->cow_mask = g.cow_mask;
+    w->skel_r = g.skel_r; w->skel_c = g.skel_c; w->skel_mask = g.skel_mask;
+    w->arrow_r = g.arrow_r; w->arrow_c = g.arrow_c; w->arrow_mask = g.arrow_mask;
+    w->light_level = g.light_level;
+}
+__global__ void refcl_k_random_actions(int32_t* act, int n, uint32_t seed, uint32_t step) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n) return;
+    uint32_t h = seed * 0x9E3779B1u ^ (step + 0x7F4A7C15u) * 0x85EBCA77u ^ ((uint32_t)e + 0x165667B1u) * 0xC2B2AE3Du;
+    h ^= h >> 15; h *= 0x2C1B3C6Du; h ^= h >> 12; h *= 0x297A2D39u; h ^= h >> 15;
+    act[e] = (int32_t)(h % NUM_ACTIONS);
+}
+__global__ void refcl_k_count_diff(const uint8_t* a, const uint8_t* b, size_t bytes, unsigned long long* out) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    unsigned long long d = 0;
+    for (; i < bytes; i += (size_t)gridDim.x * blockDim.x) d += a[i] != b[i];
+    if (d) atomicAdd(out, d);
+}
+int refcl_record_parity(int n, int steps, unsigned long long seed, double* out) {
+    cudaStream_t st;
+    RC_CHECK(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    uint8_t* arena;
+    RC_CHECK(cudaMalloc(&arena, soa_bytes(n)));
+    RC_CHECK(cudaMemset(arena, 0, soa_bytes(n)));
+    EnvSoA g = carve_soa(arena, n);
+    cfx_classic_env_view w;
+    refcl_fill_view(g, &w);
+    const size_t bytes = (size_t)n * OBS_DIM_COMPACT;
+    uint8_t *ra, *rb;
+    int8_t* done;
+    int32_t *act, *reset_list, *reset_ctrl;
+    float* rewards;
+    uint64_t* step_ctr;
+    unsigned long long* d_cnt;
+    RC_CHECK(cudaMalloc(&ra, bytes)); RC_CHECK(cudaMalloc(&rb, bytes));
+    RC_CHECK(cudaMalloc(&done, (size_t)n)); RC_CHECK(cudaMalloc(&act, (size_t)n * 4));
+    RC_CHECK(cudaMalloc(&reset_list, (size_t)n * 4)); RC_CHECK(cudaMalloc(&reset_ctrl, 8));
+    RC_CHECK(cudaMalloc(&rewards, (size_t)n * 4)); RC_CHECK(cudaMalloc(&step_ctr, 8));
+    RC_CHECK(cudaMemset(step_ctr, 0, 8));
+    RC_CHECK(cudaMalloc(&d_cnt, 4 * sizeof(unsigned long long)));
+    RC_CHECK(cudaMemset(d_cnt, 0, 4 * sizeof(unsigned long long)));
+    int dev = 0, rc = 0;
+    RC_CHECK(cudaGetDevice(&dev));
+    const int block = 256, grid = (n + block - 1) / block;
+    {
+        int wgrid = (int)(((size_t)n * 32 + RESET_WARP_BLOCK - 1) / RESET_WARP_BLOCK);
+        reset_all_warp_kernel<<<wgrid, RESET_WARP_BLOCK, 0, st>>>(g, n, seed);
+        RC_CHECK(cudaGetLastError());
+    }
+    for (int t = 0; t < steps && rc == 0; t++) {
+        RC_CHECK(cudaMemsetAsync(ra, 0xCD, bytes, st));
+        RC_CHECK(cudaMemsetAsync(rb, 0xEF, bytes, st));
+        record_obs_kernel<<<grid, block, 0, st>>>(g, ra, n);
+        if (cfx_classic_record_obs(dev, &w, rb, n, st) != CFX_OK) { fprintf(stderr, "cfx: %s\n", cfx_last_error()); rc = 1; break; }
+        refcl_k_count_diff<<<1024, 256, 0, st>>>(ra, rb, bytes, d_cnt);
+        RC_CHECK(cudaMemsetAsync(reset_ctrl, 0, 8, st));
+        refcl_k_random_actions<<<grid, block, 0, st>>>(act, n, (uint32_t)seed, (uint32_t)t);
+        step_mark_kernel<<<grid, block, 0, st>>>(g, act, rewards, done, reset_list, reset_ctrl, n);
+        refcl_k_count_done<<<grid, block, 0, st>>>(done, n, d_cnt);   /* counts[2] += episode ends */
+        int rwgrid = (n + RESET_WARP_BLOCK / 32 - 1) / (RESET_WARP_BLOCK / 32);
+        if (rwgrid > 512) rwgrid = 512;
+        reset_warp_ctr_kernel<<<rwgrid, RESET_WARP_BLOCK, 0, st>>>(g, reset_list, reset_ctrl, n, seed, step_ctr);
+        bump_ctr_kernel<<<1, 1, 0, st>>>(step_ctr);
+        RC_CHECK(cudaGetLastError());
+        if ((t & 15) == 15) RC_CHECK(cudaStreamSynchronize(st));
+    }
+    RC_CHECK(cudaStreamSynchronize(st));
+    float ms_ref = 0.f, ms_cfx = 0.f;
+    if (rc == 0) {
+        cudaEvent_t a, b;
+        RC_CHECK(cudaEventCreate(&a)); RC_CHECK(cudaEventCreate(&b));
+        for (int k = 0; k < 3; k++) record_obs_kernel<<<grid, block, 0, st>>>(g, ra, n);
+        RC_CHECK(cudaEventRecord(a, st));
+        for (int k = 0; k < 20; k++) record_obs_kernel<<<grid, block, 0, st>>>(g, ra, n);
+        RC_CHECK(cudaEventRecord(b, st));
+        RC_CHECK(cudaStreamSynchronize(st));
+        RC_CHECK(cudaEventElapsedTime(&ms_ref, a, b));
+        for (int k = 0; k < 3; k++) cfx_classic_record_obs(dev, &w, rb, n, st);
+        RC_CHECK(cudaEventRecord(a, st));
+        for (int k = 0; k < 20; k++) cfx_classic_record_obs(dev, &w, rb, n, st);
+        RC_CHECK(cudaEventRecord(b, st));
+        RC_CHECK(cudaStreamSynchronize(st));
+        RC_CHECK(cudaEventElapsedTime(&ms_cfx, a, b));
+        cudaEventDestroy(a); cudaEventDestroy(b);
+    }
+    unsigned long long cn[4];
+    RC_CHECK(cudaMemcpy(cn, d_cnt, sizeof(cn), cudaMemcpyDeviceToHost));
+    {
+        uint8_t* h = (uint8_t*)malloc(bytes);
+        RC_CHECK(cudaMemcpy(h, rb, bytes, cudaMemcpyDeviceToHost));
+        double with_mob = 0;
+        for (int e = 0; e < n; e++) {
+            int any = 0;
+            for (int c = 0; c < OBS_MAP_CELLS; c++) any |= h[(size_t)e * OBS_DIM_COMPACT + OBS_MAP_CELLS + c] != 0;
+            with_mob += any;
+        }
+        out[4] = with_mob;
+        free(h);
+    }
+    out[0] = (double)cn[0]; out[1] = (double)n * steps; out[2] = ms_ref / 20.0; out[3] = ms_cfx / 20.0;
+    out[5] = (double)cn[2];
+    cudaFree(arena); cudaFree(ra); cudaFree(rb); cudaFree(done); cudaFree(act); cudaFree(reset_list);
+    cudaFree(reset_ctrl); cudaFree(rewards); cudaFree(step_ctr); cudaFree(d_cnt);
+    cudaStreamDestroy(st);
+    return rc;
+}
 #endif
 
 } /* extern "C" */

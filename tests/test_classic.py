@@ -238,3 +238,20 @@ def test_classic_against_the_reference_kernels(cfx, gpu, oracle):
     assert np.array_equal(a, r["actions"])
     assert np.abs(lp - r["logprobs"]).max() < 1e-5             # its logf/expf are the fast-math ones
     pol.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,steps", [(4096 + 32, 160), (1048576, 3)], ids=["play-with-resets", "full-size"])
+def test_classic_record_write_equals_the_reference_kernel(cfx, gpu, oracle, n, steps):
+    """cfx_classic_record_obs writes the bytes record_obs_kernel writes (craftax_classic.cu:1574-1604,
+    :1884-1890) from the reference's own classic device state, over random play with auto-reset."""
+    if not oracle.RefClassic.available():
+        pytest.skip("oracle/_ref/libcfref_classic.so not built (reference sources absent)")
+    cfx.lib()
+    r = oracle.RefClassic().record_parity(n, steps, seed=5)
+    print(f"[classic record] n={n}: {r['rows_compared']:.0f} rows, {r['differing_bytes']:.0f} differing bytes, "
+          f"{r['episode_ends']:.0f} episode ends; record_obs_kernel {r['reference_ms']:.4f} ms, "
+          f"cfx_classic_record_obs {r['cfx_ms']:.4f} ms; {r['rows_with_mob']:.0f} of the last {n} rows show a mob")
+    assert r["rows_compared"] == n * steps and r["differing_bytes"] == 0
+    if steps > 100:
+        assert r["rows_with_mob"] > 0 and r["episode_ends"] > 0
