@@ -632,10 +632,24 @@ def run_classic(args):
             rms = ref.time_forward(d_par.ptr, d_rec.ptr, d_done.ptr, d_st.ptr, n, 3, max(5, min(args.steps, 20)), 1)
             line["reference_classic_forward"] = {"ms_per_step": rms, "value": n / (rms * 1e-3),
                                                  "what": "reference classic kernels + cublasSgemm TF32, record-driven encoder"}
+            # whole rollouts: the reference's classic step (main_classic.cu Rollout::step) from its
+            # own kernels, with the forward taken from this library, and with the record write too
+            if hasattr(ref.L, "refcl_rollout_sps"):
+                pol.close()
+                pol = None
+                del d_par, d_st, d_done
+                r = {m: ref.rollout_sps(n, max(5, min(args.steps, 20)), 3, params, m,
+                                        {"f16": cfx.PREC_F16, "bf16": cfx.PREC_BF16, "fp32": cfx.PREC_FP32}[prec])
+                     for m in (0, 1, 2)}
+                line["reference_classic_rollout"] = {
+                    "unit": UNIT, "reference": r[0], "forward_swapped": r[1], "forward_and_record_swapped": r[2],
+                    "ratio_forward_swapped": r[1] / r[0], "ratio_forward_and_record_swapped": r[2] / r[0],
+                    "what": "reference classic env + policy step (its kernels, cublasSgemm TF32), eager launches"}
     except Exception as e:   # the comparison is optional
         line["reference_classic_forward"] = {"unavailable": str(e)}
     print(json.dumps(line), flush=True)
-    pol.close()
+    if pol is not None:
+        pol.close()
 
 
 def run_ref_rollout(args):

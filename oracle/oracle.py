@@ -386,6 +386,19 @@ class RefClassic:
             raise RuntimeError("refcl_lockstep: a cfx call failed (see stderr)")
         return dict(zip(self.LOCKSTEP_KEYS, out.tolist()))
 
+    def rollout_sps(self, n, steps, seed, params, mode, precision):
+        """Whole classic rollouts on the GPU, env-steps per second: mode 0 the reference's own step
+        (main_classic.cu Rollout::step), 1 with the policy half from libcfx, 2 with the record
+        write from libcfx too."""
+        self.L.refcl_rollout_sps.restype = C.c_double
+        self.L.refcl_rollout_sps.argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_void_p, C.c_int, C.c_int]
+        p = np.ascontiguousarray(params, np.float32)
+        assert p.size == self.param_count
+        v = self.L.refcl_rollout_sps(n, steps, seed, _p(p), mode, precision)
+        if v <= 0:
+            raise RuntimeError("refcl_rollout_sps: a cfx call failed (see stderr)")
+        return v
+
     RECORD_KEYS = ("differing_bytes", "rows_compared", "reference_ms", "cfx_ms", "rows_with_mob", "episode_ends")
 
     def record_parity(self, n, steps, seed):

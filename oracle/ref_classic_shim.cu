@@ -478,6 +478,137 @@ int refcl_record_parity(int n, int steps, unsigned long long seed, double* out) 
     cudaStreamDestroy(st);
     return rc;
 }
+
+/* ---- whole classic rollouts: the step of main_classic.cu's Rollout::step (:439-474) built from the
+ * reference's own kernels, and the same step with the policy half (and the record write) taken
+ * from the library.  mode 0: reference (encode_env_warp_kernel, record_obs_kernel, cublasSgemm in
+ * its TF32 math mode :283 + mingru_epi_fwd_kernel per layer, value_sample_kernel); mode 1:
+ * record_obs_kernel + cfx_policy_forward; mode 2: cfx_classic_record_obs + cfx_policy_forward.
+ * The env half (step_mark_kernel, reset_warp_ctr_kernel, bump_ctr_kernel) is the reference's in
+ * every mode.  Random-init weights of the reference's own layout are passed in; returns
+ * env-steps per second over `steps` steps after 3 warm-up steps (CUDA events, eager launches). */
+double refcl_rollout_sps(int n, int steps, unsigned long long seed, const float* host_params, int mode,
+                         int precision) {
+    cublasHandle_t blas;
+    RC_BLAS(cublasCreate(&blas));
+    RC_BLAS(cublasSetMathMode(blas, CUBLAS_TF32_TENSOR_OP_MATH));
+    cudaStream_t st;
+    RC_CHECK(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    RC_BLAS(cublasSetStream(blas, st));
+    uint8_t* arena;
+    RC_CHECK(cudaMalloc(&arena, soa_bytes(n)));
+    RC_CHECK(cudaMemset(arena, 0, soa_bytes(n)));
+    EnvSoA g = carve_soa(arena, n);
+    float* d_params;
+    RC_CHECK(cudaMalloc(&d_params, (size_t)PARAM_COUNT * sizeof(float)));
+    RC_CHECK(cudaMemcpy(d_params, host_params, (size_t)PARAM_COUNT * sizeof(float), cudaMemcpyHostToDevice));
+    const float* W_enc = d_params + PARAM_W_ENC;
+    const float* b_enc = d_params + PARAM_B_ENC;
+    const float* W_gru = d_params + PARAM_W_GRU;
+    const float* W_a = d_params + PARAM_W_A;
+    const float* b_a = d_params + PARAM_B_A;
+    const float* W_v = d_params + PARAM_W_V;
+    const float* b_v = d_params + PARAM_B_V;
+    const size_t hn = (size_t)HIDDEN * n;
+    float *h_enc, *hout[2], *h3, *pre, *logits, *h_state, *lp, *val, *rewards, *term;
+    int32_t *act, *reset_list, *reset_ctrl;
+    int8_t* done[2];
+    uint8_t* rec;
+    uint64_t* step_ctr;
+    RC_CHECK(cudaMalloc(&h_enc, hn * sizeof(float)));
+    RC_CHECK(cudaMalloc(&hout[0], hn * sizeof(float)));
+    RC_CHECK(cudaMalloc(&hout[1], hn * sizeof(float)));
+    RC_CHECK(cudaMalloc(&h3, hn * sizeof(float)));
+    RC_CHECK(cudaMalloc(&pre, (size_t)GRU_OUT * n * sizeof(float)));
+    RC_CHECK(cudaMalloc(&logits, (size_t)NUM_ACTIONS * n * sizeof(float)));
+    RC_CHECK(cudaMalloc(&h_state, (size_t)GRU_LAYERS * hn * sizeof(float)));
+    RC_CHECK(cudaMemset(h_state, 0, (size_t)GRU_LAYERS * hn * sizeof(float)));
+    RC_CHECK(cudaMalloc(&lp, (size_t)n * 4)); RC_CHECK(cudaMalloc(&val, (size_t)n * 4));
+    RC_CHECK(cudaMalloc(&rewards, (size_t)n * 4)); RC_CHECK(cudaMalloc(&term, (size_t)n * 4));
+    RC_CHECK(cudaMalloc(&act, (size_t)n * 4)); RC_CHECK(cudaMalloc(&reset_list, (size_t)n * 4));
+    RC_CHECK(cudaMalloc(&reset_ctrl, 8));
+    RC_CHECK(cudaMalloc(&done[0], (size_t)n)); RC_CHECK(cudaMalloc(&done[1], (size_t)n));
+    RC_CHECK(cudaMalloc(&rec, (size_t)n * OBS_DIM_COMPACT));
+    RC_CHECK(cudaMalloc(&step_ctr, 8));
+    RC_CHECK(cudaMemset(step_ctr, 0, 8));
+    int dev = 0;
+    RC_CHECK(cudaGetDevice(&dev));
+    cfx_policy* cp = NULL;
+    cfx_classic_env_view w;
+    refcl_fill_view(g, &w);
+    if (mode != 0 && (cfx_policy_create_classic(&cp, dev, n, HIDDEN, GRU_LAYERS, NUM_ACTIONS, precision) != CFX_OK ||
+                      cfx_policy_set_weights(cp, d_params, PARAM_COUNT, 1) != CFX_OK)) {
+        fprintf(stderr, "cfx: %s\n", cfx_last_error());
+        return -1.0;
+    }
+    const int block = 256, grid = (n + block - 1) / block;
+    const int wgrid = (int)(((size_t)n * 32 + block - 1) / block);
+    {
+        int rgrid = (int)(((size_t)n * 32 + RESET_WARP_BLOCK - 1) / RESET_WARP_BLOCK);
+        reset_all_warp_kernel<<<rgrid, RESET_WARP_BLOCK, 0, st>>>(g, n, seed);
+        RC_CHECK(cudaGetLastError());
+        RC_CHECK(cudaStreamSynchronize(st));
+    }
+    const float one = 1.0f, zero = 0.0f;
+    const int warm = 3;
+    cudaEvent_t ea, eb;
+    RC_CHECK(cudaEventCreate(&ea)); RC_CHECK(cudaEventCreate(&eb));
+    for (int t = 0; t < warm + steps; t++) {
+        if (t == warm) RC_CHECK(cudaEventRecord(ea, st));
+        const int8_t* prev = (t == 0) ? NULL : done[(t - 1) & 1];
+        RC_CHECK(cudaMemsetAsync(reset_ctrl, 0, 8, st));
+        if (mode == 0) {
+            encode_env_warp_kernel<<<wgrid, block, 0, st>>>(g, W_enc, b_enc, h_enc, n);
+            record_obs_kernel<<<grid, block, 0, st>>>(g, rec, n);
+            const float* x = h_enc;
+            for (int l = 0; l < GRU_LAYERS; l++) {
+                RC_BLAS(cublasSgemm(blas, CUBLAS_OP_T, CUBLAS_OP_N, GRU_OUT, n, HIDDEN, &one,
+                                    W_gru + (size_t)l * GRU_OUT * HIDDEN, HIDDEN, x, HIDDEN, &zero, pre, GRU_OUT));
+                float* xn = (l < GRU_LAYERS - 1) ? hout[l & 1] : h3;
+                mingru_epi_fwd_kernel<<<(int)((hn + block - 1) / block), block, 0, st>>>(
+                    pre, x, h_state + (size_t)l * hn, xn, NULL, prev, n);
+                x = xn;
+            }
+            RC_BLAS(cublasSgemm(blas, CUBLAS_OP_T, CUBLAS_OP_N, NUM_ACTIONS, n, HIDDEN, &one, W_a, HIDDEN, h3, HIDDEN,
+                                &zero, logits, NUM_ACTIONS));
+            value_sample_kernel<<<grid, block, 0, st>>>(h3, logits, b_a, W_v, b_v, act, lp, val, n, seed, step_ctr);
+        } else {
+            if (mode == 2) {
+                if (cfx_classic_record_obs(dev, &w, rec, n, st) != CFX_OK) { fprintf(stderr, "cfx: %s\n", cfx_last_error()); return -1.0; }
+            } else {
+                record_obs_kernel<<<grid, block, 0, st>>>(g, rec, n);
+            }
+            if (prev && cfx_classic_done_to_terminals(dev, prev, term, n, st) != CFX_OK) return -1.0;
+            cfx_forward_io io;
+            memset(&io, 0, sizeof(io));
+            io.records = rec;
+            io.prev_terminals = prev ? term : NULL;
+            io.actions = act; io.logprobs = lp; io.values = val;
+            io.seed = seed;
+            if (cfx_policy_forward(cp, &io, st) != CFX_OK) { fprintf(stderr, "cfx: %s\n", cfx_last_error()); return -1.0; }
+        }
+        step_mark_kernel<<<grid, block, 0, st>>>(g, act, rewards, done[t & 1], reset_list, reset_ctrl, n);
+        int rwgrid = (n + RESET_WARP_BLOCK / 32 - 1) / (RESET_WARP_BLOCK / 32);
+        if (rwgrid > 512) rwgrid = 512;
+        reset_warp_ctr_kernel<<<rwgrid, RESET_WARP_BLOCK, 0, st>>>(g, reset_list, reset_ctrl, n, seed, step_ctr);
+        bump_ctr_kernel<<<1, 1, 0, st>>>(step_ctr);
+        RC_CHECK(cudaGetLastError());
+    }
+    RC_CHECK(cudaEventRecord(eb, st));
+    RC_CHECK(cudaStreamSynchronize(st));
+    float ms = 0.f;
+    RC_CHECK(cudaEventElapsedTime(&ms, ea, eb));
+    if (cp && cfx_policy_check(cp, st) != CFX_OK) { fprintf(stderr, "cfx: %s\n", cfx_last_error()); ms = -1.f; }
+    if (cp) cfx_policy_destroy(cp);
+    cudaEventDestroy(ea); cudaEventDestroy(eb);
+    cudaFree(arena); cudaFree(d_params); cudaFree(h_enc); cudaFree(hout[0]); cudaFree(hout[1]); cudaFree(h3);
+    cudaFree(pre); cudaFree(logits); cudaFree(h_state); cudaFree(lp); cudaFree(val); cudaFree(rewards); cudaFree(term);
+    cudaFree(act); cudaFree(reset_list); cudaFree(reset_ctrl); cudaFree(done[0]); cudaFree(done[1]); cudaFree(rec);
+    cudaFree(step_ctr);
+    cudaStreamDestroy(st);
+    cublasDestroy(blas);
+    return ms > 0.f ? (double)n * (double)steps / ((double)ms * 1e-3) : -1.0;
+}
 #endif
 
 } /* extern "C" */
