@@ -396,6 +396,19 @@ def reference_rollout(args, prec):
         if "unavailable" not in rec:
             out["record_write"] = {k: rec[k] for k in ("reference_k_record_obs_ms", "cfx_record_obs_ms", "speedup",
                                                        "differing_bytes", "rows_compared")}
+        # the classic game at its configuration's size: forward, and the reference's classic step
+        # with the forward (and the record write) swapped
+        try:
+            cl = json.loads([ln for ln in subprocess.run(
+                [sys.executable, os.path.abspath(__file__), "--impl", "classic", "--envs", "1048576", "--steps", "20",
+                 "--warmup", "3", "--precision", prec], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+                timeout=240, env={k: v for k, v in os.environ.items() if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE")}
+            ).stdout.splitlines() if ln.startswith("{")][-1])
+            out["classic_game"] = {"envs": 1048576, "forward_ms": cl["ms_per_step"], "forward_env_steps_per_s": cl["value"],
+                                   "forward_roofline_frac": cl["roofline"]["frac"],
+                                   "rollout": cl.get("reference_classic_rollout")}
+        except Exception as e:
+            out["classic_game"] = {"unavailable": f"{type(e).__name__}: {e}"}
         return out
     except Exception as e:   # a comparison arm must not take the product line down
         return {"unavailable": f"{type(e).__name__}: {e}"}
