@@ -524,7 +524,8 @@ def run_ref_cublas(args):
 
 def run_sweep(args):
     """Synthetic fused-forward sweep: batch x hidden {128, 256} x MinGRU depth x operand type
-    (the instantiations built), one JSON line per point with the fused-roofline fraction.  Under
+    (the instantiations built), one JSON line per point with the fused-roofline fraction; hidden
+    512 runs through the strict fp32 mode and is labelled so.  Under
     torchrun every rank sweeps its own GPU with its own env slice (`--envs`-independent: the batch
     sizes are per GPU) and a point's time is the max over ranks.  Points of the published sweep
     that are not built (hidden 512, tf32 operands) are listed once as unavailable, with the reason."""
@@ -546,7 +547,12 @@ def run_sweep(args):
         del rec
         d_act = cfx.DeviceBuffer((n,), np.int32, local)
         d_lav = cfx.DeviceBuffer((n, A + 1), np.float32, local)
-        for H, L, prec in [(h, l, p) for h in (256, 128) for l in (2, 3) for p in ("f16", "bf16")]:
+        # hidden 512 has no fused instantiation; its points run through the strict fp32 mode
+        # (CUDA-core kernels in the reference's summation order) and say so
+        fused_points = [(h, l, p) for h in (256, 128) for l in (2, 3) for p in ("f16", "bf16")]
+        strict_points = [(512, l, "fp32") for l in (2, 3)]
+        points = strict_points if args.sweep_hidden == 512 else fused_points + strict_points
+        for H, L, prec in points:
             pol = cfx.Policy(n, H, L, A, prec, device=local)
             pol.set_weights(init_weights(H, L, A, seed=0))
             for _ in range(3):
@@ -554,6 +560,8 @@ def run_sweep(args):
                                    env_offset=rank * n, bump_step=True)
             pol.check()
             steps = 20 if n <= 262144 else 8
+            if prec == "fp32":
+                steps = 4 if n <= 262144 else 2
             if dist is not None:
                 import torch
                 dist.barrier()
@@ -569,7 +577,8 @@ def run_sweep(args):
             flops, byts = algorithmic_work(H, L)
             t_roof = max(n * byts / (peaks["hbm_gbs"] * 1e9), n * flops / (peaks["bf16_tflops"] * 1e12))
             if rank == 0:
-                print(json.dumps({"sweep": "fused forward", "n_gpus": world, "envs_per_gpu": n, "hidden": H,
+                print(json.dumps({"sweep": "fused forward" if prec != "fp32" else "strict fp32 forward (CUDA cores)",
+                                  "n_gpus": world, "envs_per_gpu": n, "hidden": H,
                                   "layers": L, "operands": prec, "ms_per_step": ms,
                                   "env_steps_per_s": world * n / (ms * 1e-3),
                                   "fused_roofline_ms": t_roof * 1e3, "fused_roofline_frac": t_roof * 1e3 / ms,
@@ -579,7 +588,7 @@ def run_sweep(args):
     if rank == 0:
         print(json.dumps({"sweep": "fused forward", "unavailable": {
             "hidden 512": "the 16-bit input and output of a 512-wide layer fill all 512 tensor-memory columns of a "
-                          "128-env tile, leaving none for the accumulators",
+                          "128-env tile, leaving none for the accumulators; its points above are the strict fp32 mode",
             "tf32 operands": "fp32 activations of K = 256 take 256 tensor-memory columns per buffer; fp16 operands "
                              "carry the same 11-bit significand"}}), flush=True)
     if dist is not None:
@@ -759,6 +768,8 @@ def main():
     ap.add_argument("--sustained-ms", type=float, default=200.0,
                     help="length of the back-to-back run reported as `sustained`")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
+    ap.add_argument("--sweep-hidden", type=int, default=0, choices=[0, 512],
+                    help="--impl sweep: 512 runs only the hidden-512 points (strict fp32 mode)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "cfx" else args.warmup
     if args.precision is None:
